@@ -1,0 +1,87 @@
+// Shared helpers of the hand-written sm_100a kernels.  Every .cu file of this folder is
+// one translation unit that becomes one shared library with a C ABI: launchers take raw
+// device pointers and a stream, return 0 or an error code, and leave a message that
+// qwb_last_error() returns.  Nothing here allocates device memory; callers pass buffers.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define QWB_DT_F32 0
+#define QWB_DT_BF16 1
+
+#define QWB_ERR_ARG 1     // a size or option the kernel does not take
+#define QWB_ERR_CUDA 2    // the launch itself failed
+
+static thread_local char qwb_err_buf[512] = "";
+
+static int qwb_fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(qwb_err_buf, sizeof(qwb_err_buf), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+extern "C" const char* qwb_last_error() { return qwb_err_buf; }
+
+static int qwb_check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    return 0;
+}
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f32(float x) { return x; }
+__device__ __forceinline__ float to_f32(bf16 x) { return __bfloat162float(x); }
+template <typename T> __device__ __forceinline__ T from_f32(float x);
+template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float x) { return __float2bfloat16_rn(x); }
+
+// 16-byte vectors of T: 4 floats or 8 bfloat16.
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+    static constexpr int N = 4;
+    float4 v;
+    __device__ __forceinline__ void get(float* out) const { out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w; }
+};
+template <> struct Vec16<bf16> {
+    static constexpr int N = 8;
+    uint4 v;
+    __device__ __forceinline__ void get(float* out) const {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            out[2 * i] = __uint_as_float(w[i] << 16);
+            out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block in a fixed order (the same for every launch): warps first, then the
+// warps' partial sums in index order.  `scratch` holds at least 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = 0.f;
+    for (int w = 0; w < nwarp; ++w) total += scratch[w];
+    return total;
+}

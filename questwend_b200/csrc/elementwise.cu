@@ -1,0 +1,138 @@
+// Embedding gather, RMS norm (with the residual sum folded in) and the gated SiLU
+// product.  The residual stream and the sums of squares are 32-bit in both engines.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------
+// h[t,:] = float(E[id_t,:]).  A row gather without scaling (the reference:
+// core/runtime.cpp:1001, ggml-cuda/getrows.cu:73-102).  An id outside [0, V) writes a
+// row of zeros and records the first such token in *bad_token (if given).
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_gather_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                                    float* __restrict__ out, int D, int V, int* bad_token) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* o = out + (size_t)t * D;
+    if (id < 0 || id >= V) {
+        if (bad_token && threadIdx.x == 0) atomicCAS(bad_token, -1, t);
+        for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = 0.f;
+        return;
+    }
+    const T* row = table + (size_t)id * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = to_f32(row[i]);
+}
+
+extern "C" int qwb_embed_gather(const int* ids, const void* table, int table_dtype, float* out,
+                                int T, int D, int V, int* bad_token, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (D <= 0 || V <= 0) return qwb_fail(QWB_ERR_ARG, "embed_gather: bad sizes D=%d V=%d", D, V);
+    const int block = D >= 1024 ? 256 : 128;
+    if (table_dtype == QWB_DT_F32)
+        embed_gather_kernel<float><<<T, block, 0, stream>>>(ids, (const float*)table, out, D, V, bad_token);
+    else if (table_dtype == QWB_DT_BF16)
+        embed_gather_kernel<bf16><<<T, block, 0, stream>>>(ids, (const bf16*)table, out, D, V, bad_token);
+    else
+        return qwb_fail(QWB_ERR_ARG, "embed_gather: unknown dtype %d", table_dtype);
+    return qwb_check_launch("embed_gather");
+}
+
+// ---------------------------------------------------------------------------------
+// RMS norm over rows of D:  y = v * rsqrt(mean(v^2) + eps) * w,  v = x (+ delta).
+// (the reference: core/runtime.cpp:1018-1019, ggml-cuda/norm.cu:76-155.)
+//   x      [rows_in, D] float   the residual stream
+//   delta  [rows_in, D] float   optional: the sum x + delta is formed in 32-bit first
+//   sum_out[rows_in, D] float   optional: where x + delta is written (may be x itself)
+//   rows   [n_rows] int         optional: row r of the output is made from row rows[r]
+//   out    [n_rows, D]  float or bfloat16
+// One block per output row; the row is kept in shared memory between the two passes.
+// ---------------------------------------------------------------------------------
+template <typename TOut>
+__global__ void rmsnorm_kernel(const float* x, const float* __restrict__ delta,
+                               float* sum_out, const float* __restrict__ w, TOut* __restrict__ out,
+                               const int* __restrict__ rows, int D, float eps) {
+    extern __shared__ float row_cache[];
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const size_t src = (size_t)(rows ? rows[r] : r) * D;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        float v = x[src + i];
+        if (delta) v += delta[src + i];
+        if (sum_out) sum_out[src + i] = v;
+        row_cache[i] = v;
+        ss += v * v;
+    }
+    const float total = block_sum(ss, red);
+    const float scale = rsqrtf(total / (float)D + eps);
+    TOut* o = out + (size_t)r * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = from_f32<TOut>(row_cache[i] * scale * w[i]);
+}
+
+extern "C" int qwb_rmsnorm(const float* x, const float* delta, float* sum_out, const float* w,
+                           void* out, int out_dtype, const int* rows, int n_rows, int D, float eps,
+                           cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (D <= 0) return qwb_fail(QWB_ERR_ARG, "rmsnorm: bad width %d", D);
+    const size_t smem = (size_t)D * sizeof(float);
+    if (smem > 200 * 1024) return qwb_fail(QWB_ERR_ARG, "rmsnorm: width %d does not fit in shared memory (max %d)", D, 200 * 1024 / 4);
+    const int block = D >= 2048 ? 512 : (D >= 512 ? 256 : 128);
+    cudaError_t e = cudaSuccess;
+    if (out_dtype == QWB_DT_F32) {
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "rmsnorm: %s", cudaGetErrorString(e));
+        rmsnorm_kernel<float><<<n_rows, block, smem, stream>>>(x, delta, sum_out, w, (float*)out, rows, D, eps);
+    } else if (out_dtype == QWB_DT_BF16) {
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "rmsnorm: %s", cudaGetErrorString(e));
+        rmsnorm_kernel<bf16><<<n_rows, block, smem, stream>>>(x, delta, sum_out, w, (bf16*)out, rows, D, eps);
+    } else {
+        return qwb_fail(QWB_ERR_ARG, "rmsnorm: unknown dtype %d", out_dtype);
+    }
+    return qwb_check_launch("rmsnorm");
+}
+
+// ---------------------------------------------------------------------------------
+// a[t,f] = silu(g[t,f]) * u[t,f], silu(x) = x / (1 + exp(-x)), from one [T, 2F] float
+// matrix whose first F columns are the gate and last F the up projection (the reference:
+// core/runtime.cpp:1074-1076, ggml-cuda/unary.cuh:96-98).
+// ---------------------------------------------------------------------------------
+template <typename TOut>
+__global__ void silu_mul_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int T, int F) {
+    const size_t n = (size_t)T * F;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / F, f = i - t * F;
+        const float g = gu[t * 2 * F + f];
+        const float u = gu[t * 2 * F + F + f];
+        out[i] = from_f32<TOut>(g / (1.f + expf(-g)) * u);
+    }
+}
+
+extern "C" int qwb_silu_mul(const float* gate_up, void* out, int out_dtype, int T, int F, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (F <= 0) return qwb_fail(QWB_ERR_ARG, "silu_mul: bad width %d", F);
+    const size_t n = (size_t)T * F;
+    const int block = 256;
+    const int grid = (int)((n + block - 1) / block < 148 * 16 ? (n + block - 1) / block : 148 * 16);
+    if (out_dtype == QWB_DT_F32)
+        silu_mul_kernel<float><<<grid, block, 0, stream>>>(gate_up, (float*)out, T, F);
+    else if (out_dtype == QWB_DT_BF16)
+        silu_mul_kernel<bf16><<<grid, block, 0, stream>>>(gate_up, (bf16*)out, T, F);
+    else
+        return qwb_fail(QWB_ERR_ARG, "silu_mul: unknown dtype %d", out_dtype);
+    return qwb_check_launch("silu_mul");
+}
+
+// out[i] += delta[i]: the residual sum on its own, for blocks that end without a norm.
+__global__ void add_inplace_kernel(float* __restrict__ out, const float* __restrict__ delta, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] += delta[i];
+}
+
+extern "C" int qwb_add_inplace(float* out, const float* delta, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const int block = 256;
+    const long long want = (n + block - 1) / block;
+    const int grid = (int)(want < 148 * 16 ? want : 148 * 16);
+    add_inplace_kernel<<<grid, block, 0, stream>>>(out, delta, (size_t)n);
+    return qwb_check_launch("add_inplace");
+}

@@ -1,0 +1,124 @@
+// Rotary position encoding and the write into the paged key/value cache.
+//
+// Two kernels.  rope_table makes cos/sin of every token's angles once per step (all
+// layers and heads share them); qk_norm_rope_store then, per token and head, takes the
+// 32-bit output of the fused Q/K/V projection, applies the per-head RMS norm (Q and K),
+// rotates the pairs (i, i + n_rot/2) (Q and K), writes Q for the attention kernel and
+// stores K and V at the token's place in the cache.  The reference runs these as
+// rms_norm + mul + rope (+ set_rows) (core/runtime.cpp:1047-1051, 693-706;
+// ggml-cuda/rope.cu:676-754).
+#include "common.cuh"
+
+// angle[t,i] = pos[t] * inv_freq[i], in double: positions of thousands keep their digits.
+__global__ void rope_table_kernel(const int* __restrict__ pos, const double* __restrict__ inv_freq,
+                                  float* __restrict__ cos_out, float* __restrict__ sin_out, int T, int half) {
+    const int n = T * half;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const int t = i / half, j = i - t * half;
+        double s, c;
+        sincos((double)pos[t] * inv_freq[j], &s, &c);
+        cos_out[i] = (float)c;
+        sin_out[i] = (float)s;
+    }
+}
+
+extern "C" int qwb_rope_table(const int* pos, const double* inv_freq, float* cos_out, float* sin_out,
+                              int T, int half, cudaStream_t stream) {
+    if (T <= 0 || half <= 0) return 0;
+    const int n = T * half, block = 128;
+    int grid = (n + block - 1) / block;
+    if (grid > 148 * 8) grid = 148 * 8;
+    rope_table_kernel<<<grid, block, 0, stream>>>(pos, inv_freq, cos_out, sin_out, T, half);
+    return qwb_check_launch("rope_table");
+}
+
+// One warp per (token, head).  Heads 0..Hq-1 are queries, then Hkv key heads, then Hkv
+// value heads, in the order of the fused projection's columns.
+//   qkv        [T, (Hq + 2 Hkv) * hd] float
+//   q_weight, k_weight [hd] float, or null for no norm
+//   cos_t, sin_t [T, rot/2] float
+//   tok_seq, tok_pos [T]: the batch row and the position of each token
+//   page_table [B, table_width]: the pages of each batch row, in order
+//   q_out      [T, Hq, hd]
+//   k_pool, v_pool [n_pages, Hkv, page_size, hd]
+template <typename TOut>
+__global__ void qk_norm_rope_store_kernel(const float* __restrict__ qkv, const float* __restrict__ q_weight,
+                                          const float* __restrict__ k_weight, const float* __restrict__ cos_t,
+                                          const float* __restrict__ sin_t, const int* __restrict__ tok_seq,
+                                          const int* __restrict__ tok_pos, const int* __restrict__ page_table,
+                                          TOut* __restrict__ q_out, TOut* __restrict__ k_pool, TOut* __restrict__ v_pool,
+                                          int Hq, int Hkv, int hd, int rot, float eps, int page_size,
+                                          int table_width, int store_kv) {
+    const int t = blockIdx.x;
+    const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    const int n_heads = Hq + 2 * Hkv;
+    if (head >= n_heads) return;
+    const bool is_q = head < Hq, is_k = !is_q && head < Hq + Hkv;
+    if (!is_q && !store_kv) return;
+    const float* src = qkv + ((size_t)t * n_heads + head) * hd;
+
+    TOut* dst;
+    if (is_q) {
+        dst = q_out + ((size_t)t * Hq + head) * hd;
+    } else {
+        const int kvh = is_k ? head - Hq : head - Hq - Hkv;
+        const int p = tok_pos[t];
+        const int page = page_table[(size_t)tok_seq[t] * table_width + p / page_size];
+        TOut* pool = is_k ? k_pool : v_pool;
+        dst = pool + (((size_t)page * Hkv + kvh) * page_size + (p % page_size)) * hd;
+    }
+
+    const float* nw = is_q ? q_weight : (is_k ? k_weight : nullptr);
+    float scale = 1.f;
+    if (nw) {
+        float ss = 0.f;
+        for (int i = lane; i < hd; i += 32) { const float v = src[i]; ss += v * v; }
+        ss = warp_sum(ss);
+        scale = rsqrtf(ss / (float)hd + eps);
+    }
+    if (is_q || is_k) {
+        const int half = rot >> 1;
+        const float* c = cos_t + (size_t)t * half;
+        const float* s = sin_t + (size_t)t * half;
+        for (int i = lane; i < half; i += 32) {
+            float a = src[i] * scale, b = src[i + half] * scale;
+            if (nw) { a *= nw[i]; b *= nw[i + half]; }
+            dst[i] = from_f32<TOut>(a * c[i] - b * s[i]);
+            dst[i + half] = from_f32<TOut>(a * s[i] + b * c[i]);
+        }
+        for (int i = rot + lane; i < hd; i += 32) {
+            float a = src[i] * scale;
+            if (nw) a *= nw[i];
+            dst[i] = from_f32<TOut>(a);
+        }
+    } else {
+        for (int i = lane; i < hd; i += 32) dst[i] = from_f32<TOut>(src[i]);
+    }
+}
+
+extern "C" int qwb_qk_norm_rope_store(const float* qkv, const float* q_weight, const float* k_weight,
+                                      const float* cos_t, const float* sin_t, const int* tok_seq,
+                                      const int* tok_pos, const int* page_table, void* q_out, void* k_pool,
+                                      void* v_pool, int dtype, int T, int Hq, int Hkv, int hd, int rot,
+                                      float eps, int page_size, int table_width, int store_kv,
+                                      cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (Hq <= 0 || Hkv <= 0 || hd <= 0 || rot < 0 || rot > hd || (rot & 1) || page_size <= 0 || table_width <= 0)
+        return qwb_fail(QWB_ERR_ARG, "qk_norm_rope_store: bad sizes Hq=%d Hkv=%d hd=%d rot=%d page=%d width=%d",
+                        Hq, Hkv, hd, rot, page_size, table_width);
+    const int warps = 4;
+    dim3 grid(T, (Hq + 2 * Hkv + warps - 1) / warps);
+    if (grid.y > 65535) return qwb_fail(QWB_ERR_ARG, "qk_norm_rope_store: too many heads (%d)", Hq + 2 * Hkv);
+    if (dtype == QWB_DT_F32)
+        qk_norm_rope_store_kernel<float><<<grid, warps * 32, 0, stream>>>(
+            qkv, q_weight, k_weight, cos_t, sin_t, tok_seq, tok_pos, page_table, (float*)q_out, (float*)k_pool,
+            (float*)v_pool, Hq, Hkv, hd, rot, eps, page_size, table_width, store_kv);
+    else if (dtype == QWB_DT_BF16)
+        qk_norm_rope_store_kernel<bf16><<<grid, warps * 32, 0, stream>>>(
+            qkv, q_weight, k_weight, cos_t, sin_t, tok_seq, tok_pos, page_table, (bf16*)q_out, (bf16*)k_pool,
+            (bf16*)v_pool, Hq, Hkv, hd, rot, eps, page_size, table_width, store_kv);
+    else
+        return qwb_fail(QWB_ERR_ARG, "qk_norm_rope_store: unknown dtype %d", dtype);
+    return qwb_check_launch("qk_norm_rope_store");
+}

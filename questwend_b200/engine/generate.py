@@ -1,0 +1,160 @@
+"""The generation loop above the step function.
+
+The reference's loop is for one sequence (cli/main.cpp:408-425): run the prompt,
+then sample, stop if the token is a stop token (it is neither emitted nor counted),
+emit, run the token, until ``max_tokens``.  Here the same loop runs for batches:
+as many requests as fit start together with their whole prompts in one step; every
+later step brings one token for each sequence that is still going; a sequence that
+ends leaves the batch and gives its slot back at once; when a batch is done the next
+requests start in the slots that came free.
+
+The decisions (who starts, who ends and why, who goes on) use nothing of the
+device, so they can be followed with any object that has ``open_sequences``,
+``close_sequences``, ``step``, ``max_batch`` and ``cache``-like limits.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+
+from ..cache.manager import pages_for
+from ..sampling.params import GREEDY, SamplingParams
+from ..sampling.sampler import DeviceSampler, PenaltyWindow
+from .engine import StepEntry
+
+FINISH_STOP = "stop"          # a stop token was sampled
+FINISH_LENGTH = "length"      # max_new_tokens were emitted
+FINISH_CONTEXT = "context"    # the sequence reached the longest length the cache allows
+
+
+@dataclass
+class GenerationResult:
+    tokens: list = field(default_factory=list)
+    finish_reason: str = ""
+    prompt_tokens: int = 0
+
+
+@dataclass
+class GenerationStats:
+    prompt_tokens: int = 0
+    generated_tokens: int = 0
+    prefill_seconds: float = 0.0
+    decode_seconds: float = 0.0
+    batches: int = 0
+    steps: int = 0
+
+    def line(self) -> str:
+        """The reference's speed line (cli/main.cpp:427-432)."""
+        pf = self.prompt_tokens / self.prefill_seconds if self.prefill_seconds > 0 else 0.0
+        gen = self.generated_tokens / self.decode_seconds if self.decode_seconds > 0 else 0.0
+        return (f"[prefill: {self.prompt_tokens} tok in {self.prefill_seconds:.3f} s = {pf:.1f} tok/s | "
+                f"gen: {self.generated_tokens} tok in {self.decode_seconds:.3f} s = {gen:.1f} tok/s]")
+
+
+def plan_batches(prompt_lengths, max_new_tokens: int, max_batch: int, max_tokens: int, max_seq_len: int):
+    """Cut the requests, in order, into batches that fit: at most ``max_batch`` sequences, and
+    pages for every sequence at its longest (prompt + new tokens, capped by ``max_seq_len``)."""
+    batches, cur, cur_pages = [], [], 0
+    total_pages = pages_for(max_tokens)
+    for i, n in enumerate(prompt_lengths):
+        need = pages_for(min(n + max_new_tokens, max_seq_len))
+        if need > total_pages:
+            raise ValueError(f"request {i}: {n} prompt tokens and {max_new_tokens} new tokens need {need} pages; "
+                             f"the cache has {total_pages} (max_tokens={max_tokens})")
+        if cur and (len(cur) >= max_batch or cur_pages + need > total_pages):
+            batches.append(cur)
+            cur, cur_pages = [], 0
+        cur.append(i)
+        cur_pages += need
+    if cur:
+        batches.append(cur)
+    return batches
+
+
+def generate(engine, prompts, max_new_tokens: int = 128, sampling: SamplingParams = GREEDY,
+             stop_ids=None, ignore_eos: bool = False, sampler=None, stats: GenerationStats | None = None,
+             clock=time.perf_counter) -> list[GenerationResult]:
+    """Generate for every prompt (a list of token ids each).
+
+    stop_ids    tokens that end a sequence; default: the model's own (``eos_token_id``)
+    ignore_eos  never stop on a token (benchmarks)
+    sampler     ``(logits, sequence_indices, step, windows) -> list of ids``; default: the device sampler
+    """
+    prompts = [list(p) for p in prompts]
+    for i, p in enumerate(prompts):
+        if not p:
+            raise ValueError(f"request {i}: the prompt is empty")
+        if len(p) > engine.cache.max_seq_len:
+            raise ValueError(f"request {i}: the prompt has {len(p)} tokens; the longest sequence allowed is "
+                             f"{engine.cache.max_seq_len}")
+    if stop_ids is None:
+        stop_ids = tuple(getattr(engine.plan, "stop_token_ids", ()))
+    stops = frozenset() if ignore_eos else frozenset(stop_ids)
+    if sampler is None:
+        sampler = DeviceSampler(sampling, engine.device)
+    stats = stats if stats is not None else GenerationStats()
+    results = [GenerationResult(prompt_tokens=len(p)) for p in prompts]
+    max_seq_len = engine.cache.max_seq_len
+
+    for batch in plan_batches([len(p) for p in prompts], max_new_tokens, engine.max_batch,
+                              engine.cache.max_tokens, max_seq_len):
+        stats.batches += 1
+        slots = engine.open_sequences(len(batch))
+        slot_of = dict(zip(batch, slots))
+        windows = {i: PenaltyWindow(sampling, prompts[i]) for i in batch}
+        length = {i: len(prompts[i]) for i in batch}
+        active = list(batch)
+        try:
+            t0 = clock()
+            if max_new_tokens > 0:
+                logits = engine.step([StepEntry(slot_of[i], prompts[i], [len(prompts[i]) - 1]) for i in active])
+            else:
+                engine.step([StepEntry(slot_of[i], prompts[i], []) for i in active])
+                logits = None
+            step = 0
+            first = True
+            while active and logits is not None:
+                ids = sampler(logits, active, step, [windows[i] for i in active])
+                now = clock()
+                if first:
+                    stats.prefill_seconds += now - t0
+                    stats.prompt_tokens += sum(len(prompts[i]) for i in active)
+                    first = False
+                else:
+                    stats.decode_seconds += now - t0
+                t0 = now
+                going, done = [], []
+                for i, tok in zip(active, ids):
+                    tok = int(tok)
+                    if tok in stops:                         # not emitted, not counted
+                        results[i].finish_reason = FINISH_STOP
+                        done.append(i)
+                        continue
+                    results[i].tokens.append(tok)
+                    windows[i].accept(tok)
+                    stats.generated_tokens += 1
+                    if len(results[i].tokens) >= max_new_tokens:
+                        results[i].finish_reason = FINISH_LENGTH
+                        done.append(i)
+                    elif length[i] + 1 > max_seq_len:        # no room to run this token
+                        results[i].finish_reason = FINISH_CONTEXT
+                        done.append(i)
+                    else:
+                        going.append(i)
+                if done:
+                    engine.close_sequences([slot_of.pop(i) for i in done])
+                active = going
+                if not active:
+                    break
+                logits = engine.step([StepEntry(slot_of[i], [results[i].tokens[-1]], [0]) for i in active])
+                for i in active:
+                    length[i] += 1
+                step += 1
+                stats.steps += 1
+        finally:
+            if slot_of:
+                engine.close_sequences(list(slot_of.values()))
+        for i in batch:
+            if not results[i].finish_reason:
+                results[i].finish_reason = FINISH_LENGTH
+    return results

@@ -1,0 +1,264 @@
+"""Python entry points of the hand-written kernels.
+
+Each function checks its tensors (device, dtype, layout), calls the C launcher
+on the current CUDA stream and raises ``KernelError`` with the launcher's
+message if it refuses the sizes.  Tensors must live on a CUDA device: there is
+no CPU path.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from .build import load_module
+
+DT_F32, DT_BF16 = 0, 1
+PAGE_SIZE = 64          # tokens per cache page
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _dt(t: torch.dtype) -> int:
+    if t == torch.float32:
+        return DT_F32
+    if t == torch.bfloat16:
+        return DT_BF16
+    raise KernelError(f"kernels take float32 or bfloat16, got {t}")
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, ndim=None):
+    if not t.is_cuda:
+        raise KernelError(f"{name}: must be a CUDA tensor (this library has no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name}: must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name}: must be {dtype}, got {t.dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise KernelError(f"{name}: must have {ndim} dimensions, got {t.dim()}")
+
+
+def _call(module: str, fn: str, *args):
+    lib = load_module(module)
+    rc = getattr(lib, fn)(*args)
+    if rc != 0:
+        raise KernelError(lib.qwb_last_error().decode("utf-8", "replace") or f"{fn} failed with code {rc}")
+
+
+_i = ctypes.c_int
+_f = ctypes.c_float
+
+
+# ----------------------------------------------------------------------------- elementwise
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, bad_token: torch.Tensor | None = None) -> torch.Tensor:
+    """Rows of ``table`` [V, D] for int32 ``ids`` [T], as float32 [T, D]."""
+    _need(ids, "ids", torch.int32, 1)
+    _need(table, "table", ndim=2)
+    T, (V, D) = ids.numel(), table.shape
+    out = torch.empty((T, D), dtype=torch.float32, device=table.device)
+    _call("elementwise", "qwb_embed_gather", _ptr(ids), _ptr(table), _i(_dt(table.dtype)), _ptr(out),
+          _i(T), _i(D), _i(V), _ptr(bad_token), _stream())
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+            delta: torch.Tensor | None = None, write_sum: bool = False,
+            rows: torch.Tensor | None = None) -> torch.Tensor:
+    """RMS norm of the rows of float32 ``x`` [T, D] (plus ``delta``), times ``weight``.
+
+    With ``write_sum`` the sum x + delta replaces x.  With ``rows`` (int32) only
+    those rows are normed and the output has one row per entry.
+    """
+    _need(x, "x", torch.float32, 2)
+    _need(weight, "weight", torch.float32, 1)
+    T, D = x.shape
+    if weight.numel() != D:
+        raise KernelError(f"rmsnorm: weight has {weight.numel()} entries for rows of {D}")
+    if delta is not None:
+        _need(delta, "delta", torch.float32, 2)
+        if delta.shape != x.shape:
+            raise KernelError(f"rmsnorm: delta {tuple(delta.shape)} does not match x {tuple(x.shape)}")
+    n_rows = T
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+        n_rows = rows.numel()
+    out = torch.empty((n_rows, D), dtype=out_dtype, device=x.device)
+    _call("elementwise", "qwb_rmsnorm", _ptr(x), _ptr(delta), _ptr(x if (write_sum and delta is not None) else None),
+          _ptr(weight), _ptr(out), _i(_dt(out_dtype)), _ptr(rows), _i(n_rows), _i(D), _f(eps), _stream())
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """silu(gate) * up from a float32 [T, 2F] matrix (gate columns first)."""
+    _need(gate_up, "gate_up", torch.float32, 2)
+    T, F2 = gate_up.shape
+    if F2 % 2:
+        raise KernelError(f"silu_mul: {F2} columns cannot be split into gate and up")
+    out = torch.empty((T, F2 // 2), dtype=out_dtype, device=gate_up.device)
+    _call("elementwise", "qwb_silu_mul", _ptr(gate_up), _ptr(out), _i(_dt(out_dtype)), _i(T), _i(F2 // 2), _stream())
+    return out
+
+
+def add_inplace(out: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    _need(out, "out", torch.float32)
+    _need(delta, "delta", torch.float32)
+    if out.shape != delta.shape:
+        raise KernelError(f"add_inplace: shapes {tuple(out.shape)} and {tuple(delta.shape)} differ")
+    _call("elementwise", "qwb_add_inplace", _ptr(out), _ptr(delta), ctypes.c_longlong(out.numel()), _stream())
+    return out
+
+
+# ----------------------------------------------------------------------------- rope + cache write
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """cos and sin of positions[t] * inv_freq[i] as float32 [T, half]; the angles are formed in float64."""
+    _need(positions, "positions", torch.int32, 1)
+    _need(inv_freq, "inv_freq", torch.float64, 1)
+    T, half = positions.numel(), inv_freq.numel()
+    cos = torch.empty((T, half), dtype=torch.float32, device=positions.device)
+    sin = torch.empty_like(cos)
+    _call("rope_kv", "qwb_rope_table", _ptr(positions), _ptr(inv_freq), _ptr(cos), _ptr(sin), _i(T), _i(half), _stream())
+    return cos, sin
+
+
+def qk_norm_rope_store(qkv: torch.Tensor, q_weight, k_weight, cos, sin, tok_seq, tok_pos, page_table,
+                       k_pool, v_pool, n_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int,
+                       eps: float, store_kv: bool = True) -> torch.Tensor:
+    """Per-head norm, rotation and cache write.  ``qkv`` float32 [T, (Hq + 2 Hkv) * hd];
+    returns the rotated queries [T, Hq, hd] in the cache's dtype."""
+    _need(qkv, "qkv", torch.float32, 2)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (n_heads + 2 * n_kv_heads) * head_dim:
+        raise KernelError(f"qk_norm_rope_store: qkv has {qkv.shape[1]} columns, expected "
+                          f"{(n_heads + 2 * n_kv_heads) * head_dim}")
+    _need(k_pool, "k_pool", ndim=4)
+    _need(v_pool, "v_pool", k_pool.dtype, 4)
+    if tuple(k_pool.shape[1:]) != (n_kv_heads, k_pool.shape[2], head_dim) or v_pool.shape != k_pool.shape:
+        raise KernelError(f"qk_norm_rope_store: cache pool {tuple(k_pool.shape)} does not fit "
+                          f"{n_kv_heads} heads of {head_dim}")
+    for name, t in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if t is not None:
+            _need(t, name, torch.float32, 1)
+            if t.numel() != head_dim:
+                raise KernelError(f"qk_norm_rope_store: {name} has {t.numel()} entries for heads of {head_dim}")
+    if rotary_dim:
+        _need(cos, "cos", torch.float32, 2)
+        _need(sin, "sin", torch.float32, 2)
+        if tuple(cos.shape) != (T, rotary_dim // 2) or sin.shape != cos.shape:
+            raise KernelError(f"qk_norm_rope_store: cos/sin {tuple(cos.shape)} do not fit {T} tokens and "
+                              f"rotary size {rotary_dim}")
+    _need(tok_seq, "tok_seq", torch.int32, 1)
+    _need(tok_pos, "tok_pos", torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2)
+    q_out = torch.empty((T, n_heads, head_dim), dtype=k_pool.dtype, device=qkv.device)
+    _call("rope_kv", "qwb_qk_norm_rope_store", _ptr(qkv), _ptr(q_weight), _ptr(k_weight), _ptr(cos), _ptr(sin),
+          _ptr(tok_seq), _ptr(tok_pos), _ptr(page_table), _ptr(q_out), _ptr(k_pool), _ptr(v_pool),
+          _i(_dt(k_pool.dtype)), _i(T), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(rotary_dim), _f(eps),
+          _i(k_pool.shape[2]), _i(page_table.shape[1]), _i(1 if store_kv else 0), _stream())
+    return q_out
+
+
+# ----------------------------------------------------------------------------- attention
+def attn_prefill(q, k_pool, v_pool, page_table, cu_seqlens, pos0, max_new: int, scale: float,
+                 window: int = 0) -> torch.Tensor:
+    """Causal attention of new tokens over the cache.  q [T, Hq, hd]; returns [T, Hq * hd]."""
+    _need(q, "q", k_pool.dtype, 3)
+    _need(k_pool, "k_pool", ndim=4)
+    _need(v_pool, "v_pool", k_pool.dtype, 4)
+    _need(page_table, "page_table", torch.int32, 2)
+    _need(cu_seqlens, "cu_seqlens", torch.int32, 1)
+    _need(pos0, "pos0", torch.int32, 1)
+    T, Hq, hd = q.shape
+    B = pos0.numel()
+    if cu_seqlens.numel() != B + 1 or page_table.shape[0] < B:
+        raise KernelError("attn_prefill: cu_seqlens / page_table do not fit the batch")
+    out = torch.empty((T, Hq * hd), dtype=q.dtype, device=q.device)
+    _call("attention", "qwb_attn_prefill", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _ptr(cu_seqlens),
+          _ptr(pos0), _ptr(out), _i(_dt(q.dtype)), _i(B), _i(max_new), _i(Hq), _i(k_pool.shape[1]), _i(hd),
+          _i(k_pool.shape[2]), _i(page_table.shape[1]), _f(scale), _i(window), _stream())
+    return out
+
+
+def attn_decode_scratch_floats(B: int, Hq: int, hd: int, max_runs: int) -> int:
+    return B * Hq * max_runs * (hd + 2)
+
+
+def attn_decode(q, k_pool, v_pool, page_table, seq_len, scale: float, max_len: int, window: int = 0,
+                split_tokens: int = 256, scratch: torch.Tensor | None = None) -> torch.Tensor:
+    """Attention of one new token per sequence over the cache.  q [B, Hq, hd]; ``seq_len`` counts
+    the new token; ``max_len`` bounds every entry of ``seq_len``.  Returns [B, Hq * hd]."""
+    _need(q, "q", k_pool.dtype, 3)
+    _need(k_pool, "k_pool", ndim=4)
+    _need(v_pool, "v_pool", k_pool.dtype, 4)
+    _need(page_table, "page_table", torch.int32, 2)
+    _need(seq_len, "seq_len", torch.int32, 1)
+    B, Hq, hd = q.shape
+    max_runs = max(1, math.ceil(max_len / split_tokens))
+    need = attn_decode_scratch_floats(B, Hq, hd, max_runs) if max_runs > 1 else 0
+    if need and (scratch is None or scratch.numel() < need):
+        scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+    if scratch is not None:
+        _need(scratch, "scratch", torch.float32)
+    out = torch.empty((B, Hq * hd), dtype=q.dtype, device=q.device)
+    _call("attention", "qwb_attn_decode", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _ptr(seq_len),
+          _ptr(scratch), _ptr(out), _i(_dt(q.dtype)), _i(B), _i(Hq), _i(k_pool.shape[1]), _i(hd),
+          _i(k_pool.shape[2]), _i(page_table.shape[1]), _f(scale), _i(window), _i(split_tokens), _i(max_runs),
+          _stream())
+    return out
+
+
+# ----------------------------------------------------------------------------- matrix products
+SMALL_M = 16            # at most this many rows go to the weight-streaming kernel
+
+
+def gemm_small(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor | None = None,
+               out: torch.Tensor | None = None) -> torch.Tensor:
+    """x [M, K] times weight [N, K] transposed, as float32 [M, N] (+ residual), for few rows."""
+    _need(x, "x", weight.dtype, 2)
+    _need(weight, "weight", ndim=2)
+    M, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K:
+        raise KernelError(f"gemm_small: x has {K} columns, the weight {weight.shape[1]}")
+    if out is None:
+        out = residual if residual is not None else torch.empty((M, N), dtype=torch.float32, device=x.device)
+    _need(out, "out", torch.float32, 2)
+    if residual is not None:
+        _need(residual, "residual", torch.float32, 2)
+    _call("gemm_small", "qwb_gemm_small", _ptr(x), _ptr(weight), _ptr(residual), _ptr(out), _i(_dt(x.dtype)),
+          _i(M), _i(N), _i(K), _stream())
+    return out
+
+
+# ----------------------------------------------------------------------------- sampling
+def sample(logits: torch.Tensor, temperature: float, top_k: int = 0, top_p: float = 1.0, seed: int = 0,
+           sequence_index: torch.Tensor | None = None, step: int = 0, recent: torch.Tensor | None = None,
+           repeat_penalty: float = 1.0, presence_penalty: float = 0.0, frequency_penalty: float = 0.0,
+           out_u: torch.Tensor | None = None) -> torch.Tensor:
+    """One token id per row of float32 ``logits`` [B, V] (changed in place by penalties)."""
+    _need(logits, "logits", torch.float32, 2)
+    B, V = logits.shape
+    window = 0
+    if recent is not None:
+        _need(recent, "recent", torch.int32, 2)
+        window = recent.shape[1]
+    if sequence_index is not None:
+        _need(sequence_index, "sequence_index", torch.int32, 1)
+    if out_u is not None:
+        _need(out_u, "out_u", torch.float64, 1)
+    out = torch.empty((B,), dtype=torch.int32, device=logits.device)
+    _call("sampling", "qwb_sample", _ptr(logits), _i(B), _i(V), _ptr(recent), _i(window), _f(repeat_penalty),
+          _f(presence_penalty), _f(frequency_penalty), _f(temperature), _i(top_k), _f(top_p),
+          ctypes.c_ulonglong(seed & (2 ** 64 - 1)), _ptr(sequence_index), ctypes.c_uint(step & 0xFFFFFFFF),
+          _ptr(out), _ptr(out_u), _stream())
+    return out

@@ -1,0 +1,90 @@
+"""Grouped-query attention over the paged cache, with optional per-head q/k norm, a position
+encoding applied to q and k, and an optional window.  The reference's order (core/runtime.cpp:
+1039-1058, 681-734): project, split heads, norm q and k (same eps), rotate, store k and v, attend
+with scale 1/sqrt(head size), project back."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..kernels import ops
+from ..weights.manifest import MATRIX, NORM_WEIGHT, VECTOR, TensorSpec
+from .base import KVSpec, Mixer
+from .linear import linear
+from .registry import register_mixer
+
+DECODE_SPLIT_TOKENS = 256     # keys per run of the decode kernel; fixed, so results do not depend on the batch
+
+
+class GroupedQueryAttention(Mixer):
+    """params: hidden_size, n_heads, n_kv_heads, head_dim, qk_norm (bool), norm_eps, window (0: none),
+    scale (default 1/sqrt(head_dim)), names (optional overrides of the tensor names)."""
+
+    NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+             "q_norm": "q_norm.weight", "k_norm": "k_norm.weight"}
+
+    def __init__(self, spec, runtime, position=None):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.n_heads = int(p["n_heads"])
+        self.n_kv_heads = int(p["n_kv_heads"])
+        self.head_dim = int(p["head_dim"])
+        self.qk_norm = bool(p.get("qk_norm", False))
+        self.eps = float(p.get("norm_eps", 0.0))
+        self.window = int(p.get("window", 0) or 0)
+        self.scale = float(p.get("scale", 1.0 / math.sqrt(self.head_dim)))
+        self.names = {**self.NAMES, **dict(p.get("names", {}))}
+        self.position = position
+        self.rotary_dim = getattr(position, "rotary_dim", 0) if position is not None else 0
+        if self.n_heads % self.n_kv_heads:
+            raise ValueError(f"{self.n_heads} heads are not a multiple of {self.n_kv_heads} key/value heads")
+        if self.rotary_dim > self.head_dim:
+            raise ValueError(f"rotary size {self.rotary_dim} exceeds the head size {self.head_dim}")
+        self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
+
+    def tensors(self):
+        q, kv, hd, D = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim, self.head_dim, self.hidden
+        n = self.names
+        out = [TensorSpec(self.prefix + n["q"], (q, D), MATRIX), TensorSpec(self.prefix + n["k"], (kv, D), MATRIX),
+               TensorSpec(self.prefix + n["v"], (kv, D), MATRIX), TensorSpec(self.prefix + n["o"], (D, q), MATRIX)]
+        if self.qk_norm:
+            out += [TensorSpec(self.prefix + n["q_norm"], (hd,), VECTOR, NORM_WEIGHT),
+                    TensorSpec(self.prefix + n["k_norm"], (hd,), VECTOR, NORM_WEIGHT)]
+        return out
+
+    def bind(self, weights):
+        n, px = self.names, self.prefix
+        # one fused projection: rows of q, then k, then v (a row concat, no change to the math)
+        self.w_qkv = torch.cat([weights[px + n["q"]], weights[px + n["k"]], weights[px + n["v"]]], dim=0).contiguous()
+        self.w_o = weights[px + n["o"]]
+        if self.qk_norm:
+            self.q_norm_w = weights[px + n["q_norm"]].to(torch.float32).contiguous()
+            self.k_norm_w = weights[px + n["k_norm"]].to(torch.float32).contiguous()
+
+    def kernel_modules(self):
+        return ("rope_kv", "attention", "gemm_small")
+
+    def kv_spec(self):
+        return KVSpec(self.n_kv_heads, self.head_dim, self.window)
+
+    def forward(self, x, ctx, cache):
+        qkv = linear(x, self.w_qkv)
+        cos = sin = None
+        if self.position is not None:
+            cos, sin = self.position.prepare(ctx)
+        table = ctx.page_tables[cache.group_id]
+        q = ops.qk_norm_rope_store(qkv, self.q_norm_w, self.k_norm_w, cos, sin, ctx.tok_seq, ctx.tok_pos, table,
+                                   cache.k_pool, cache.v_pool, self.n_heads, self.n_kv_heads, self.head_dim,
+                                   self.rotary_dim, self.eps, store_kv=cache.writable)
+        if ctx.single_token:
+            att = ops.attn_decode(q, cache.k_pool, cache.v_pool, table, ctx.seq_len, self.scale, ctx.max_len,
+                                  window=self.window, split_tokens=DECODE_SPLIT_TOKENS)
+        else:
+            att = ops.attn_prefill(q, cache.k_pool, cache.v_pool, table, ctx.cu_seqlens, ctx.pos0, ctx.max_new,
+                                   self.scale, window=self.window)
+        return linear(att, self.w_o)
+
+
+register_mixer("gqa", GroupedQueryAttention)

@@ -1,0 +1,47 @@
+"""Pre-norm residual block: h += mixer(norm1(h)); h += feed_forward(norm2(h))
+(the reference: core/runtime.cpp:1015-1081; for this arrangement the second norm reads the
+same tensor that the second residual sum starts from, :1066-1067).  The sums are folded into
+the norms: each norm takes (h, delta), writes h + delta back and norms it."""
+from __future__ import annotations
+
+from dataclasses import replace
+
+from .base import Block
+from .registry import build_part, register_block
+
+
+class PreNormBlock(Block):
+    """params: mixer_norm, ffn_norm (tensor-name stems of the two norms), mixer_prefix, ffn_prefix."""
+
+    def __init__(self, spec, runtime, layer=None, position=None):
+        super().__init__(spec, runtime)
+        p = spec.params
+        px = spec.prefix
+        self.norm1 = build_part("norm", replace(layer.norm, prefix=px + p.get("mixer_norm", "input_layernorm") + "."), runtime)
+        self.norm2 = build_part("norm", replace(layer.norm, prefix=px + p.get("ffn_norm", "post_attention_layernorm") + "."), runtime)
+        self.mixer = build_part("mixer", replace(layer.mixer, prefix=px + p.get("mixer_prefix", "self_attn") + "."),
+                                runtime, position=position)
+        self.ffn = build_part("feed_forward", replace(layer.feed_forward, prefix=px + p.get("ffn_prefix", "mlp") + "."), runtime)
+
+    def parts(self):
+        return [self.norm1, self.mixer, self.norm2, self.ffn]
+
+    def tensors(self):
+        return [t for part in self.parts() for t in part.tensors()]
+
+    def bind(self, weights):
+        for part in self.parts():
+            part.bind(weights)
+
+    def kernel_modules(self):
+        return tuple(m for part in self.parts() for m in part.kernel_modules())
+
+    def forward(self, h, delta, ctx, cache):
+        x = self.norm1.forward(h, delta, write_sum=True)
+        delta = self.mixer.forward(x, ctx, cache)
+        x = self.norm2.forward(h, delta, write_sum=True)
+        delta = self.ffn.forward(x, ctx)
+        return h, delta
+
+
+register_block("pre_norm", PreNormBlock)

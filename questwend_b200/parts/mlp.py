@@ -1,0 +1,45 @@
+"""Dense gated feed-forward: down( silu(gate(x)) * up(x) ) (the reference: core/runtime.cpp:1074-1076)."""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..weights.manifest import MATRIX, TensorSpec
+from .base import FeedForward
+from .linear import linear
+from .registry import register_feed_forward
+
+
+class GatedMLP(FeedForward):
+    """params: hidden_size, intermediate_size, names (optional overrides)."""
+
+    NAMES = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.hidden = int(spec.params["hidden_size"])
+        self.inter = int(spec.params["intermediate_size"])
+        self.names = {**self.NAMES, **dict(spec.params.get("names", {}))}
+        self.w_gate_up = self.w_down = None
+
+    def tensors(self):
+        n, px = self.names, self.prefix
+        return [TensorSpec(px + n["gate"], (self.inter, self.hidden), MATRIX),
+                TensorSpec(px + n["up"], (self.inter, self.hidden), MATRIX),
+                TensorSpec(px + n["down"], (self.hidden, self.inter), MATRIX)]
+
+    def bind(self, weights):
+        n, px = self.names, self.prefix
+        self.w_gate_up = torch.cat([weights[px + n["gate"]], weights[px + n["up"]]], dim=0).contiguous()
+        self.w_down = weights[px + n["down"]]
+
+    def kernel_modules(self):
+        return ("elementwise", "gemm_small")
+
+    def forward(self, x, ctx):
+        gate_up = linear(x, self.w_gate_up)
+        act = ops.silu_mul(gate_up, self.runtime.dtype)
+        return linear(act, self.w_down)
+
+
+register_feed_forward("gated_mlp", GatedMLP)

@@ -136,3 +136,32 @@ extern "C" int qwb_add_inplace(float* out, const float* delta, long long n, cuda
     add_inplace_kernel<<<grid, block, 0, stream>>>(out, delta, (size_t)n);
     return qwb_check_launch("add_inplace");
 }
+
+// After a decode step that sampled on the device: the sampled token becomes the next
+// step's input, every sequence is one token longer, the step counter goes up, and the
+// token enters the sequence's penalty window (a ring of `window` ids).
+__global__ void decode_advance_kernel(const int* __restrict__ sampled, int* token_ids, int* tok_pos, int* pos0,
+                                      int* seq_len, unsigned int* step_counter, int* recent, int* n_seen,
+                                      int window, int B) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b == 0 && step_counter) *step_counter += 1;
+    if (b >= B) return;
+    const int tok = sampled[b];
+    token_ids[b] = tok;
+    tok_pos[b] += 1;
+    pos0[b] += 1;
+    seq_len[b] += 1;
+    if (recent && window > 0) {
+        recent[(size_t)b * window + (n_seen[b] % window)] = tok;
+        n_seen[b] += 1;
+    }
+}
+
+extern "C" int qwb_decode_advance(const int* sampled, int* token_ids, int* tok_pos, int* pos0, int* seq_len,
+                                  unsigned int* step_counter, int* recent, int* n_seen, int window, int B,
+                                  cudaStream_t stream) {
+    if (B <= 0) return 0;
+    decode_advance_kernel<<<(B + 127) / 128, 128, 0, stream>>>(sampled, token_ids, tok_pos, pos0, seq_len,
+                                                               step_counter, recent, n_seen, window, B);
+    return qwb_check_launch("decode_advance");
+}

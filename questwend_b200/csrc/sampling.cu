@@ -125,13 +125,14 @@ __device__ Cut radix_cut(const float* row, int V, const Cut within, bool by_mass
 }
 
 // logits [B, V] float (changed in place when penalties apply); recent [B, window] token ids
-// seen lately, -1 where empty; sequence_index [B] and step key the random stream;
-// out_ids [B]; out_u [B] optional: the uniform numbers that were used.
+// seen lately, -1 where empty; sequence_index [B] and step (+ *step_add, if given: a counter on
+// the device, for steps replayed from a CUDA graph) key the random stream; out_ids [B];
+// out_u [B] optional: the uniform numbers that were used.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, float repeat_penalty,
               float presence_penalty, float frequency_penalty, float temperature, int top_k, float top_p,
               unsigned long long seed, const int* __restrict__ sequence_index, unsigned int step,
-              int* __restrict__ out_ids, double* out_u) {
+              const unsigned int* __restrict__ step_add, int* __restrict__ out_ids, double* out_u) {
     __shared__ double hist[256];
     __shared__ int hist_n[256];
     __shared__ double sh_above;
@@ -241,7 +242,8 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
     }
     __syncthreads();
     const double total = sh_above;
-    const double u = philox_uniform(seed, (unsigned int)(sequence_index ? sequence_index[b] : b), step);
+    const double u = philox_uniform(seed, (unsigned int)(sequence_index ? sequence_index[b] : b),
+                                    step + (step_add ? *step_add : 0u));
     const double r = u * total;
     const double before = warp_base[warp] + incl - mine;
     if (mine > 0.0 && r > before && r <= before + mine) {
@@ -266,14 +268,14 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
 
 extern "C" int qwb_sample(float* logits, int B, int V, const int* recent, int window, float repeat_penalty,
                           float presence_penalty, float frequency_penalty, float temperature, int top_k, float top_p,
-                          unsigned long long seed, const int* sequence_index, unsigned int step, int* out_ids,
-                          double* out_u, cudaStream_t stream) {
+                          unsigned long long seed, const int* sequence_index, unsigned int step,
+                          const unsigned int* step_add, int* out_ids, double* out_u, cudaStream_t stream) {
     if (B <= 0) return 0;
     if (V <= 0) return qwb_fail(QWB_ERR_ARG, "sample: bad vocabulary size %d", V);
     if (temperature > 0.f && !(top_p > 0.f)) return qwb_fail(QWB_ERR_ARG, "sample: top_p must be > 0, got %g", (double)top_p);
     if (repeat_penalty <= 0.f) return qwb_fail(QWB_ERR_ARG, "sample: repeat_penalty must be > 0, got %g", (double)repeat_penalty);
     sample_kernel<<<B, SAMPLE_THREADS, 0, stream>>>(logits, V, recent, window, repeat_penalty, presence_penalty,
                                                    frequency_penalty, temperature, top_k, top_p, seed, sequence_index,
-                                                   step, out_ids, out_u);
+                                                   step, step_add, out_ids, out_u);
     return qwb_check_launch("sample");
 }

@@ -1,0 +1,153 @@
+"""Decode steps from a CUDA graph.
+
+After the prompts have run, every step is the same work on one more token per
+sequence.  ``DecodeRunner`` keeps that step's inputs in fixed device buffers
+(token ids, positions, lengths, page tables, the sampler's state), captures
+"model step -> sample -> advance" once per batch size and attention-grid bucket,
+and replays it.  The step inside the graph is the same ``Model.forward`` that
+``Engine.step`` runs; only its inputs come from the fixed buffers.  The host keeps
+the cache's bookkeeping (it knows every length without asking the device) and
+refreshes the page tables when a sequence needs a new page.
+
+The reference does the same for its single sequence: a persistent graph whose
+write position and mask are inputs, rebuilt only when the key count crosses a
+bucket of 32 (core/runtime.cpp:1768-1829), replayed as a CUDA graph inside ggml.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+from ..parts.attention import DECODE_SPLIT_TOKENS
+from ..parts.base import StepContext
+from ..sampling.params import SamplingParams
+
+
+class DecodeRunner:
+    """Fixed buffers and graphs for decode steps of ``batch`` sequences with one sampling setup."""
+
+    def __init__(self, engine, batch: int, sampling: SamplingParams, seed: int, use_graph: bool = True):
+        self.engine = engine
+        self.B = B = batch
+        self.sampling = sampling
+        self.seed = seed
+        self.use_graph = use_graph
+        dev = engine.device
+        cache = engine.cache
+        # int32 state: token_ids, tok_pos, pos0, seq_len, sequence_index, n_seen | constants: tok_seq, cu_seqlens, rows
+        self.state = torch.zeros((6, B), dtype=torch.int32, device=dev)
+        self.token_ids, self.tok_pos, self.pos0, self.seq_len, self.seq_index, self.n_seen = self.state.unbind(0)
+        self.tok_seq = torch.arange(B, dtype=torch.int32, device=dev)
+        self.cu_seqlens = torch.arange(B + 1, dtype=torch.int32, device=dev)
+        self.rows = torch.arange(B, dtype=torch.int32, device=dev)
+        self.step_counter = torch.zeros((1,), dtype=torch.int32, device=dev)
+        self.sampled = torch.zeros((B,), dtype=torch.int32, device=dev)
+        self.window = sampling.repeat_last_n if sampling.penalized else 0
+        self.recent = (torch.full((B, self.window), -1, dtype=torch.int32, device=dev) if self.window else None)
+        self.tables = {g: torch.zeros((B, cache.table_width), dtype=torch.int32, device=dev)
+                       for g in range(cache.n_groups())}
+        self.state_host = torch.zeros((6, B), dtype=torch.int32).pin_memory()
+        self.tokens_host = torch.zeros((B,), dtype=torch.int32).pin_memory()
+        self.sampled_host = torch.zeros((B,), dtype=torch.int32).pin_memory()
+        self.graphs: dict = {}
+        self.slots: list = []
+        self._pages_seen: list = []
+        self.launches_per_step = 0
+
+    # ------------------------------------------------------------------ binding a batch
+    def bind(self, slots, tokens, sequence_indices, step: int, windows=None) -> None:
+        """Point the buffers at these sequences: ``tokens`` are the next inputs (one each)."""
+        assert len(slots) == self.B
+        cache = self.engine.cache
+        self.slots = list(slots)
+        lens = [cache.length(s) for s in slots]
+        h = self.state_host
+        h[0] = torch.tensor(tokens, dtype=torch.int32)
+        h[1] = torch.tensor(lens, dtype=torch.int32)
+        h[2] = h[1]
+        h[3] = h[1] + 1
+        h[4] = torch.tensor(sequence_indices, dtype=torch.int32)
+        if self.window:
+            rows = [w.row() for w in windows]
+            h[5] = torch.tensor([sum(1 for t in r if t >= 0) for r in rows], dtype=torch.int32)
+            self.recent.copy_(torch.tensor(rows, dtype=torch.int32))
+        else:
+            h[5] = 0
+        self.state.copy_(h, non_blocking=True)
+        self.step_counter.fill_(step)
+        self._pages_seen = [None] * cache.n_groups()
+        torch.cuda.current_stream().synchronize()      # the pinned buffer may be written again
+
+    def set_tokens(self, tokens) -> None:
+        """This step's input tokens from the host (pinned memory, one copy)."""
+        self.tokens_host.copy_(torch.as_tensor(tokens, dtype=torch.int32))
+        self.token_ids.copy_(self.tokens_host, non_blocking=True)
+
+    # ------------------------------------------------------------------ one step
+    def _context(self, max_len_bucket: int) -> StepContext:
+        return StepContext(n_tokens=self.B, n_seqs=self.B, token_ids=self.token_ids, tok_seq=self.tok_seq,
+                           tok_pos=self.tok_pos, cu_seqlens=self.cu_seqlens, pos0=self.pos0, seq_len=self.seq_len,
+                           slots=self.tok_seq, max_new=1, max_len=max_len_bucket, single_token=True,
+                           page_tables=self.tables, host_slots=self.slots)
+
+    def _forward_and_sample(self, max_len_bucket: int) -> None:
+        eng, p = self.engine, self.sampling
+        logits = eng.model.forward(self._context(max_len_bucket), eng.unit_caches, self.rows)
+        ops.sample(logits, p.temperature, top_k=p.top_k, top_p=p.top_p, seed=self.seed,
+                   sequence_index=self.seq_index, step=0, step_add=self.step_counter, recent=self.recent,
+                   repeat_penalty=p.repeat_penalty, presence_penalty=p.presence_penalty,
+                   frequency_penalty=p.frequency_penalty, out=self.sampled)
+
+    def _advance(self) -> None:
+        ops.decode_advance(self.sampled, self.token_ids, self.tok_pos, self.pos0, self.seq_len,
+                           step_counter=self.step_counter, recent=self.recent,
+                           n_seen=self.n_seen if self.window else None)
+
+    def _capture(self, bucket: int):
+        # one plain run first: it loads the kernels and sets their attributes; it writes only what
+        # the captured run writes again (this step's keys and values, the sampled ids)
+        self._forward_and_sample(bucket)
+        torch.cuda.current_stream().synchronize()
+        g = torch.cuda.CUDAGraph()
+        before = ops.LAUNCHES[0]
+        with torch.cuda.graph(g):
+            self._forward_and_sample(bucket)
+            self._advance()
+        self.launches_per_step = ops.LAUNCHES[0] - before
+        return g
+
+    def step(self) -> None:
+        """Run one decode step for the bound sequences; the sampled ids land in ``self.sampled``
+        and become the next inputs."""
+        cache = self.engine.cache
+        wants = {s: cache.length(s) + 1 for s in self.slots}
+        cache.reserve(wants)
+        for g in range(cache.n_groups()):
+            counts = [len(cache._groups[g].pages[s]) for s in self.slots]
+            if counts != self._pages_seen[g]:
+                self._pages_seen[g] = counts
+                self.tables[g].copy_(torch.from_numpy(cache.page_table_host(g, self.slots)))
+        bucket = math.ceil(max(wants.values()) / DECODE_SPLIT_TOKENS) * DECODE_SPLIT_TOKENS
+        with torch.cuda.device(self.engine.device):
+            if self.use_graph:
+                g = self.graphs.get(bucket)
+                if g is None:
+                    g = self.graphs[bucket] = self._capture(bucket)
+                g.replay()
+            else:
+                before = ops.LAUNCHES[0]
+                self._forward_and_sample(bucket)
+                self._advance()
+                self.launches_per_step = ops.LAUNCHES[0] - before
+        for s in self.slots:
+            cache.advance(s, 1)
+        self.engine.steps_run += 1
+
+    def read_sampled(self) -> list:
+        """The ids sampled by the last step, on the host (one copy, waits for the step)."""
+        self.sampled_host.copy_(self.sampled, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self.sampled_host.tolist()

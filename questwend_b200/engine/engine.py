@@ -90,6 +90,7 @@ class Engine:
         self.cache = CacheManager(self.model.cache_units(), max_tokens, max_batch, max_seq_len, dtype, device)
         self.unit_caches = [self.cache.unit_cache(i) for i in range(len(self.model.schedule))]
         self.steps_run = 0
+        self._runners: dict = {}
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -187,6 +188,17 @@ class Engine:
             self.cache.advance(e.slot, len(e.tokens))
         self.steps_run += 1
         return logits
+
+    def decode_runner(self, batch: int, sampling, seed: int, use_graph: bool = True):
+        """The fixed buffers and CUDA graphs for decode steps of ``batch`` sequences (made once, kept)."""
+        from .decode import DecodeRunner
+        key = (batch, sampling, seed, use_graph)
+        runner = self._runners.get(key)
+        if runner is None:
+            if len(self._runners) >= 16:             # graphs hold memory: drop the oldest
+                self._runners.pop(next(iter(self._runners)))
+            runner = self._runners[key] = DecodeRunner(self, batch, sampling, seed, use_graph)
+        return runner
 
     # ------------------------------------------------------------------ facts
     def describe(self) -> dict:

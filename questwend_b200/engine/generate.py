@@ -71,14 +71,46 @@ def plan_batches(prompt_lengths, max_new_tokens: int, max_batch: int, max_tokens
     return batches
 
 
+class _PlainStepper:
+    """Decode steps through ``engine.step`` and a sampler callable."""
+
+    def __init__(self, engine, sampler, slot_of, windows):
+        self.engine, self.sampler, self.slot_of, self.windows = engine, sampler, slot_of, windows
+
+    def run(self, active, tokens, step):
+        logits = self.engine.step([StepEntry(self.slot_of[i], [t], [0]) for i, t in zip(active, tokens)])
+        return self.sampler(logits, active, step, [self.windows[i] for i in active])
+
+
+class _GraphStepper:
+    """Decode steps replayed from CUDA graphs (``DecodeRunner``); rebinds when the batch changes."""
+
+    def __init__(self, engine, sampling, seed, slot_of, windows):
+        self.engine, self.sampling, self.seed = engine, sampling, seed
+        self.slot_of, self.windows = slot_of, windows
+        self.bound = None
+        self.runner = None
+
+    def run(self, active, tokens, step):
+        if self.bound != active:
+            self.runner = self.engine.decode_runner(len(active), self.sampling, self.seed)
+            self.runner.bind([self.slot_of[i] for i in active], tokens, active, step,
+                             [self.windows[i] for i in active])
+            self.bound = list(active)
+        self.runner.set_tokens(tokens)
+        self.runner.step()
+        return self.runner.read_sampled()
+
+
 def generate(engine, prompts, max_new_tokens: int = 128, sampling: SamplingParams = GREEDY,
              stop_ids=None, ignore_eos: bool = False, sampler=None, stats: GenerationStats | None = None,
-             clock=time.perf_counter) -> list[GenerationResult]:
+             clock=time.perf_counter, use_graph: bool = True) -> list[GenerationResult]:
     """Generate for every prompt (a list of token ids each).
 
     stop_ids    tokens that end a sequence; default: the model's own (``eos_token_id``)
     ignore_eos  never stop on a token (benchmarks)
     sampler     ``(logits, sequence_indices, step, windows) -> list of ids``; default: the device sampler
+    use_graph   replay decode steps from CUDA graphs (needs the default sampler)
     """
     prompts = [list(p) for p in prompts]
     for i, p in enumerate(prompts):
@@ -90,6 +122,7 @@ def generate(engine, prompts, max_new_tokens: int = 128, sampling: SamplingParam
     if stop_ids is None:
         stop_ids = tuple(getattr(engine.plan, "stop_token_ids", ()))
     stops = frozenset() if ignore_eos else frozenset(stop_ids)
+    graph_path = use_graph and sampler is None and hasattr(engine, "decode_runner")
     if sampler is None:
         sampler = DeviceSampler(sampling, engine.device)
     stats = stats if stats is not None else GenerationStats()
@@ -104,25 +137,18 @@ def generate(engine, prompts, max_new_tokens: int = 128, sampling: SamplingParam
         windows = {i: PenaltyWindow(sampling, prompts[i]) for i in batch}
         length = {i: len(prompts[i]) for i in batch}
         active = list(batch)
+        stepper = (_GraphStepper(engine, sampling, sampler.seed, slot_of, windows) if graph_path
+                   else _PlainStepper(engine, sampler, slot_of, windows))
         try:
             t0 = clock()
-            if max_new_tokens > 0:
-                logits = engine.step([StepEntry(slot_of[i], prompts[i], [len(prompts[i]) - 1]) for i in active])
-            else:
-                engine.step([StepEntry(slot_of[i], prompts[i], []) for i in active])
-                logits = None
-            step = 0
-            first = True
-            while active and logits is not None:
-                ids = sampler(logits, active, step, [windows[i] for i in active])
-                now = clock()
-                if first:
-                    stats.prefill_seconds += now - t0
-                    stats.prompt_tokens += sum(len(prompts[i]) for i in active)
-                    first = False
-                else:
-                    stats.decode_seconds += now - t0
-                t0 = now
+            want_last = max_new_tokens > 0
+            logits = engine.step([StepEntry(slot_of[i], prompts[i], [len(prompts[i]) - 1] if want_last else [])
+                                  for i in active])
+            ids = sampler(logits, active, 0, [windows[i] for i in active]) if want_last else []
+            stats.prefill_seconds += clock() - t0
+            stats.prompt_tokens += sum(len(prompts[i]) for i in active)
+            step = 1
+            while want_last and active:
                 going, done = [], []
                 for i, tok in zip(active, ids):
                     tok = int(tok)
@@ -146,7 +172,9 @@ def generate(engine, prompts, max_new_tokens: int = 128, sampling: SamplingParam
                 active = going
                 if not active:
                     break
-                logits = engine.step([StepEntry(slot_of[i], [results[i].tokens[-1]], [0]) for i in active])
+                t0 = clock()
+                ids = stepper.run(active, [results[i].tokens[-1] for i in active], step)
+                stats.decode_seconds += clock() - t0
                 for i in active:
                     length[i] += 1
                 step += 1

@@ -49,9 +49,13 @@ def _need(t: torch.Tensor, name: str, dtype=None, ndim=None):
         raise KernelError(f"{name}: must have {ndim} dimensions, got {t.dim()}")
 
 
-def _call(module: str, fn: str, *args):
+LAUNCHES = [0]          # kernels of this library launched so far (through these entry points)
+
+
+def _call(module: str, fn: str, *args, kernels: int = 1):
     lib = load_module(module)
     rc = getattr(lib, fn)(*args)
+    LAUNCHES[0] += kernels
     if rc != 0:
         raise KernelError(lib.qwb_last_error().decode("utf-8", "replace") or f"{fn} failed with code {rc}")
 
@@ -213,7 +217,7 @@ def attn_decode(q, k_pool, v_pool, page_table, seq_len, scale: float, max_len: i
     _call("attention", "qwb_attn_decode", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _ptr(seq_len),
           _ptr(scratch), _ptr(out), _i(_dt(q.dtype)), _i(B), _i(Hq), _i(k_pool.shape[1]), _i(hd),
           _i(k_pool.shape[2]), _i(page_table.shape[1]), _f(scale), _i(window), _i(split_tokens), _i(max_runs),
-          _stream())
+          _stream(), kernels=2 if max_runs > 1 else 1)
     return out
 
 
@@ -236,7 +240,7 @@ def gemm_small(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor | N
     if residual is not None:
         _need(residual, "residual", torch.float32, 2)
     _call("gemm_small", "qwb_gemm_small", _ptr(x), _ptr(weight), _ptr(residual), _ptr(out), _i(_dt(x.dtype)),
-          _i(M), _i(N), _i(K), _stream())
+          _i(M), _i(N), _i(K), _stream(), kernels=(M + 7) // 8)
     return out
 
 
@@ -244,7 +248,8 @@ def gemm_small(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor | N
 def sample(logits: torch.Tensor, temperature: float, top_k: int = 0, top_p: float = 1.0, seed: int = 0,
            sequence_index: torch.Tensor | None = None, step: int = 0, recent: torch.Tensor | None = None,
            repeat_penalty: float = 1.0, presence_penalty: float = 0.0, frequency_penalty: float = 0.0,
-           out_u: torch.Tensor | None = None) -> torch.Tensor:
+           out_u: torch.Tensor | None = None, step_add: torch.Tensor | None = None,
+           out: torch.Tensor | None = None) -> torch.Tensor:
     """One token id per row of float32 ``logits`` [B, V] (changed in place by penalties)."""
     _need(logits, "logits", torch.float32, 2)
     B, V = logits.shape
@@ -256,9 +261,18 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int = 0, top_p: floa
         _need(sequence_index, "sequence_index", torch.int32, 1)
     if out_u is not None:
         _need(out_u, "out_u", torch.float64, 1)
-    out = torch.empty((B,), dtype=torch.int32, device=logits.device)
+    if out is None:
+        out = torch.empty((B,), dtype=torch.int32, device=logits.device)
     _call("sampling", "qwb_sample", _ptr(logits), _i(B), _i(V), _ptr(recent), _i(window), _f(repeat_penalty),
           _f(presence_penalty), _f(frequency_penalty), _f(temperature), _i(top_k), _f(top_p),
           ctypes.c_ulonglong(seed & (2 ** 64 - 1)), _ptr(sequence_index), ctypes.c_uint(step & 0xFFFFFFFF),
-          _ptr(out), _ptr(out_u), _stream())
+          _ptr(step_add), _ptr(out), _ptr(out_u), _stream())
     return out
+
+
+def decode_advance(sampled, token_ids, tok_pos, pos0, seq_len, step_counter=None, recent=None, n_seen=None) -> None:
+    """The sampled ids become the next inputs; positions and lengths go up by one."""
+    B = sampled.numel()
+    window = recent.shape[1] if recent is not None else 0
+    _call("elementwise", "qwb_decode_advance", _ptr(sampled), _ptr(token_ids), _ptr(tok_pos), _ptr(pos0),
+          _ptr(seq_len), _ptr(step_counter), _ptr(recent), _ptr(n_seen), _i(window), _i(B), _stream())

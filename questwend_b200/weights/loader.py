@@ -81,7 +81,10 @@ def load_tensors(model_dir: str, manifest: list[TensorSpec], compute_dtype: torc
             if spec.name not in infos or spec.ignored:
                 continue
             t = folder.tensor(spec.name)
-            out[spec.name] = t.to(device=device, dtype=held_dtype(spec, t.dtype, compute_dtype)).contiguous()
+            held = t.to(device=device, dtype=held_dtype(spec, t.dtype, compute_dtype)).contiguous()
+            if held.data_ptr() == t.data_ptr():
+                held = held.clone()              # never hand out the file's own (read-only) bytes
+            out[spec.name] = held
         return out
     finally:
         folder.close()

@@ -89,12 +89,8 @@ class SafetensorsFile:
         return flat.view(dt).reshape(shape)
 
     def close(self):
-        if self._mm is not None:
-            try:
-                self._mm.close()
-            except BufferError:
-                pass                             # tensors still reference the map; the GC frees it
-            self._mm = None
+        # Tensors handed out keep the map alive; it is unmapped when the last of them goes.
+        self._mm = None
         self._f.close()
 
 

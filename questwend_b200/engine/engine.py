@@ -57,6 +57,65 @@ def _require_cuda(device: torch.device) -> None:
         raise EngineError(f"the kernels are built for sm_100a (B200); this device is sm_{major}{minor}")
 
 
+def build_step_context(cache: CacheManager, entries: list, vocab_size: int, device) -> tuple[StepContext, torch.Tensor]:
+    """Pack one step's entries for the device: reserves cache pages for the new tokens (or raises and
+    changes nothing), and returns the context and the packed rows whose logits are wanted."""
+    if not entries:
+        raise EngineError("a step needs at least one sequence")
+    slots = [e.slot for e in entries]
+    if len(set(slots)) != len(slots):
+        raise EngineError(f"a slot appears twice in one step: {slots}")
+    B = len(entries)
+    n_new = []
+    for e in entries:
+        if len(e.tokens) == 0:
+            raise EngineError(f"slot {e.slot}: a step must bring at least one token for each sequence")
+        n_new.append(len(e.tokens))
+    T = sum(n_new)
+    pos0 = [cache.length(s) for s in slots]
+
+    # one packed int32 buffer, one copy to the device
+    n_want = sum(len(e.want) for e in entries)
+    offs = np.cumsum([0, T, T, T, B + 1, B, B, B, n_want])
+    buf = np.empty(offs[-1], dtype=np.int32)
+    ids, tok_seq, tok_pos, cu, p0, slen, slot_a, want = (buf[offs[i]:offs[i + 1]] for i in range(8))
+    t = 0
+    w = 0
+    for b, e in enumerate(entries):
+        n = n_new[b]
+        try:
+            ids[t:t + n] = e.tokens
+        except (TypeError, ValueError, OverflowError):
+            raise EngineError(f"slot {e.slot}: token ids must be integers") from None
+        tok_seq[t:t + n] = b
+        tok_pos[t:t + n] = np.arange(pos0[b], pos0[b] + n)
+        cu[b] = t
+        for i in e.want:
+            if not 0 <= i < n:
+                raise EngineError(f"slot {e.slot}: wanted place {i} is outside this step's {n} tokens")
+            want[w] = t + i
+            w += 1
+        t += n
+    cu[B] = T
+    if T and (ids.min() < 0 or ids.max() >= vocab_size):
+        bad = int(ids[(ids < 0) | (ids >= vocab_size)][0])
+        raise EngineError(f"token id {bad} is outside the vocabulary of {vocab_size}")
+    p0[:] = pos0
+    slen[:] = [p + n for p, n in zip(pos0, n_new)]
+    slot_a[:] = slots
+    cache.reserve({s: p + n for s, p, n in zip(slots, pos0, n_new)})     # after every check: a refused step holds nothing
+    dev = torch.from_numpy(buf).to(device)
+    parts = [dev[offs[i]:offs[i + 1]] for i in range(8)]
+    tables = {}
+    for gid in range(cache.n_groups()):
+        tables[gid] = torch.from_numpy(cache.page_table_host(gid, slots)).to(device)
+    ctx = StepContext(n_tokens=T, n_seqs=B, token_ids=parts[0], tok_seq=parts[1], tok_pos=parts[2],
+                      cu_seqlens=parts[3], pos0=parts[4], seq_len=parts[5], slots=parts[6],
+                      max_new=max(n_new), max_len=int(max(slen)), single_token=all(n == 1 for n in n_new),
+                      page_tables=tables, host_slots=slots)
+    return ctx, parts[7]
+
+
 class Engine:
     """Build with ``Engine.from_folder`` or ``Engine.from_config``.
 
@@ -122,60 +181,7 @@ class Engine:
 
     # ------------------------------------------------------------------ the step
     def build_context(self, entries: list[StepEntry]) -> tuple[StepContext, torch.Tensor]:
-        if not entries:
-            raise EngineError("a step needs at least one sequence")
-        slots = [e.slot for e in entries]
-        if len(set(slots)) != len(slots):
-            raise EngineError(f"a slot appears twice in one step: {slots}")
-        B = len(entries)
-        n_new = []
-        for e in entries:
-            if len(e.tokens) == 0:
-                raise EngineError(f"slot {e.slot}: a step must bring at least one token for each sequence")
-            n_new.append(len(e.tokens))
-        T = sum(n_new)
-        pos0 = [self.cache.length(s) for s in slots]
-        self.cache.reserve({s: p + n for s, p, n in zip(slots, pos0, n_new)})
-
-        # one packed int32 buffer, one copy to the device
-        n_want = sum(len(e.want) for e in entries)
-        offs = np.cumsum([0, T, T, T, B + 1, B, B, B, n_want])
-        buf = np.empty(offs[-1], dtype=np.int32)
-        ids, tok_seq, tok_pos, cu, p0, slen, slot_a, want = (buf[offs[i]:offs[i + 1]] for i in range(8))
-        t = 0
-        w = 0
-        for b, e in enumerate(entries):
-            n = n_new[b]
-            try:
-                ids[t:t + n] = e.tokens
-            except (TypeError, ValueError, OverflowError):
-                raise EngineError(f"slot {e.slot}: token ids must be integers") from None
-            tok_seq[t:t + n] = b
-            tok_pos[t:t + n] = np.arange(pos0[b], pos0[b] + n)
-            cu[b] = t
-            for i in e.want:
-                if not 0 <= i < n:
-                    raise EngineError(f"slot {e.slot}: wanted place {i} is outside this step's {n} tokens")
-                want[w] = t + i
-                w += 1
-            t += n
-        cu[B] = T
-        if T and (ids.min() < 0 or ids.max() >= self.vocab_size):
-            bad = int(ids[(ids < 0) | (ids >= self.vocab_size)][0])
-            raise EngineError(f"token id {bad} is outside the vocabulary of {self.vocab_size}")
-        p0[:] = pos0
-        slen[:] = [p + n for p, n in zip(pos0, n_new)]
-        slot_a[:] = slots
-        dev = torch.from_numpy(buf).to(self.device)
-        parts = [dev[offs[i]:offs[i + 1]] for i in range(8)]
-        tables = {}
-        for gid in range(self.cache.n_groups()):
-            tables[gid] = torch.from_numpy(self.cache.page_table_host(gid, slots)).to(self.device)
-        ctx = StepContext(n_tokens=T, n_seqs=B, token_ids=parts[0], tok_seq=parts[1], tok_pos=parts[2],
-                          cu_seqlens=parts[3], pos0=parts[4], seq_len=parts[5], slots=parts[6],
-                          max_new=max(n_new), max_len=int(max(slen)), single_token=all(n == 1 for n in n_new),
-                          page_tables=tables, host_slots=slots)
-        return ctx, parts[7]
+        return build_step_context(self.cache, entries, self.vocab_size, self.device)
 
     @torch.no_grad()
     def step(self, entries: list[StepEntry]) -> torch.Tensor:

@@ -1,0 +1,176 @@
+"""The engine through its Python entry points: long decoding, the first tokens of a sequence, greedy and
+sampled generation, slots used again, refusals (needs a B200)."""
+import numpy as np
+import pytest
+import torch
+
+import plain_model as pm
+import questwend_b200 as qw
+from helpers import BF16_TOL, FP32_TOL, TINY, make_folder, rel_err
+from questwend_b200.cache import CacheFull
+from questwend_b200.engine.engine import EngineError, StepEntry
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    out = {}
+    for name, (cfgd, seed) in TINY.items():
+        for dtype in ("float32", "bfloat16"):
+            out[name, dtype] = make_folder(tmp_path_factory.mktemp(f"{name}_{dtype}"), cfgd, seed, dtype)
+    return out
+
+
+def tol(dtype):
+    return FP32_TOL if dtype == "float32" else BF16_TOL
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(folders, dtype):
+    """300 tokens one by one after a short prompt: across pages (64) and across runs of the decode kernel (256)."""
+    folder = folders["B", dtype]
+    cfg, w = pm.read_model_folder(folder)
+    eng = qw.Engine.from_folder(folder, dtype=dtype, max_tokens=512)
+    rng = np.random.default_rng(3)
+    toks = rng.integers(0, cfg["vocab_size"], 310).tolist()
+    ref = pm.forward_logits(cfg, w, toks, round16=None if dtype == "float32" else "bf16")
+    (s,) = eng.open_sequences(1)
+    rows = list(eng.step([StepEntry(s, toks[:10], list(range(10)))]).cpu().numpy())
+    for t in toks[10:]:
+        rows.append(eng.step([StepEntry(s, [t], [0])]).cpu().numpy()[0])
+    err = np.abs(np.stack(rows) - ref).max(axis=1) / np.abs(ref).max()
+    assert err.max() < tol(dtype), f"first position off: {int(np.argmax(err > tol(dtype)))}"
+    eng.close_sequences([s])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_first_tokens_of_a_sequence(folders, name, dtype):
+    """Position 0 has one key and no rotation; prompts of one and two tokens, then one token each."""
+    folder = folders[name, dtype]
+    cfg, w = pm.read_model_folder(folder)
+    eng = qw.Engine.from_folder(folder, dtype=dtype, max_tokens=256)
+    seqs = [[5, 9, 2, 7], [11, 3, 3, 8], [0, 1, 2, 3]]
+    heads = [1, 2, 4]
+    refs = [pm.forward_logits(cfg, w, t, round16=None if dtype == "float32" else "bf16") for t in seqs]
+    slots = eng.open_sequences(3)
+    first = eng.step([StepEntry(s, t[:h], list(range(h))) for s, t, h in zip(slots, seqs, heads)]).cpu().numpy()
+    off = 0
+    for r, h in zip(refs, heads):
+        assert rel_err(first[off:off + h], r[:h]) < tol(dtype)
+        off += h
+    for j in (1, 2, 3):
+        live = [i for i in range(3) if heads[i] <= j]
+        out = eng.step([StepEntry(slots[i], [seqs[i][j]], [0]) for i in live]).cpu().numpy()
+        for row, i in zip(out, live):
+            assert rel_err(row, refs[i][j]) < tol(dtype)
+
+
+@pytest.mark.parametrize("use_graph", [True, False])
+def test_greedy_generation_matches_the_plain_implementation(folders, use_graph):
+    folder = folders["B", "float32"]
+    cfg, w = pm.read_model_folder(folder)
+    rng = np.random.default_rng(8)
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (5, 1, 17, 9, 3)]
+    want = [pm.greedy_continue(cfg, w, p, 10) for p in prompts]
+    eng = qw.Engine.from_folder(folder, dtype="float32", max_tokens=1024, max_batch=2)   # three batches, slots reused
+    stats = qw.GenerationStats()
+    res = qw.generate(eng, prompts, max_new_tokens=10, use_graph=use_graph, stats=stats, ignore_eos=True)
+    assert [r.tokens for r in res] == want and stats.batches == 3
+    # a stop token ends a sequence early and is not emitted; the others go on
+    stop = want[2][4]
+    res = qw.generate(eng, prompts, max_new_tokens=10, stop_ids=[stop], use_graph=use_graph)
+    for r, full in zip(res, want):
+        cut = full.index(stop) if stop in full else len(full)
+        assert r.tokens == full[:cut] and r.finish_reason == ("stop" if stop in full else "length")
+    assert eng.cache.slots.n_free == 2 and eng.cache.free_pages() == [eng.cache.n_pages]
+
+
+def test_bfloat16_greedy_generation(folders):
+    folder = folders["B", "bfloat16"]
+    cfg, w = pm.read_model_folder(folder)
+    prompts = [[3, 14, 15, 92, 65], [35, 89, 79], [32, 38, 46, 26, 43, 38, 32, 79, 50]]
+    want = [pm.greedy_continue(cfg, w, p, 8, round16="bf16") for p in prompts]
+    eng = qw.Engine.from_folder(folder, dtype="bfloat16", max_tokens=1024)
+    got = [r.tokens for r in qw.generate(eng, prompts, max_new_tokens=8, ignore_eos=True)]
+    assert got == want
+
+
+def test_sampled_generation_is_a_function_of_the_seed(folders):
+    folder = folders["A", "float32"]
+    eng = qw.Engine.from_folder(folder, dtype="float32", max_tokens=1024, max_batch=3)
+    prompts = [[1, 2, 3], [4, 5], [6, 7, 8, 9]]
+    sp = qw.SamplingParams(temperature=0.8, top_k=40, top_p=0.95, seed=5)
+    a = [r.tokens for r in qw.generate(eng, prompts, max_new_tokens=12, sampling=sp, ignore_eos=True)]
+    b = [r.tokens for r in qw.generate(eng, prompts, max_new_tokens=12, sampling=sp, ignore_eos=True, use_graph=False)]
+    assert a == b                                           # graph replay and plain stepping draw the same
+    c = [r.tokens for r in qw.generate(eng, prompts, max_new_tokens=12, ignore_eos=True,
+                                       sampling=qw.SamplingParams(temperature=0.8, top_k=40, top_p=0.95, seed=6))]
+    assert a != c
+    # one sequence at a time (other batches) gives every sequence the same tokens
+    eng1 = qw.Engine.from_folder(folder, dtype="float32", max_tokens=1024, max_batch=1)
+    d = [r.tokens for r in qw.generate(eng1, prompts, max_new_tokens=12, sampling=sp, ignore_eos=True)]
+    assert a == d
+    # penalties change the outcome and keep it reproducible
+    pen = qw.SamplingParams(temperature=0.0, repeat_penalty=1.5, frequency_penalty=0.5)
+    e = [r.tokens for r in qw.generate(eng, prompts, max_new_tokens=12, sampling=pen, ignore_eos=True)]
+    f = [r.tokens for r in qw.generate(eng, prompts, max_new_tokens=12, sampling=pen, ignore_eos=True, use_graph=False)]
+    g = [r.tokens for r in qw.generate(eng, prompts, max_new_tokens=12, ignore_eos=True)]
+    assert e == f and e != g
+
+
+def test_refusals_leave_the_cache_as_it_was(folders):
+    eng = qw.Engine.from_folder(folders["A", "float32"], dtype="float32", max_tokens=128, max_batch=2)
+    a, b = eng.open_sequences(2)
+    with pytest.raises(EngineError, match="vocabulary"):
+        eng.step([StepEntry(a, [1, 256], [])])
+    with pytest.raises(EngineError, match="at least one token"):
+        eng.step([StepEntry(a, [], [])])
+    with pytest.raises(EngineError, match="twice"):
+        eng.step([StepEntry(a, [1], []), StepEntry(a, [2], [])])
+    with pytest.raises(EngineError, match="wanted place"):
+        eng.step([StepEntry(a, [1, 2], [2])])
+    with pytest.raises(CacheFull):
+        eng.step([StepEntry(a, [1] * 100, []), StepEntry(b, [1] * 100, [])])     # 2 + 2 pages, the cache has 2
+    assert eng.cache.length(a) == 0 and eng.cache.free_pages() == [2]
+    eng.step([StepEntry(a, [1] * 64, []), StepEntry(b, [1] * 64, [])])
+    with pytest.raises(CacheFull):
+        eng.step([StepEntry(a, [1], [0])])
+    assert eng.cache.length(a) == 64
+    with pytest.raises(EngineError, match="CUDA"):
+        qw.Engine.from_folder(folders["A", "float32"], dtype="float32", device="cpu", max_tokens=64)
+
+
+def test_a_32bit_folder_in_the_bfloat16_engine_and_back(folders):
+    """The engine's dtype decides how the matrices are held, whatever the file holds."""
+    cfg, w = pm.read_model_folder(folders["A", "float32"])
+    toks = list(range(3, 40))
+    eng = qw.Engine.from_folder(folders["A", "float32"], dtype="bfloat16", max_tokens=128)
+    (s,) = eng.open_sequences(1)
+    got = eng.step([StepEntry(s, toks, list(range(len(toks))))]).cpu().numpy()
+    w16 = {k: pm.round_bf16(v) if v.ndim == 2 else v for k, v in w.items()}
+    assert rel_err(got, pm.forward_logits(cfg, w16, toks, round16="bf16")) < BF16_TOL
+    assert eng.model.blocks[0].norm1.weight.dtype == torch.float32
+    cfg, w = pm.read_model_folder(folders["A", "bfloat16"])
+    eng = qw.Engine.from_folder(folders["A", "bfloat16"], dtype="float32", max_tokens=128)
+    (s,) = eng.open_sequences(1)
+    got = eng.step([StepEntry(s, toks, list(range(len(toks))))]).cpu().numpy()
+    assert rel_err(got, pm.forward_logits(cfg, w, toks)) < FP32_TOL
+
+
+def test_command_line(folders, tmp_path):
+    import os, subprocess, sys
+    from helpers import ROOT
+    folder = folders["B", "float32"]
+    cfg, w = pm.read_model_folder(folder)
+    want = [pm.greedy_continue(cfg, w, p, 5) for p in ([3, 14, 15], [9, 26])]
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "qw-cli"), "-m", folder, "-p", "3 14 15", "-p", "9,26",
+                           "-n", "5", "--dtype", "float32", "--log-tokens-per-sec", "--ignore-eos"],
+                          capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr
+    assert [[int(x) for x in line.split()] for line in proc.stdout.strip().splitlines()] == want
+    assert "tok/s" in proc.stderr
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "qw-cli"), "-m", folder, "--info"],
+                          capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0 and '"parameters"' in proc.stdout

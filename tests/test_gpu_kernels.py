@@ -1,0 +1,384 @@
+"""Each kernel alone against a plain reference of the same operation, at sizes other than the
+engine's (needs a B200)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model as pm
+from questwend_b200.kernels import ops
+from questwend_b200.kernels.ops import KernelError
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return 5e-6 if dtype == torch.float32 else 2.0 ** -7
+
+
+def close(got, ref, dtype, scale=None):
+    got = got.detach().to(torch.float64).cpu().numpy()
+    ref = np.asarray(ref, dtype=np.float64)
+    s = np.abs(ref).max() if scale is None else scale
+    err = np.abs(got - ref).max() / s
+    assert err <= tol(dtype), f"relative error {err:.3e} above {tol(dtype):.1e}"
+
+
+def f64(t):
+    return t.detach().to(torch.float64).cpu().numpy()
+
+
+# ----------------------------------------------------------------------------- elementwise
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed_gather(dtype):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(37, 100, generator=g).to(dtype).to(DEV)
+    ids = torch.tensor([5, 0, 36, 5, 17], dtype=torch.int32, device=DEV)
+    out = ops.embed_gather(ids, table)
+    assert out.dtype == torch.float32 and torch.equal(out, table[ids.long()].float())
+    bad = torch.full((1,), -1, dtype=torch.int32, device=DEV)
+    out = ops.embed_gather(torch.tensor([1, 99, 2], dtype=torch.int32, device=DEV), table, bad_token=bad)
+    assert int(bad) == 1 and float(out[1].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("D", [100, 1000, 4100, 13000])
+@pytest.mark.parametrize("out_dtype", DTYPES)
+def test_rmsnorm(D, out_dtype):
+    g = torch.Generator().manual_seed(D)
+    x = (torch.randn(7, D, generator=g) * 3).to(DEV)
+    delta = torch.randn(7, D, generator=g).to(DEV)
+    w = (1 + 0.1 * torch.randn(D, generator=g)).to(DEV)
+    eps = 1e-5
+    close(ops.rmsnorm(x, w, eps, out_dtype), pm.rms_norm(f64(x), f64(w), eps), out_dtype)
+    x2 = x.clone()
+    out = ops.rmsnorm(x2, w, eps, out_dtype, delta=delta, write_sum=True)
+    assert torch.equal(x2, x + delta)                                  # the residual sum, in 32-bit
+    close(out, pm.rms_norm(f64(x) + f64(delta), f64(w), eps), out_dtype)
+    x3 = x.clone()
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    out = ops.rmsnorm(x3, w, eps, out_dtype, delta=delta, rows=rows)
+    assert torch.equal(x3, x) and out.shape == (3, D)
+    close(out, pm.rms_norm((f64(x) + f64(delta))[[6, 0, 3]], f64(w), eps), out_dtype)
+
+
+def test_rmsnorm_refuses_a_row_that_does_not_fit():
+    with pytest.raises(KernelError, match="shared memory"):
+        ops.rmsnorm(torch.zeros(1, 60000, device=DEV), torch.ones(60000, device=DEV), 1e-6, torch.float32)
+    with pytest.raises(KernelError, match="CUDA"):
+        ops.rmsnorm(torch.zeros(1, 8), torch.ones(8), 1e-6, torch.float32)
+
+
+@pytest.mark.parametrize("out_dtype", DTYPES)
+def test_silu_mul(out_dtype):
+    gu = (torch.randn(5, 2 * 77, generator=torch.Generator().manual_seed(1)) * 4).to(DEV)
+    close(ops.silu_mul(gu, out_dtype), pm.swiglu(f64(gu)[:, :77], f64(gu)[:, 77:]), out_dtype)
+
+
+def test_add_inplace_and_decode_advance():
+    a, b = torch.randn(3, 11, device=DEV), torch.randn(3, 11, device=DEV)
+    want = a + b
+    assert torch.equal(ops.add_inplace(a, b), want)
+    sampled = torch.tensor([7, 8, 9], dtype=torch.int32, device=DEV)
+    st = [torch.tensor(v, dtype=torch.int32, device=DEV) for v in ([1, 2, 3], [10, 20, 30], [10, 20, 30], [11, 21, 31])]
+    counter = torch.tensor([4], dtype=torch.int32, device=DEV)
+    recent = torch.full((3, 2), -1, dtype=torch.int32, device=DEV)
+    n_seen = torch.tensor([0, 1, 5], dtype=torch.int32, device=DEV)
+    ops.decode_advance(sampled, *st, step_counter=counter, recent=recent, n_seen=n_seen)
+    assert st[0].tolist() == [7, 8, 9] and st[1].tolist() == [11, 21, 31] and st[3].tolist() == [12, 22, 32]
+    assert int(counter) == 5 and recent.tolist() == [[7, -1], [-1, 8], [-1, 9]] and n_seen.tolist() == [1, 2, 6]
+
+
+# ----------------------------------------------------------------------------- rotation and cache write
+def test_rope_table_keeps_digits_at_far_positions():
+    pos = torch.tensor([0, 1, 4095, 131071, 1000003], dtype=torch.int32, device=DEV)
+    inv = (1e6 ** (-2.0 * torch.arange(24, dtype=torch.float64) / 48)).to(DEV)
+    cos, sin = ops.rope_table(pos, inv)
+    ang = pm.rope_angles(pos.cpu().numpy(), 48, 1e6)
+    assert np.abs(f64(cos) - np.cos(ang)).max() < 1e-7 and np.abs(f64(sin) - np.sin(ang)).max() < 1e-7
+
+
+def paged(dense, n_kv_heads, head_dim, dtype, page_size=64, seed=0, extra_pages=3):
+    """Put per-sequence [len, Hkv, hd] arrays into a pool with shuffled page ids; returns pool, table."""
+    n_pages = sum(-(-len(d) // page_size) for d in dense) + extra_pages
+    order = np.random.default_rng(seed).permutation(n_pages)
+    pool = torch.full((n_pages, n_kv_heads, page_size, head_dim), 1e4, dtype=dtype)   # junk where nothing is stored
+    width = max(-(-len(d) // page_size) for d in dense) + 1
+    table = np.zeros((len(dense), width), dtype=np.int32)
+    nxt = 0
+    for b, d in enumerate(dense):
+        for p in range(-(-len(d) // page_size)):
+            pid = int(order[nxt]); nxt += 1
+            table[b, p] = pid
+            chunk = torch.as_tensor(d[p * page_size:(p + 1) * page_size]).to(dtype)    # [n, Hkv, hd]
+            pool[pid, :, :chunk.shape[0]] = chunk.permute(1, 0, 2)
+    return pool.to(DEV), torch.from_numpy(table).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("Hq,Hkv,hd,rot,norm", [(5, 1, 48, 32, True), (4, 2, 16, 16, True), (3, 3, 80, 80, False),
+                                                (2, 1, 32, 0, True)])
+def test_qk_norm_rope_store(dtype, Hq, Hkv, hd, rot, norm):
+    rng = np.random.default_rng(hd)
+    page = 64
+    # two sequences: tokens at positions 60..69 of row 0 (crossing a page edge) and 0..2 of row 1
+    tok_seq = np.array([0] * 10 + [1] * 3, dtype=np.int32)
+    tok_pos = np.array(list(range(60, 70)) + [0, 1, 2], dtype=np.int32)
+    T = len(tok_seq)
+    qkv = rng.normal(size=(T, (Hq + 2 * Hkv) * hd)).astype(np.float32)
+    qw = (1 + 0.1 * rng.normal(size=hd)).astype(np.float32) if norm else None
+    kw = (1 + 0.1 * rng.normal(size=hd)).astype(np.float32) if norm else None
+    eps = 1e-5
+    table = torch.tensor([[4, 1, 0], [2, 0, 0]], dtype=torch.int32, device=DEV)
+    k_pool = torch.full((6, Hkv, page, hd), 777.0, dtype=dtype, device=DEV)
+    v_pool = torch.full((6, Hkv, page, hd), 777.0, dtype=dtype, device=DEV)
+    cos = sin = None
+    if rot:
+        inv = (1e4 ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)).to(DEV)
+        cos, sin = ops.rope_table(torch.from_numpy(tok_pos).to(DEV), inv)
+    dev = lambda a: None if a is None else torch.from_numpy(a).to(DEV)
+    q_out = ops.qk_norm_rope_store(dev(qkv), dev(qw), dev(kw), cos, sin, dev(tok_seq), dev(tok_pos), table, k_pool, v_pool,
+                                   Hq, Hkv, hd, rot, eps)
+    x = qkv.astype(np.float64)
+    q = x[:, :Hq * hd].reshape(T, Hq, hd)
+    k = x[:, Hq * hd:(Hq + Hkv) * hd].reshape(T, Hkv, hd)
+    v = x[:, (Hq + Hkv) * hd:].reshape(T, Hkv, hd)
+    if norm:
+        q, k = pm.rms_norm(q, qw.astype(np.float64), eps), pm.rms_norm(k, kw.astype(np.float64), eps)
+    if rot:
+        ang = pm.rope_angles(tok_pos, rot, 1e4)
+        q, k = pm.apply_rope_neox(q, ang, rot), pm.apply_rope_neox(k, ang, rot)
+    close(q_out, q, dtype)
+    for t in range(T):
+        pid = int(table[tok_seq[t], tok_pos[t] // page])
+        close(k_pool[pid, :, tok_pos[t] % page], k[t], dtype, scale=np.abs(k).max())
+        close(v_pool[pid, :, tok_pos[t] % page], v[t], dtype, scale=np.abs(v).max())
+    written = torch.zeros_like(k_pool, dtype=torch.bool)
+    for t in range(T):
+        written[int(table[tok_seq[t], tok_pos[t] // page]), :, tok_pos[t] % page] = True
+    assert bool((k_pool[~written] == 777.0).all()) and bool((v_pool[~written] == 777.0).all())
+    # a run that reads another run's cache stores nothing
+    k2 = torch.full_like(k_pool, 5.0)
+    ops.qk_norm_rope_store(dev(qkv), dev(qw), dev(kw), cos, sin, dev(tok_seq), dev(tok_pos), table, k2, k2.clone(),
+                           Hq, Hkv, hd, rot, eps, store_kv=False)
+    assert bool((k2 == 5.0).all())
+
+
+# ----------------------------------------------------------------------------- attention
+ATTN_SHAPES = [(4, 2, 16), (6, 1, 32), (3, 3, 48), (8, 2, 64), (8, 1, 128), (2, 1, 256), (12, 1, 16)]
+
+
+def make_qkv(lens, Hq, Hkv, hd, seed):
+    rng = np.random.default_rng(seed)
+    q = [rng.normal(size=(n, Hq, hd)) for n in lens]
+    k = [rng.normal(size=(n, Hkv, hd)) for n in lens]
+    v = [rng.normal(size=(n, Hkv, hd)) for n in lens]
+    return q, k, v
+
+
+def rounded(arrs, dtype):
+    return [pm.round_bf16(a) if dtype == torch.bfloat16 else a for a in arrs]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("Hq,Hkv,hd", ATTN_SHAPES)
+@pytest.mark.parametrize("window", [0, 37])
+def test_attn_prefill(dtype, Hq, Hkv, hd, window):
+    lens = [1, 17, 70, 150, 64]
+    new = [1, 17, 33, 22, 64]                       # the last `new` tokens of each sequence are this step's
+    q, k, v = (rounded(a, dtype) for a in make_qkv(lens, Hq, Hkv, hd, hd + Hq))
+    k_pool, table = paged(k, Hkv, hd, dtype, seed=1)
+    v_pool, _ = paged(v, Hkv, hd, dtype, seed=1)
+    q_new = torch.cat([torch.as_tensor(qq[n - m:]) for qq, n, m in zip(q, lens, new)]).to(dtype).to(DEV)
+    cu = torch.tensor(np.cumsum([0] + new), dtype=torch.int32, device=DEV)
+    pos0 = torch.tensor([n - m for n, m in zip(lens, new)], dtype=torch.int32, device=DEV)
+    out = ops.attn_prefill(q_new, k_pool, v_pool, table, cu, pos0, max(new), 1 / math.sqrt(hd), window=window)
+    ref = np.concatenate([pm.attention_causal(qq, kk, vv, window=window or None)[n - m:].reshape(m, Hq * hd)
+                          for qq, kk, vv, n, m in zip(q, k, v, lens, new)])
+    close(out, ref, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("Hq,Hkv,hd", ATTN_SHAPES)
+@pytest.mark.parametrize("window,split,page", [(0, 128, 64), (100, 64, 64), (0, 256, 64), (0, 128, 32), (50, 64, 16),
+                                               (0, 128, 128)])
+def test_attn_decode(dtype, Hq, Hkv, hd, window, split, page):
+    if page == 128 and hd == 256 and dtype == torch.float32:
+        pytest.skip("refused: see test_attention_refusals")
+    lens = [1, 64, 65, 300, 129, 700]
+    q, k, v = (rounded(a, dtype) for a in make_qkv(lens, Hq, Hkv, hd, hd + split))
+    k_pool, table = paged(k, Hkv, hd, dtype, page_size=page, seed=2)
+    v_pool, _ = paged(v, Hkv, hd, dtype, page_size=page, seed=2)
+    q_last = torch.stack([torch.as_tensor(qq[-1]) for qq in q]).to(dtype).to(DEV)
+    seq_len = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    out = ops.attn_decode(q_last, k_pool, v_pool, table, seq_len, 1 / math.sqrt(hd), max(lens), window=window,
+                          split_tokens=split)
+    ref = np.stack([pm.attention_causal(qq, kk, vv, window=window or None)[-1].reshape(Hq * hd)
+                    for qq, kk, vv in zip(q, k, v)])
+    close(out, ref, dtype)
+    # more runs than the longest sequence needs (a graph's bucket) change nothing
+    again = ops.attn_decode(q_last, k_pool, v_pool, table, seq_len, 1 / math.sqrt(hd), max(lens) + 3 * split,
+                            window=window, split_tokens=split)
+    assert torch.equal(out, again)
+    # a sequence's result does not depend on the rest of the batch
+    alone = ops.attn_decode(q_last[3:4], k_pool, v_pool, table[3:4], seq_len[3:4], 1 / math.sqrt(hd), lens[3],
+                            window=window, split_tokens=split)
+    assert torch.equal(alone[0], out[3])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_one_far_key_among_hundreds(dtype):
+    """Random scores hide a key that is read from the wrong place: make one far key's score stand out,
+    so that the output must be that key's value."""
+    Hq, Hkv, hd, n = 4, 2, 64, 900
+    for far in (3, 63, 64, 511, 640):
+        q, k, v = make_qkv([n], Hq, Hkv, hd, far)
+        q[0][-1] = 0.0
+        q[0][-1, :, 5] = 30.0
+        k[0][:, :, 5] = 0.0
+        k[0][far, :, 5] = 30.0                       # score 900/8 above every other key's
+        q, k, v = (rounded(a, dtype) for a in (q, k, v))
+        k_pool, table = paged(k, Hkv, hd, dtype, seed=far)
+        v_pool, _ = paged(v, Hkv, hd, dtype, seed=far)
+        want = np.stack([v[0][far, h // 2] for h in range(Hq)]).reshape(1, Hq * hd)
+        seq_len = torch.tensor([n], dtype=torch.int32, device=DEV)
+        out = ops.attn_decode(torch.as_tensor(q[0][-1:]).to(dtype).to(DEV), k_pool, v_pool, table, seq_len,
+                              1 / math.sqrt(hd), n, split_tokens=128)
+        close(out, want, dtype)
+        out = ops.attn_prefill(torch.as_tensor(q[0][-5:]).to(dtype).to(DEV), k_pool, v_pool, table,
+                               torch.tensor([0, 5], dtype=torch.int32, device=DEV),
+                               torch.tensor([n - 5], dtype=torch.int32, device=DEV), 5, 1 / math.sqrt(hd))
+        close(out[-1:], want, dtype)
+
+
+def test_window_edge():
+    """With a window of w the key at distance w is hidden and the key at distance w - 1 is seen."""
+    Hq = Hkv = 1
+    hd, n, w = 16, 200, 70
+    q, k, v = make_qkv([n], Hq, Hkv, hd, 9)
+    q[0][-1] = 0.0
+    q[0][-1, :, 0] = 20.0
+    k[0][:, :, 0] = 0.0
+    for dist, seen in ((w, False), (w - 1, True)):
+        kk = [k[0].copy()]
+        kk[0][n - 1 - dist, :, 0] = 20.0
+        k_pool, table = paged(kk, Hkv, hd, torch.float32)
+        v_pool, _ = paged(v, Hkv, hd, torch.float32)
+        seq_len = torch.tensor([n], dtype=torch.int32, device=DEV)
+        qd = torch.as_tensor(q[0][-1:]).float().to(DEV)
+        out_d = ops.attn_decode(qd, k_pool, v_pool, table, seq_len, 1.0, n, window=w, split_tokens=64)
+        out_p = ops.attn_prefill(qd, k_pool, v_pool, table, torch.tensor([0, 1], dtype=torch.int32, device=DEV),
+                                 torch.tensor([n - 1], dtype=torch.int32, device=DEV), 1, 1.0, window=w)
+        target = v[0][n - 1 - dist, 0]
+        for out in (out_d, out_p):
+            hit = np.abs(f64(out)[0] - target).max() < 1e-3
+            assert hit == seen
+
+
+def test_attention_refusals():
+    q = torch.zeros(1, 4, 24, device=DEV)
+    pool = torch.zeros(2, 2, 64, 24, device=DEV)
+    table = torch.zeros(1, 2, dtype=torch.int32, device=DEV)
+    one = torch.ones(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(KernelError, match="multiple of 16"):
+        ops.attn_decode(q, pool, pool, table, one, 1.0, 1)
+    with pytest.raises(KernelError, match="multiple of 16"):
+        ops.attn_prefill(q, pool, pool, table, torch.tensor([0, 1], dtype=torch.int32, device=DEV), one, 1, 1.0)
+    q = torch.zeros(1, 3, 32, device=DEV)
+    pool = torch.zeros(2, 2, 64, 32, device=DEV)
+    with pytest.raises(KernelError, match="not a multiple"):
+        ops.attn_decode(q, pool, pool, table, one, 1.0, 1)
+    q = torch.zeros(1, 1, 256, device=DEV)
+    pool = torch.zeros(2, 1, 128, 256, device=DEV)
+    with pytest.raises(KernelError, match="shared memory"):
+        ops.attn_decode(q, pool, pool, table, one, 1.0, 1)
+    pool = torch.zeros(2, 1, 48, 256, device=DEV)
+    with pytest.raises(KernelError, match="page size"):
+        ops.attn_decode(q, pool, pool, table, one, 1.0, 1)
+
+
+# ----------------------------------------------------------------------------- matrix product for few rows
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M", [1, 2, 3, 5, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(37, 96), (200, 200), (11, 100), (5, 4100)])
+def test_gemm_small(dtype, M, N, K):
+    g = torch.Generator().manual_seed(M * 1000 + K)
+    x = torch.randn(M, K, generator=g).to(dtype).to(DEV)
+    w = torch.randn(N, K, generator=g).to(dtype).to(DEV)
+    ref = f64(x) @ f64(w).T
+    out = ops.gemm_small(x, w)
+    assert out.dtype == torch.float32
+    close(out, ref, torch.float32, scale=np.abs(ref).max() * 4)          # 32-bit sums of exact products
+    res = torch.randn(M, N, generator=g).to(DEV)
+    want = f64(res) + ref
+    close(ops.gemm_small(x, w, residual=res.clone()), want, torch.float32, scale=np.abs(want).max() * 4)
+    # a row's result does not depend on how many rows come with it
+    assert torch.equal(ops.gemm_small(x[:1], w)[0], out[0])
+
+
+# ----------------------------------------------------------------------------- sampling
+def test_greedy_takes_the_lowest_id_among_equals():
+    lg = torch.zeros(3, 1000, device=DEV)
+    lg[0, [400, 17, 900]] = 5.0
+    lg[1, 999] = 1.0
+    lg[2] = -3.0
+    assert ops.sample(lg, 0.0).tolist() == [17, 999, 0]
+
+
+@pytest.mark.parametrize("top_k,top_p,temp", [(0, 1.0, 1.0), (40, 0.95, 0.8), (5, 1.0, 1.3), (0, 0.5, 0.7), (1, 1.0, 1.0)])
+def test_sample_draws_from_the_reference_distribution(top_k, top_p, temp):
+    V, n = 1500, 6000
+    rng = np.random.default_rng(top_k)
+    row = (rng.normal(size=V) * 2.5).astype(np.float32)
+    probs = pm.candidate_probabilities(row, temp, top_k=top_k, top_p=top_p)
+    lg = torch.from_numpy(row).to(DEV).repeat(n, 1)
+    seq = torch.arange(n, dtype=torch.int32, device=DEV)
+    u = torch.zeros(n, dtype=torch.float64, device=DEV)
+    ids = ops.sample(lg, temp, top_k=top_k, top_p=top_p, seed=11, sequence_index=seq, step=3, out_u=u).cpu().numpy()
+    support = set(np.nonzero(probs)[0])
+    assert set(ids) <= support                                           # never outside top-k / top-p
+    counts = np.bincount(ids, minlength=V)
+    sigma = np.sqrt(n * probs * (1 - probs)) + 1e-9
+    assert (np.abs(counts - n * probs) <= 5 * sigma + 2).all()           # the right frequencies
+    un = u.cpu().numpy()
+    assert (un > 0).all() and (un < 1).all() and abs(un.mean() - 0.5) < 0.02
+    # each draw is the walk through the kept tokens in id order with that uniform number
+    cum = np.cumsum(probs)
+    walk = np.searchsorted(cum, un * cum[-1], side="left")
+    assert (walk == ids).mean() > 0.999
+    # the same (seed, sequence, step) gives the same token wherever the row is in the batch
+    again = ops.sample(lg[:7].clone().flip(0), temp, top_k=top_k, top_p=top_p, seed=11,
+                       sequence_index=seq[:7].flip(0).contiguous(), step=3).cpu().numpy()
+    assert (again[::-1] == ids[:7]).all()
+    other = ops.sample(lg, temp, top_k=top_k, top_p=top_p, seed=11, sequence_index=seq, step=4).cpu().numpy()
+    assert top_k == 1 or (other != ids).any()
+    # a step counter on the device adds to the step
+    counter = torch.tensor([1], dtype=torch.int32, device=DEV)
+    same = ops.sample(lg, temp, top_k=top_k, top_p=top_p, seed=11, sequence_index=seq, step=2, step_add=counter)
+    assert (same.cpu().numpy() == ids).all()
+
+
+def test_ties_at_the_cut_go_to_the_lower_ids():
+    V = 300
+    row = np.full(V, -5.0, dtype=np.float32)
+    row[[10, 20, 30, 40]] = 2.0                                          # four equal logits, top_k = 2
+    lg = torch.from_numpy(row).to(DEV).repeat(500, 1)
+    seq = torch.arange(500, dtype=torch.int32, device=DEV)
+    ids = set(ops.sample(lg, 1.0, top_k=2, top_p=1.0, seed=1, sequence_index=seq).tolist())
+    assert ids == {10, 20}
+    ids = set(ops.sample(lg, 1.0, top_k=0, top_p=0.6, seed=1, sequence_index=seq).tolist())
+    assert ids == {10, 20, 30}                                           # 3 of 4 equal shares reach 0.6
+
+
+def test_penalties():
+    V = 200
+    rng = np.random.default_rng(5)
+    row = (rng.normal(size=V) * 2).astype(np.float32)
+    recent = [7, 7, 150, 3, 7, -1, -1, 199]
+    want = pm.penalized_logits(row, [t for t in recent if t >= 0], repeat_penalty=1.3, presence=0.4, frequency=0.2)
+    lg = torch.from_numpy(row).to(DEV).reshape(1, V).clone()
+    ids = ops.sample(lg, 0.0, recent=torch.tensor([recent], dtype=torch.int32, device=DEV), repeat_penalty=1.3,
+                     presence_penalty=0.4, frequency_penalty=0.2)
+    assert np.abs(f64(lg)[0] - want).max() < 1e-5 and int(ids[0]) == int(np.argmax(want))

@@ -1,0 +1,261 @@
+"""Each part of a layer alone, and a toy architecture with a mixer that keeps state of its own,
+registered from here without touching the library's files (needs a B200)."""
+from dataclasses import dataclass
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model as pm
+from helpers import BF16_TOL, FP32_TOL, rel_err
+from questwend_b200.cache import CacheManager
+from questwend_b200.config import ConfigReader, ModelConfig, register_architecture
+from questwend_b200.engine.engine import Engine, StepEntry, build_step_context
+from questwend_b200.engine.plan import LayerSpec, ModelPlan, Run
+from questwend_b200.parts import (Mixer, PartSpec, Runtime, StateSpec, build_part, register_mixer)
+from questwend_b200.weights import MATRIX, TensorSpec, random_tensors
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def f64(t):
+    return t.detach().to(torch.float64).cpu().numpy()
+
+
+def tol(dtype):
+    return FP32_TOL if dtype == torch.float32 else BF16_TOL
+
+
+def r16(dtype):
+    return None if dtype == torch.float32 else "bf16"
+
+
+def make_part(family, spec, dtype, seed=0, **extra):
+    rt = Runtime(DEV, dtype)
+    part = build_part(family, spec, rt, **extra)
+    w = random_tensors(part.tensors(), seed, dtype, device="cpu")
+    part.bind({k: v.to(DEV) for k, v in w.items()})
+    return part, {k: f64(v) for k, v in w.items()}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_norm_part(dtype):
+    part, w = make_part("norm", PartSpec("rms", {"dim": 72, "eps": 1e-4}, prefix="n."), dtype)
+    x = torch.randn(5, 72, device=DEV) * 2
+    assert rel_err(f64(part.forward(x)), pm.rms_norm(f64(x), w["n.weight"], 1e-4)) < tol(dtype)
+    assert part.forward(x).dtype == dtype and part.forward(x, out_dtype=torch.float32).dtype == torch.float32
+
+
+def step_context(cache, slots, token_lists):
+    return build_step_context(cache, [StepEntry(s, t, []) for s, t in zip(slots, token_lists)], 10 ** 6, DEV)[0]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [0, 20])
+def test_attention_part_prompt_then_tokens(dtype, window):
+    D, Hq, Hkv, hd = 80, 5, 1, 48
+    rt = Runtime(DEV, dtype)
+    pos = build_part("position", PartSpec("rotary_neox", {"theta": 5e4, "rotary_dim": 32}), rt)
+    spec = PartSpec("gqa", {"hidden_size": D, "n_heads": Hq, "n_kv_heads": Hkv, "head_dim": hd, "qk_norm": True,
+                            "norm_eps": 1e-5, "window": window}, prefix="a.")
+    part, w = make_part("mixer", spec, dtype, seed=3, position=pos)
+    cache = CacheManager([(part.kv_spec(), None, None)], 1024, 4, 512, dtype, DEV)
+    unit = cache.unit_cache(0)
+    lens, extra = [70, 9, 33], 5
+    rng = np.random.default_rng(1)
+    xs = [rng.normal(size=(n + extra, D)) for n in lens]
+    if dtype == torch.bfloat16:
+        xs = [pm.round_bf16(x) for x in xs]
+
+    def plain(x):
+        T = x.shape[0]
+        q = pm.rms_norm(pm.linear(x, w["a.q_proj.weight"]).reshape(T, Hq, hd), w["a.q_norm.weight"], 1e-5)
+        k = pm.rms_norm(pm.linear(x, w["a.k_proj.weight"]).reshape(T, Hkv, hd), w["a.k_norm.weight"], 1e-5)
+        v = pm.linear(x, w["a.v_proj.weight"]).reshape(T, Hkv, hd)
+        ang = pm.rope_angles(np.arange(T), 32, 5e4)
+        rr = pm._rounder(r16(dtype))
+        q, k, v = rr(pm.apply_rope_neox(q, ang, 32)), rr(pm.apply_rope_neox(k, ang, 32)), rr(v)
+        att = rr(pm.attention_causal(q, k, v, window=window or None).reshape(T, Hq * hd))
+        return pm.linear(att, w["a.o_proj.weight"])
+
+    refs = [plain(x) for x in xs]
+    slots = cache.open(3)
+    ctx = step_context(cache, slots, [[0] * n for n in lens])
+    x_dev = torch.cat([torch.as_tensor(x[:n]) for x, n in zip(xs, lens)]).to(dtype).to(DEV)
+    out = f64(part.forward(x_dev, ctx, unit))
+    for s, n in zip(slots, lens):
+        cache.advance(s, n)
+    off = 0
+    scale = max(np.abs(r).max() for r in refs)
+    for x, n, ref in zip(xs, lens, refs):
+        assert np.abs(out[off:off + n] - ref[:n]).max() / scale < tol(dtype)
+        off += n
+    for i in range(extra):                                  # then one token each, from the cache
+        ctx = step_context(cache, slots, [[0]] * 3)
+        x_dev = torch.stack([torch.as_tensor(x[n + i]) for x, n in zip(xs, lens)]).to(dtype).to(DEV)
+        out = f64(part.forward(x_dev, ctx, unit))
+        for b, (n, ref) in enumerate(zip(lens, refs)):
+            assert np.abs(out[b] - ref[n + i]).max() / scale < tol(dtype)
+        for s in slots:
+            cache.advance(s, 1)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_feed_forward_part(dtype):
+    spec = PartSpec("gated_mlp", {"hidden_size": 56, "intermediate_size": 100}, prefix="f.")
+    part, w = make_part("feed_forward", spec, dtype, seed=2)
+    for T in (3, 40):                                       # few rows: own kernel; many: the library product
+        x = torch.randn(T, 56, device=DEV).to(dtype)
+        a = pm.swiglu(pm.linear(f64(x), w["f.gate_proj.weight"]), pm.linear(f64(x), w["f.up_proj.weight"]))
+        a = pm._rounder(r16(dtype))(a)
+        assert rel_err(f64(part.forward(x, None)), pm.linear(a, w["f.down_proj.weight"])) < tol(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding_and_head_parts(dtype):
+    emb, w = make_part("embedding", PartSpec("token", {"vocab_size": 50, "hidden_size": 24}, prefix="model."), dtype)
+    ids = torch.tensor([3, 49, 0], dtype=torch.int32, device=DEV)
+    assert np.array_equal(f64(emb.forward(ids)), w["model.embed_tokens.weight"][[3, 49, 0]])
+    rt = Runtime(DEV, dtype)
+    for tied in (True, False, None):
+        head = build_part("head", PartSpec("linear", {"vocab_size": 50, "hidden_size": 24, "tied": tied,
+                                                      "tied_to": "model.embed_tokens.weight"}), rt)
+        own = torch.randn(50, 24).to(dtype)
+        head.bind({"model.embed_tokens.weight": emb.table, "lm_head.weight": own.to(DEV)})
+        x = torch.randn(2, 24, device=DEV).to(dtype)
+        want = w["model.embed_tokens.weight"] if tied else f64(own)
+        assert rel_err(f64(head.forward(x)), f64(x) @ want.T) < tol(dtype)
+    head.bind({"model.embed_tokens.weight": emb.table})     # undecided and no head stored: tied
+    assert head.weight is emb.table
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_block_part(dtype):
+    cfg = {"hidden_size": 64, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16,
+           "rms_norm_eps": 1e-6, "rope_theta": 1e4}
+    layer = LayerSpec(block=PartSpec("pre_norm", {}, prefix="model.layers.0."),
+                      mixer=PartSpec("gqa", {"hidden_size": 64, "n_heads": 4, "n_kv_heads": 2, "head_dim": 16,
+                                             "qk_norm": True, "norm_eps": 1e-6}),
+                      feed_forward=PartSpec("gated_mlp", {"hidden_size": 64, "intermediate_size": 88}),
+                      norm=PartSpec("rms", {"dim": 64, "eps": 1e-6}),
+                      position=PartSpec("rotary_neox", {"theta": 1e4, "rotary_dim": 16}))
+    rt = Runtime(DEV, dtype)
+    pos = build_part("position", layer.position, rt)
+    block, w = make_part("block", layer.block, dtype, seed=4, layer=layer, position=pos)
+    cache = CacheManager([(block.mixer.kv_spec(), None, None)], 256, 2, 256, dtype, DEV)
+    (slot,) = cache.open(1)
+    T = 19
+    h = np.random.default_rng(0).normal(size=(T, 64)).astype(np.float32)
+    ref = pm.decoder_layer(h.astype(np.float64), w, "model.layers.0.", cfg, np.arange(T), round16=r16(dtype))
+    ctx = step_context(cache, [slot], [[0] * T])
+    h_dev, delta = block.forward(torch.from_numpy(h).to(DEV), None, ctx, cache.unit_cache(0))
+    assert h_dev.dtype == torch.float32 and delta.dtype == torch.float32     # the residual stream is 32-bit
+    assert rel_err(f64(h_dev) + f64(delta), ref) < tol(dtype)
+
+
+# ----------------------------------------------------------------------------- a toy architecture, defined here
+class RunningMeanMixer(Mixer):
+    """y_t = mean(x_0..x_t) W.  Keeps, per sequence, the running sum and the count: fixed-size state,
+    no keys or values.  Written with torch operations; it is a test's toy, not a model."""
+
+    def __init__(self, spec, runtime, position=None):
+        super().__init__(spec, runtime)
+        self.hidden = spec.params["hidden_size"]
+
+    def tensors(self):
+        return [TensorSpec(self.prefix + "w.weight", (self.hidden, self.hidden), MATRIX)]
+
+    def bind(self, weights):
+        self.w = weights[self.prefix + "w.weight"]
+
+    def state_spec(self):
+        return StateSpec((self.hidden + 1,), torch.float32)
+
+    def forward(self, x, ctx, cache):
+        out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+        cu = ctx.cu_seqlens.tolist()
+        for b, slot in enumerate(ctx.host_slots):
+            xs = x[cu[b]:cu[b + 1]].float()
+            state = cache.state[slot]
+            sums = state[:-1] + torch.cumsum(xs, 0)
+            counts = state[-1] + torch.arange(1, xs.shape[0] + 1, device=x.device)
+            out[cu[b]:cu[b + 1]] = (sums / counts[:, None]).to(x.dtype).float() @ self.w.float().T
+            if cache.writable:
+                state[:-1] = sums[-1]
+                state[-1] = counts[-1]
+        return out
+
+
+@dataclass(frozen=True)
+class ToyConfig(ModelConfig):
+    hidden_size: int
+    vocab_size: int
+    architecture = "ToyStateForCausalLM"
+
+    @classmethod
+    def from_reader(cls, r: ConfigReader):
+        return cls(r.integer("hidden_size"), r.integer("vocab_size"))
+
+    def to_dict(self):
+        return {"architectures": [self.architecture], "hidden_size": self.hidden_size, "vocab_size": self.vocab_size}
+
+
+def toy_plan(cfg: ToyConfig) -> ModelPlan:
+    D = cfg.hidden_size
+    norm = PartSpec("rms", {"dim": D, "eps": 1e-5})
+    ffn = PartSpec("gated_mlp", {"hidden_size": D, "intermediate_size": 2 * D})
+    attn = PartSpec("gqa", {"hidden_size": D, "n_heads": 2, "n_kv_heads": 1, "head_dim": 16, "qk_norm": False})
+    toy = PartSpec("toy_running_mean", {"hidden_size": D})
+    rope = PartSpec("rotary_neox", {"theta": 1e4, "rotary_dim": 16})
+    block = lambda i: PartSpec("pre_norm", {"mixer_norm": "n1", "ffn_norm": "n2", "mixer_prefix": "mix", "ffn_prefix": "ff"},
+                               prefix=f"layers.{i}.")
+    layers = [LayerSpec(block(0), toy, ffn, norm), LayerSpec(block(1), attn, ffn, norm, rope),
+              LayerSpec(block(2), toy, ffn, norm)]
+    # layer 1 runs twice; its second run reads the first run's keys and values
+    schedule = [Run(0), Run(1), Run(2), Run(1, cache_of=1), Run(0)]
+    return ModelPlan(architecture=cfg.architecture, hidden_size=D, vocab_size=cfg.vocab_size,
+                     embedding=PartSpec("token", {"vocab_size": cfg.vocab_size, "hidden_size": D, "name": "emb.weight"}),
+                     layers=layers, schedule=schedule, final_norm=PartSpec("rms", {"dim": D, "eps": 1e-5}, prefix="norm."),
+                     head=PartSpec("linear", {"vocab_size": cfg.vocab_size, "hidden_size": D, "tied": True,
+                                              "tied_to": "emb.weight"}))
+
+
+def test_toy_mixer_with_state_of_its_own():
+    register_mixer("toy_running_mean", RunningMeanMixer, replace=True)
+    register_architecture("ToyStateForCausalLM", ToyConfig, toy_plan, replace=True)
+    cfg = ToyConfig(32, 40)
+    eng = Engine.from_config(cfg, seed=7, dtype="float32", max_tokens=512)
+    units = eng.model.cache_units()
+    assert [u[0] is not None for u in units] == [False, True, False, True, False]
+    assert [u[1] is not None for u in units] == [True, False, True, False, True]
+    assert eng.cache.n_groups() == 1 and not eng.unit_caches[3].writable
+    assert eng.unit_caches[0].state.data_ptr() != eng.unit_caches[4].state.data_ptr()   # a layer run twice: two states
+    rng = np.random.default_rng(0)
+    seqs = [rng.integers(0, 40, n).tolist() for n in (23, 5, 70)]
+    slots = eng.open_sequences(3)
+    whole = eng.step([StepEntry(s, t, list(range(len(t)))) for s, t in zip(slots, seqs)]).cpu().numpy()
+    eng.close_sequences(slots)
+    # the same sequences: a prompt of a few tokens, then token by token, in slots that were used before
+    slots = eng.open_sequences(3)
+    rows = {i: [] for i in range(3)}
+    cuts = [4, 1, 66]
+    first = eng.step([StepEntry(s, t[:c], list(range(c))) for s, t, c in zip(slots, seqs, cuts)]).cpu().numpy()
+    off = 0
+    for i, c in enumerate(cuts):
+        rows[i] += list(first[off:off + c]); off += c
+    live = [0, 1, 2]
+    pos = list(cuts)
+    while live:
+        out = eng.step([StepEntry(slots[i], [seqs[i][pos[i]]], [0]) for i in live]).cpu().numpy()
+        for r, i in enumerate(live):
+            rows[i].append(out[r]); pos[i] += 1
+        done = [i for i in live if pos[i] == len(seqs[i])]
+        eng.close_sequences([slots[i] for i in done])
+        live = [i for i in live if i not in done]
+    off = 0
+    for i, t in enumerate(seqs):
+        assert rel_err(np.stack(rows[i]), whole[off:off + len(t)]) < FP32_TOL
+        off += len(t)
+    assert eng.cache.slots.n_free == eng.max_batch

@@ -419,3 +419,47 @@ extern "C" int qwb_attn_decode(const void* q, const void* k_pool, const void* v_
                                    table_width, scale, window, split_tokens, max_runs, stream);
     return qwb_fail(QWB_ERR_ARG, "attn_decode: unknown dtype %d", dtype);
 }
+
+// ---------------------------------------------------------------------------------
+// The same decode attention with its scratch inside the library (attention_noalloc.h).
+// ---------------------------------------------------------------------------------
+#include "attention_noalloc.h"
+
+#define QWB_NOALLOC_MAX_DEVICES 64
+
+// In host code this name is only a handle of the symbol, never a device address: a kernel is
+// given the address that cudaGetSymbolAddress returns for the current device.
+static __device__ __align__(256) float qwb_noalloc_scratch[QWB_NOALLOC_SCRATCH_FLOATS];
+static float* qwb_noalloc_scratch_ptr[QWB_NOALLOC_MAX_DEVICES];     // per device, looked up once
+
+extern "C" long long qwb_attn_decode_noalloc_capacity(void) { return QWB_NOALLOC_SCRATCH_FLOATS; }
+
+extern "C" int qwb_attn_decode_noalloc(const void* q, const void* k_pool, const void* v_pool, const int* page_table,
+                                       const int* seq_len, void* out, int dtype, int B, int Hq, int Hkv, int hd,
+                                       int page_size, int table_width, float scale, int window, int split_tokens,
+                                       int max_runs, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (Hq <= 0 || hd <= 0 || max_runs <= 0)
+        return qwb_fail(QWB_ERR_ARG, "attn_decode_noalloc: bad sizes Hq=%d hd=%d max_runs=%d", Hq, hd, max_runs);
+    const long long need = qwb_attn_decode_scratch_floats(B, Hq, hd, max_runs);
+    if (max_runs > 1 && need > (long long)QWB_NOALLOC_SCRATCH_FLOATS)
+        return qwb_fail(QWB_ERR_ARG,
+                        "attn_decode_noalloc: %d sequences x %d heads x %d runs x (%d + 2) = %lld floats of scratch, the "
+                        "built-in array holds %lld; use qwb_attn_decode with scratch of your own",
+                        B, Hq, max_runs, hd, need, (long long)QWB_NOALLOC_SCRATCH_FLOATS);
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "attn_decode_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
+    if (device < 0 || device >= QWB_NOALLOC_MAX_DEVICES)
+        return qwb_fail(QWB_ERR_ARG, "attn_decode_noalloc: device %d is beyond the %d this library keeps track of", device,
+                        QWB_NOALLOC_MAX_DEVICES);
+    if (!qwb_noalloc_scratch_ptr[device]) {                         // set-up, once per device
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, qwb_noalloc_scratch);
+        if (e != cudaSuccess || !p)
+            return qwb_fail(QWB_ERR_CUDA, "attn_decode_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        qwb_noalloc_scratch_ptr[device] = p;
+    }
+    return qwb_attn_decode(q, k_pool, v_pool, page_table, seq_len, qwb_noalloc_scratch_ptr[device], out, dtype, B, Hq, Hkv,
+                           hd, page_size, table_width, scale, window, split_tokens, max_runs, stream);
+}

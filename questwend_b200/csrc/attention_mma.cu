@@ -1,0 +1,433 @@
+// Tensor-core attention over the paged bfloat16 cache, for head sizes 64 and 128.
+//
+// Same contract as attention.cu (causal, grouped heads, optional window, pages of 64 keys);
+// those kernels stay the path for float32 and for other head sizes.  Here the scores
+// S = Q K^T and the output O = P V run on mma.m16n8k16 (bf16 in, 32-bit out), with the
+// running maximum, the sum and O kept in 32-bit registers (the reference's tensor-core
+// kernel does the same on mma.sync, ggml-cuda/fattn-mma-f16.cuh).
+//
+// A block serves one key/value head.  Its rows are (token, query head of the group) pairs, so
+// the heads that share the key/value head share every K and V tile that is loaded (the
+// reference packs heads the same way, ggml-cuda/fattn.cu:91-110).  A K or V tile is one
+// (page, head) block of the cache: 64 keys x hd, contiguous, copied to shared memory with
+// 16-byte cp.async and stored with its 16-byte chunks XOR-swizzled by the row, so that
+// ldmatrix reads without bank conflicts.  K feeds the mma as is; V goes through
+// ldmatrix.trans.  Rows of a tile beyond the sequence's keys are zeroed (V) or masked (K).
+//
+//   prefill: 4 warps x 16 rows = 64 rows per block (64 / group tokens), all warps walk the
+//            same tiles, double buffered.
+//   decode : one token per sequence; the rows are the group's heads (padded to 16); the
+//            4 warps take different pages of the block's run of keys and their partial
+//            results meet in shared memory.  Runs, scratch layout and the combine kernel
+//            are those of attention.cu.
+#include "common.cuh"
+
+#define AM_TILE 64          // keys per tile = tokens per cache page
+#define AM_WARPS 4
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t* r, const void* smem_ptr) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem_ptr);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t* r, const void* smem_ptr) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem_ptr);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Copy one (page, head) block of K or V, [64][HD] bf16, into a swizzled shared tile.  Rows from
+// `n_valid` on are zeroed (their cache memory may hold anything).  `nthreads` threads take part.
+template <int HD>
+__device__ __forceinline__ void load_tile(bf16* tile, const bf16* src, int n_valid, int tid, int nthreads) {
+    constexpr int CPR = HD / 8;                       // 16-byte chunks per row
+    for (int i = tid; i < AM_TILE * CPR; i += nthreads) {
+        const int row = i / CPR, c = i % CPR;
+        bf16* dst = tile + row * HD + ((c ^ (row & 7)) << 3);
+        if (row < n_valid) cp_async16(dst, src + row * HD + (c << 3));
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+    }
+}
+
+// One warp, 16 rows, one tile of 64 keys: S = Q K^T, mask, online softmax, O += P V.
+//   qf     Q fragments of the warp's 16 rows: [HD/16][4]
+//   key0   position of the tile's first key; row_pos[2]: positions of rows g and g + 8 (-1: row unused)
+//   len    keys of the sequence; window (0: none)
+//   m, l   running maximum and (this thread's share of the) sum for rows g and g + 8;  o: [HD/8][4]
+template <int HD>
+__device__ __forceinline__ void tile_step(const uint32_t (*qf)[4], const bf16* Kt, const bf16* Vt, int key0, const int* row_pos,
+                                          int len, int window, float sl2, float* m, float* l, float (*o)[4], int lane) {
+    constexpr int KS = HD / 16, NT = AM_TILE / 8, DT = HD / 8;
+    const int t = lane & 3;
+    float s[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    const int mi = lane >> 3, mr = lane & 7;          // ldmatrix: which matrix this lane addresses, and its row
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+        for (int j = 0; j < NT; j += 2) {
+            const int key = 8 * (j + (mi >> 1)) + mr, chunk = 2 * ks + (mi & 1);
+            uint32_t b[4];
+            ldmatrix_x4(b, Kt + key * HD + ((chunk ^ (key & 7)) << 3));
+            mma_16816(s[j], qf[ks], b[0], b[1]);
+            mma_16816(s[j + 1], qf[ks], b[2], b[3]);
+        }
+    }
+    // mask and running maximum
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int key = key0 + 8 * j + 2 * t + (r & 1);
+            const int qp = row_pos[r >> 1];
+            const bool ok = qp >= 0 && key <= qp && key < len && (window <= 0 || key > qp - window);
+            s[j][r] = ok ? s[j][r] : -INFINITY;
+            mx[r >> 1] = fmaxf(mx[r >> 1], s[j][r]);
+        }
+    }
+    float alpha[2], base[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        const float m_new = fmaxf(m[h], mx[h]);
+        base[h] = m_new == -INFINITY ? 0.f : m_new * sl2;
+        alpha[h] = exp2f(m[h] * sl2 - base[h]);       // m = -inf gives 0
+        m[h] = m_new;
+        l[h] *= alpha[h];
+    }
+#pragma unroll
+    for (int d = 0; d < DT; ++d) {
+        o[d][0] *= alpha[0]; o[d][1] *= alpha[0];
+        o[d][2] *= alpha[1]; o[d][3] *= alpha[1];
+    }
+    // probabilities, then O += P V
+#pragma unroll
+    for (int kk = 0; kk < AM_TILE / 16; ++kk) {
+        uint32_t pf[4];
+        float p[2][4];
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                p[u][r] = exp2f(s[2 * kk + u][r] * sl2 - base[r >> 1]);
+                l[r >> 1] += p[u][r];
+            }
+        pf[0] = pack_bf16(p[0][0], p[0][1]);
+        pf[1] = pack_bf16(p[0][2], p[0][3]);
+        pf[2] = pack_bf16(p[1][0], p[1][1]);
+        pf[3] = pack_bf16(p[1][2], p[1][3]);
+#pragma unroll
+        for (int jd = 0; jd < DT; jd += 2) {
+            const int key = 16 * kk + 8 * (mi & 1) + mr, chunk = jd + (mi >> 1);
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, Vt + key * HD + ((chunk ^ (key & 7)) << 3));
+            mma_16816(o[jd], pf, b[0], b[1]);
+            mma_16816(o[jd + 1], pf, b[2], b[3]);
+        }
+    }
+}
+
+// Q fragments of rows (g, g + 8) of a warp; q_lo / q_hi point at the rows' hd values (or null).
+template <int HD>
+__device__ __forceinline__ void load_q_frags(uint32_t (*qf)[4], const bf16* q_lo, const bf16* q_hi, int lane) {
+    const int t = lane & 3;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+        const int d = 16 * ks + 2 * t;
+        qf[ks][0] = q_lo ? *reinterpret_cast<const uint32_t*>(q_lo + d) : 0u;
+        qf[ks][1] = q_hi ? *reinterpret_cast<const uint32_t*>(q_hi + d) : 0u;
+        qf[ks][2] = q_lo ? *reinterpret_cast<const uint32_t*>(q_lo + d + 8) : 0u;
+        qf[ks][3] = q_hi ? *reinterpret_cast<const uint32_t*>(q_hi + d + 8) : 0u;
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// prefill
+// ---------------------------------------------------------------------------------
+template <int HD>
+__global__ void __launch_bounds__(AM_WARPS * 32)
+attn_mma_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+                        const int* __restrict__ page_table, const int* __restrict__ cu_seqlens, const int* __restrict__ pos0,
+                        bf16* __restrict__ out, int Hq, int Hkv, int table_width, float scale, int window, int Gc, int chunks) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* tiles = reinterpret_cast<bf16*>(smem_raw);                 // [2 buffers][K, V][64][HD]
+    const int b = blockIdx.z;
+    const int kvh = blockIdx.y / chunks, chunk = blockIdx.y % chunks;
+    const int G = Hq / Hkv;
+    const int tok_per_block = (AM_WARPS * 16) / Gc;
+    const int t0 = cu_seqlens[b], n_new = cu_seqlens[b + 1] - t0;
+    const int q0 = blockIdx.x * tok_per_block;
+    if (q0 >= n_new) return;
+    const int p0 = pos0[b];
+    const int len = p0 + n_new;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+
+    // rows of this thread: r = warp * 16 + g (+ 8) -> (token q0 + r / Gc, head chunk * Gc + r % Gc)
+    int row_pos[2];
+    const bf16* qrow[2];
+    bf16* orow[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = warp * 16 + g + 8 * h;
+        const int tok = q0 + r / Gc, head_in = chunk * Gc + r % Gc;
+        const bool ok = r < tok_per_block * Gc && tok < n_new && head_in < G;
+        row_pos[h] = ok ? p0 + tok : -1;
+        const size_t at = ((size_t)(t0 + tok) * Hq + kvh * G + head_in) * HD;
+        qrow[h] = ok ? q + at : nullptr;
+        orow[h] = ok ? out + at : nullptr;
+    }
+    uint32_t qf[HD / 16][4];
+    load_q_frags<HD>(qf, qrow[0], qrow[1], lane);
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f}, o[HD / 8][4];
+#pragma unroll
+    for (int d = 0; d < HD / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+
+    const int last_tok = min(n_new, q0 + tok_per_block) - 1;
+    const int k_last = p0 + last_tok;                                          // last key any row sees
+    const int k_first = window > 0 ? max(0, p0 + q0 - window + 1) : 0;
+    const int tile_first = k_first / AM_TILE, tile_last = k_last / AM_TILE;
+    const int* pages = page_table + (size_t)b * table_width;
+    const float sl2 = scale * 1.4426950408889634f;
+
+    auto issue = [&](int tile, int buf) {
+        const size_t src = ((size_t)pages[tile] * Hkv + kvh) * AM_TILE * HD;
+        const int n_valid = min(AM_TILE, len - tile * AM_TILE);
+        bf16* kt = tiles + (size_t)buf * 2 * AM_TILE * HD;
+        load_tile<HD>(kt, k_pool + src, n_valid, threadIdx.x, blockDim.x);
+        load_tile<HD>(kt + AM_TILE * HD, v_pool + src, n_valid, threadIdx.x, blockDim.x);
+        cp_async_commit();
+    };
+    issue(tile_first, 0);
+    for (int tile = tile_first; tile <= tile_last; ++tile) {
+        const int buf = (tile - tile_first) & 1;
+        if (tile < tile_last) { issue(tile + 1, buf ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+        __syncthreads();
+        const bf16* kt = tiles + (size_t)buf * 2 * AM_TILE * HD;
+        // a warp whose rows all lie before this tile has nothing to see in it
+        const int warp_last_tok = min(last_tok, q0 + (warp * 16 + 15) / Gc);
+        if (tile * AM_TILE <= p0 + warp_last_tok)
+            tile_step<HD>(qf, kt, kt + AM_TILE * HD, tile * AM_TILE, row_pos, len, window, sl2, m, l, o, lane);
+        __syncthreads();
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        if (!orow[h]) continue;
+        const float inv = 1.f / l[h];
+#pragma unroll
+        for (int d = 0; d < HD / 8; ++d)
+            *reinterpret_cast<uint32_t*>(orow[h] + 8 * d + 2 * t) = pack_bf16(o[d][2 * h] * inv, o[d][2 * h + 1] * inv);
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// decode: block = (run, key/value head and head chunk, sequence); warp w takes the run's pages w, w + 4, ...
+// ---------------------------------------------------------------------------------
+template <int HD>
+__global__ void __launch_bounds__(AM_WARPS * 32)
+attn_mma_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+                       const int* __restrict__ page_table, const int* __restrict__ seq_len, float* __restrict__ part_acc,
+                       float* __restrict__ part_m, float* __restrict__ part_l, bf16* __restrict__ out, int Hq, int Hkv,
+                       int table_width, float scale, int window, int split_tokens, int max_runs, int Gc, int chunks) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int b = blockIdx.z, run = blockIdx.x;
+    const int len = seq_len[b];
+    const int k_lo = window > 0 ? max(0, len - window) : 0;
+    const int run_first = k_lo / split_tokens, run_end = (len + split_tokens - 1) / split_tokens;
+    if (run < run_first || run >= run_end) return;
+    const int kvh = blockIdx.y / chunks, chunk = blockIdx.y % chunks;
+    const int G = Hq / Hkv;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    bf16* my_tiles = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * 2 * AM_TILE * HD;   // K then V, this warp's own
+
+    int row_pos[2];
+    const bf16* qrow[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = g + 8 * h, head_in = chunk * Gc + r;
+        const bool ok = r < Gc && head_in < G;
+        row_pos[h] = ok ? len - 1 : -1;
+        qrow[h] = ok ? q + ((size_t)b * Hq + kvh * G + head_in) * HD : nullptr;
+    }
+    uint32_t qf[HD / 16][4];
+    load_q_frags<HD>(qf, qrow[0], qrow[1], lane);
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f}, o[HD / 8][4];
+#pragma unroll
+    for (int d = 0; d < HD / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+
+    const int tok_begin = run * split_tokens, tok_end = min(len, tok_begin + split_tokens);
+    const int* pages = page_table + (size_t)b * table_width;
+    const float sl2 = scale * 1.4426950408889634f;
+    for (int base = tok_begin + warp * AM_TILE; base < tok_end; base += AM_WARPS * AM_TILE) {
+        if (base + AM_TILE <= k_lo) continue;                                  // a page wholly before the window
+        const size_t src = ((size_t)pages[base / AM_TILE] * Hkv + kvh) * AM_TILE * HD;
+        const int n_valid = min(AM_TILE, len - base);
+        __syncwarp();
+        load_tile<HD>(my_tiles, k_pool + src, n_valid, lane, 32);
+        load_tile<HD>(my_tiles + AM_TILE * HD, v_pool + src, n_valid, lane, 32);
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncwarp();
+        tile_step<HD>(qf, my_tiles, my_tiles + AM_TILE * HD, base, row_pos, len, window, sl2, m, l, o, lane);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+    // the warps' partial results meet in shared memory: [warp][16 rows][HD + 2]
+    __syncthreads();
+    float* merge = reinterpret_cast<float*>(smem_raw);
+    constexpr int RS = HD + 2;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float* row = merge + ((size_t)warp * 16 + g + 8 * h) * RS;
+#pragma unroll
+        for (int d = 0; d < HD / 8; ++d) { row[8 * d + 2 * t] = o[d][2 * h]; row[8 * d + 2 * t + 1] = o[d][2 * h + 1]; }
+        if (t == 0) { row[HD] = m[h]; row[HD + 1] = l[h]; }
+    }
+    __syncthreads();
+    const bool single = (run_end - run_first) == 1;
+    for (int idx = threadIdx.x; idx < Gc * HD; idx += blockDim.x) {
+        const int r = idx / HD, d = idx - r * HD, head_in = chunk * Gc + r;
+        if (head_in >= G) continue;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < AM_WARPS; ++w) M = fmaxf(M, merge[((size_t)w * 16 + r) * RS + HD]);
+        float L = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < AM_WARPS; ++w) {
+            const float* row = merge + ((size_t)w * 16 + r) * RS;
+            const float f = row[HD] == -INFINITY ? 0.f : exp2f((row[HD] - M) * sl2);
+            L += row[HD + 1] * f;
+            acc += row[d] * f;
+        }
+        const int head = kvh * G + head_in;
+        if (single) {
+            out[((size_t)b * Hq + head) * HD + d] = __float2bfloat16_rn(acc / L);
+        } else {
+            const size_t at = ((size_t)b * Hq + head) * max_runs + run;
+            part_acc[at * HD + d] = acc;
+            if (d == 0) { part_m[at] = M * scale; part_l[at] = L; }   // the combine kernel works with scaled scores
+        }
+    }
+}
+
+// out = sum_r acc_r e^(m_r - M) / sum_r l_r e^(m_r - M) over the runs, in index order (as in attention.cu).
+__global__ void attn_mma_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_m,
+                                        const float* __restrict__ part_l, const int* __restrict__ seq_len,
+                                        bf16* __restrict__ out, int Hq, int hd, int window, int split_tokens, int max_runs) {
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int len = seq_len[b];
+    const int k_lo = window > 0 ? max(0, len - window) : 0;
+    const int run_first = k_lo / split_tokens, run_end = (len + split_tokens - 1) / split_tokens;
+    if (run_end - run_first <= 1) return;
+    const size_t row = ((size_t)b * Hq + h) * max_runs;
+    float M = -INFINITY;
+    for (int r = run_first; r < run_end; ++r) M = fmaxf(M, part_m[row + r]);
+    float L = 0.f;
+    for (int r = run_first; r < run_end; ++r) L += part_l[row + r] * expf(part_m[row + r] - M);
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float a = 0.f;
+        for (int r = run_first; r < run_end; ++r) a += part_acc[(row + r) * hd + d] * expf(part_m[row + r] - M);
+        out[((size_t)b * Hq + h) * hd + d] = __float2bfloat16_rn(a / L);
+    }
+}
+
+static int group_chunk(int G) { return G < 16 ? G : 16; }
+
+template <int HD>
+static int launch_prefill(const void* q, const void* k_pool, const void* v_pool, const int* page_table, const int* cu_seqlens,
+                          const int* pos0, void* out, int B, int max_new, int Hq, int Hkv, int table_width, float scale,
+                          int window, cudaStream_t stream) {
+    const int G = Hq / Hkv, Gc = group_chunk(G), chunks = (G + Gc - 1) / Gc;
+    const int tok_per_block = (AM_WARPS * 16) / Gc;
+    const size_t smem = (size_t)2 * 2 * AM_TILE * HD * sizeof(bf16);
+    cudaError_t e = cudaFuncSetAttribute(attn_mma_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "attn_mma_prefill: %s", cudaGetErrorString(e));
+    dim3 grid((max_new + tok_per_block - 1) / tok_per_block, Hkv * chunks, B);
+    attn_mma_prefill_kernel<HD><<<grid, AM_WARPS * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
+        page_table, cu_seqlens, pos0, (bf16*)out, Hq, Hkv, table_width, scale, window, Gc, chunks);
+    return qwb_check_launch("attn_mma_prefill");
+}
+
+static int check_sizes(const char* what, int Hq, int Hkv, int hd, int page_size, int B) {
+    if (hd != 64 && hd != 128) return qwb_fail(QWB_ERR_ARG, "%s: head size %d is not 64 or 128", what, hd);
+    if (page_size != AM_TILE) return qwb_fail(QWB_ERR_ARG, "%s: page size %d is not %d", what, page_size, AM_TILE);
+    if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) return qwb_fail(QWB_ERR_ARG, "%s: %d query heads are not a multiple of %d key/value heads", what, Hq, Hkv);
+    if (B > 65535 || Hq > 65535) return qwb_fail(QWB_ERR_ARG, "%s: batch %d or heads %d above 65535", what, B, Hq);
+    return 0;
+}
+
+// bfloat16 only.  Arguments as qwb_attn_prefill.
+extern "C" int qwb_attn_mma_prefill(const void* q, const void* k_pool, const void* v_pool, const int* page_table,
+                                    const int* cu_seqlens, const int* pos0, void* out, int B, int max_new, int Hq, int Hkv,
+                                    int hd, int page_size, int table_width, float scale, int window, cudaStream_t stream) {
+    if (B <= 0 || max_new <= 0) return 0;
+    if (int rc = check_sizes("attn_mma_prefill", Hq, Hkv, hd, page_size, B)) return rc;
+    if (hd == 64) return launch_prefill<64>(q, k_pool, v_pool, page_table, cu_seqlens, pos0, out, B, max_new, Hq, Hkv, table_width, scale, window, stream);
+    return launch_prefill<128>(q, k_pool, v_pool, page_table, cu_seqlens, pos0, out, B, max_new, Hq, Hkv, table_width, scale, window, stream);
+}
+
+template <int HD>
+static int launch_decode(const void* q, const void* k_pool, const void* v_pool, const int* page_table, const int* seq_len,
+                         float* scratch, void* out, int B, int Hq, int Hkv, int table_width, float scale, int window,
+                         int split_tokens, int max_runs, cudaStream_t stream) {
+    const int G = Hq / Hkv, Gc = group_chunk(G), chunks = (G + Gc - 1) / Gc;
+    size_t smem = (size_t)AM_WARPS * 2 * AM_TILE * HD * sizeof(bf16);
+    const size_t merge = (size_t)AM_WARPS * 16 * (HD + 2) * sizeof(float);
+    if (merge > smem) smem = merge;
+    cudaError_t e = cudaFuncSetAttribute(attn_mma_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "attn_mma_decode: %s", cudaGetErrorString(e));
+    float* part_acc = scratch;
+    float* part_m = scratch + (size_t)B * Hq * max_runs * HD;
+    float* part_l = part_m + (size_t)B * Hq * max_runs;
+    dim3 grid(max_runs, Hkv * chunks, B);
+    attn_mma_decode_kernel<HD><<<grid, AM_WARPS * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
+        page_table, seq_len, part_acc, part_m, part_l, (bf16*)out, Hq, Hkv, table_width, scale, window, split_tokens, max_runs,
+        Gc, chunks);
+    if (int rc = qwb_check_launch("attn_mma_decode")) return rc;
+    if (max_runs > 1) {
+        attn_mma_combine_kernel<<<dim3(Hq, B), 128, 0, stream>>>(part_acc, part_m, part_l, seq_len, (bf16*)out, Hq, HD, window,
+                                                                 split_tokens, max_runs);
+        return qwb_check_launch("attn_mma_combine");
+    }
+    return 0;
+}
+
+// bfloat16 only.  Arguments as qwb_attn_decode (scratch of the same size).
+extern "C" int qwb_attn_mma_decode(const void* q, const void* k_pool, const void* v_pool, const int* page_table,
+                                   const int* seq_len, float* scratch, void* out, int B, int Hq, int Hkv, int hd, int page_size,
+                                   int table_width, float scale, int window, int split_tokens, int max_runs, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (int rc = check_sizes("attn_mma_decode", Hq, Hkv, hd, page_size, B)) return rc;
+    if (split_tokens <= 0 || split_tokens % AM_TILE || max_runs <= 0)
+        return qwb_fail(QWB_ERR_ARG, "attn_mma_decode: run of %d keys is not a multiple of %d, or %d runs", split_tokens, AM_TILE, max_runs);
+    if (max_runs > 1 && !scratch) return qwb_fail(QWB_ERR_ARG, "attn_mma_decode: %d runs need scratch memory", max_runs);
+    if (hd == 64) return launch_decode<64>(q, k_pool, v_pool, page_table, seq_len, scratch, out, B, Hq, Hkv, table_width, scale, window, split_tokens, max_runs, stream);
+    return launch_decode<128>(q, k_pool, v_pool, page_table, seq_len, scratch, out, B, Hq, Hkv, table_width, scale, window, split_tokens, max_runs, stream);
+}

@@ -1,0 +1,113 @@
+// Weight-streaming matrix product on the tensor cores, for up to 64 rows of bfloat16 x:
+//     y[M,N] = x[M,K] W[N,K]^T (+ residual),  32-bit sums, y float.
+// A decode step reads every weight once and does little arithmetic per byte, so the only
+// goal is to keep HBM busy: each block owns 16 rows of W, its 8 warps split K between
+// them, every thread pulls its part of W straight from global memory into registers with
+// 16-byte loads that bypass L1 (W is used once; x stays cached), and feeds
+// mma.m16n8k16 with W as the 16-row operand and 8 rows of x as the 8-column operand
+// (y^T = W x^T).  A 16-byte load gives a thread eight consecutive k of one row; the
+// instruction wants pairs (2t, 2t+1) and (2t+8, 2t+9).  The sum over k does not care about
+// the order, so both operands use the same renumbering of k inside each block of 32 and
+// no shuffle is needed.  The warps' partial sums meet in shared memory and are added in
+// warp order, so a row's result depends neither on the batch nor on timing.
+// (The reference's counterpart for few rows: ggml-cuda/mmvf.cu and mmf.cuh.)
+#include "common.cuh"
+
+#define GS_WARPS 8
+#define GS_ROWS 16
+
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void mma_bf16_16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// NT = number of 8-row tiles of x handled at once (M <= 8 * NT).
+template <int NT>
+__global__ void __launch_bounds__(GS_WARPS * 32)
+gemm_stream_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const float* residual, float* y,
+                   int M, int N, int K) {
+    __shared__ float part[GS_WARPS][NT][4][32];          // [warp][tile][c register][lane]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * GS_ROWS;
+    const int chunks = K >> 3;                            // 16-byte chunks per row
+    const int blocks = (chunks + 3) >> 2;                 // blocks of 32 k
+    const int per_warp = (blocks + GS_WARPS - 1) / GS_WARPS;
+    const int kb0 = warp * per_warp, kb1 = min(blocks, kb0 + per_warp);
+
+    const int r_lo = n0 + g, r_hi = n0 + g + 8;
+    const uint4* w_lo = reinterpret_cast<const uint4*>(W + (size_t)min(r_lo, N - 1) * K);
+    const uint4* w_hi = reinterpret_cast<const uint4*>(W + (size_t)min(r_hi, N - 1) * K);
+    const uint4* xr[NT];
+    bool x_ok[NT];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        const int m = 8 * j + g;
+        x_ok[j] = m < M;
+        xr[j] = reinterpret_cast<const uint4*>(x + (size_t)min(m, M - 1) * K);
+    }
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll 4
+    for (int kb = kb0; kb < kb1; ++kb) {
+        const int c = kb * 4 + t;
+        const bool in = c < chunks;
+        const uint4 lo = in ? ld_stream16(w_lo + c) : zero;
+        const uint4 hi = in ? ld_stream16(w_hi + c) : zero;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            const uint4 xv = (in && x_ok[j]) ? __ldg(xr[j] + c) : zero;
+            mma_bf16_16816(acc[j], lo.x, hi.x, lo.y, hi.y, xv.x, xv.y);
+            mma_bf16_16816(acc[j], lo.z, hi.z, lo.w, hi.w, xv.z, xv.w);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) part[warp][j][r][lane] = acc[j][r];
+    __syncthreads();
+
+    // c0: (row g, col 2t), c1: (row g, col 2t+1), c2: (row g+8, col 2t), c3: (row g+8, col 2t+1);
+    // rows are rows of W (outputs n), columns are rows of x (m).
+    for (int idx = threadIdx.x; idx < NT * 4 * 32; idx += blockDim.x) {
+        const int j = idx >> 7, r = (idx >> 5) & 3, ln = idx & 31;
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < GS_WARPS; ++w) s += part[w][j][r][ln];
+        const int gg = ln >> 2, tt = ln & 3;
+        const int n = n0 + gg + ((r & 2) ? 8 : 0);
+        const int m = 8 * j + 2 * tt + (r & 1);
+        if (n < N && m < M) {
+            const size_t at = (size_t)m * N + n;
+            y[at] = residual ? residual[at] + s : s;
+        }
+    }
+}
+
+extern "C" int qwb_gemm_stream(const void* x, const void* W, const float* residual, float* y, int M, int N, int K,
+                               cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8) return qwb_fail(QWB_ERR_ARG, "gemm_stream: inner size %d is not a multiple of 8", K);
+    if (M > 64) return qwb_fail(QWB_ERR_ARG, "gemm_stream: %d rows; this kernel is for at most 64", M);
+    if ((uintptr_t)x % 16 || (uintptr_t)W % 16) return qwb_fail(QWB_ERR_ARG, "gemm_stream: operands must be 16-byte aligned");
+    const int grid = (N + GS_ROWS - 1) / GS_ROWS;
+    const bf16* xp = (const bf16*)x;
+    const bf16* wp = (const bf16*)W;
+    if (M <= 8) gemm_stream_kernel<1><<<grid, GS_WARPS * 32, 0, stream>>>(xp, wp, residual, y, M, N, K);
+    else if (M <= 16) gemm_stream_kernel<2><<<grid, GS_WARPS * 32, 0, stream>>>(xp, wp, residual, y, M, N, K);
+    else if (M <= 32) gemm_stream_kernel<4><<<grid, GS_WARPS * 32, 0, stream>>>(xp, wp, residual, y, M, N, K);
+    else gemm_stream_kernel<8><<<grid, GS_WARPS * 32, 0, stream>>>(xp, wp, residual, y, M, N, K);
+    return qwb_check_launch("gemm_stream");
+}

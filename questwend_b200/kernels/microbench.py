@@ -1,0 +1,153 @@
+"""Times one kernel of the library at a given size with CUDA events.
+
+    python -m questwend_b200.kernels.microbench gemm --m 8 --n 24576 --k 4096 [--impl stream|small|library]
+    python -m questwend_b200.kernels.microbench attn_decode --batch 8 --ctx 1152 [--heads 32 --kv-heads 8 --head-dim 128]
+    python -m questwend_b200.kernels.microbench attn_prefill --tokens 2048
+    python -m questwend_b200.kernels.microbench rmsnorm --m 8 --k 4096
+    python -m questwend_b200.kernels.microbench decode_shapes --m 8        (every product of a Qwen3-8B decode step)
+
+Inputs rotate through enough copies to exceed the 126 MB L2, so every timed launch reads from HBM.
+Prints one JSON line per case: microseconds (median of the timed launches), the bytes the kernel has to
+move, and GB/s.  Also the program to put under ncu for a capture of one kernel on a small case.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import statistics
+
+import torch
+
+from . import ops
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def _time(fn, n_variants: int, iters: int, warmup: int = 3, burst: int = 10) -> float:
+    """Median microseconds per launch; each timed region holds `burst` launches back to back, so that
+    the host's launch overhead does not hide a kernel of a few microseconds."""
+    for i in range(warmup):
+        fn(i % n_variants)
+    torch.cuda.synchronize()
+    burst = max(burst, n_variants)
+    graph = torch.cuda.CUDAGraph()          # the burst is replayed from a graph: no host time between launches
+    with torch.cuda.graph(graph):
+        for k in range(burst):
+            fn(k % n_variants)
+    graph.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) * 1e3 / burst)
+    return statistics.median(times)
+
+
+def bench_gemm(M: int, N: int, K: int, impl: str, iters: int, dtype=torch.bfloat16) -> dict:
+    elem = 2 if dtype == torch.bfloat16 else 4
+    copies = max(2, math.ceil(2 * L2_BYTES / (N * K * elem)))
+    ws = [torch.randn(N, K, device="cuda", dtype=torch.float32).mul_(0.02).to(dtype) for _ in range(copies)]
+    x = torch.randn(M, K, device="cuda").to(dtype)
+    if impl == "stream":
+        fn = lambda i: ops.gemm_stream(x, ws[i])
+    elif impl == "small":
+        fn = lambda i: ops.gemm_small(x, ws[i])
+    elif impl == "tc":
+        fn = lambda i: ops.gemm_tc(x, ws[i])
+    else:
+        fn = (lambda i: torch.mm(x, ws[i].t(), out_dtype=torch.float32)) if dtype == torch.bfloat16 else \
+             (lambda i: torch.mm(x, ws[i].t()))
+    us = _time(fn, copies, iters)
+    nbytes = N * K * elem + M * K * elem + M * N * 4
+    return {"kernel": f"gemm_{impl}", "M": M, "N": N, "K": K, "us": us, "bytes": nbytes,
+            "GBps": nbytes / us / 1e3, "TFLOPs": 2.0 * M * N * K / us / 1e6}
+
+
+def bench_attn_decode(B, ctx, Hq, Hkv, hd, iters, dtype=torch.bfloat16, split=256) -> dict:
+    page = ops.PAGE_SIZE
+    pages_per = math.ceil(ctx / page)
+    per_copy = B * pages_per
+    elem = 2 if dtype == torch.bfloat16 else 4
+    copy_bytes = 2 * per_copy * Hkv * page * hd * elem
+    copies = max(2, math.ceil(2 * L2_BYTES / copy_bytes))
+    n_pages = per_copy * copies
+    k_pool = torch.randn(n_pages, Hkv, page, hd, device="cuda").to(dtype)
+    v_pool = torch.randn(n_pages, Hkv, page, hd, device="cuda").to(dtype)
+    tables = [(torch.arange(per_copy, dtype=torch.int32, device="cuda") + c * per_copy).reshape(B, pages_per).contiguous()
+              for c in range(copies)]
+    q = torch.randn(B, Hq, hd, device="cuda").to(dtype)
+    seq_len = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+    fn = lambda i: ops.attn_decode(q, k_pool, v_pool, tables[i], seq_len, 1 / math.sqrt(hd), ctx, split_tokens=split)
+    us = _time(fn, copies, iters)
+    nbytes = 2 * B * ctx * Hkv * hd * elem
+    return {"kernel": "attn_decode", "B": B, "ctx": ctx, "Hq": Hq, "Hkv": Hkv, "hd": hd, "us": us, "bytes": nbytes,
+            "GBps": nbytes / us / 1e3}
+
+
+def bench_attn_prefill(T, Hq, Hkv, hd, iters, dtype=torch.bfloat16) -> dict:
+    page = ops.PAGE_SIZE
+    n_pages = math.ceil(T / page)
+    k_pool = torch.randn(n_pages, Hkv, page, hd, device="cuda").to(dtype)
+    v_pool = torch.randn(n_pages, Hkv, page, hd, device="cuda").to(dtype)
+    table = torch.arange(n_pages, dtype=torch.int32, device="cuda").reshape(1, n_pages)
+    q = torch.randn(T, Hq, hd, device="cuda").to(dtype)
+    cu = torch.tensor([0, T], dtype=torch.int32, device="cuda")
+    pos0 = torch.zeros(1, dtype=torch.int32, device="cuda")
+    fn = lambda i: ops.attn_prefill(q, k_pool, v_pool, table, cu, pos0, T, 1 / math.sqrt(hd))
+    us = _time(fn, 1, iters)
+    flops = 4.0 * Hq * hd * T * (T + 1) / 2
+    return {"kernel": "attn_prefill", "T": T, "Hq": Hq, "Hkv": Hkv, "hd": hd, "us": us, "TFLOPs": flops / us / 1e6}
+
+
+def bench_rmsnorm(M, K, iters) -> dict:
+    copies = max(2, math.ceil(2 * L2_BYTES / (M * K * 4)))
+    copies = min(copies, 64)
+    xs = [torch.randn(M, K, device="cuda") for _ in range(copies)]
+    d = torch.randn(M, K, device="cuda")
+    w = torch.ones(K, device="cuda")
+    fn = lambda i: ops.rmsnorm(xs[i], w, 1e-6, torch.bfloat16, delta=d, write_sum=True)
+    us = _time(fn, copies, iters)
+    return {"kernel": "rmsnorm", "M": M, "K": K, "us": us}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "attn_decode", "attn_prefill", "rmsnorm", "decode_shapes"])
+    ap.add_argument("--m", type=int, default=8)
+    ap.add_argument("--n", type=int, default=24576)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--impl", default="stream", choices=["stream", "small", "library", "tc"])
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--ctx", type=int, default=1152)
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--iters", type=int, default=20)
+    args = ap.parse_args()
+    dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
+    if args.what == "gemm":
+        print(json.dumps(bench_gemm(args.m, args.n, args.k, args.impl, args.iters, dtype)))
+    elif args.what == "decode_shapes":
+        for name, n, k in (("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 24576, 4096), ("down", 4096, 12288),
+                           ("lm_head", 151936, 4096)):
+            r = bench_gemm(args.m, n, k, args.impl, args.iters, dtype)
+            r["name"] = name
+            print(json.dumps(r))
+    elif args.what == "attn_decode":
+        print(json.dumps(bench_attn_decode(args.batch, args.ctx, args.heads, args.kv_heads, args.head_dim, args.iters, dtype)))
+    elif args.what == "attn_prefill":
+        print(json.dumps(bench_attn_prefill(args.tokens, args.heads, args.kv_heads, args.head_dim, args.iters, dtype)))
+    else:
+        print(json.dumps(bench_rmsnorm(args.m, args.k, args.iters)))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

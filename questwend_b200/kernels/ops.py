@@ -173,9 +173,15 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_weight, k_weight, cos, sin, tok_seq,
 
 
 # ----------------------------------------------------------------------------- attention
+def mma_attention_fits(dtype: torch.dtype, head_dim: int, page_size: int) -> bool:
+    """Whether the tensor-core attention kernels take this case (else the plain ones do)."""
+    return dtype == torch.bfloat16 and head_dim in (64, 128) and page_size == 64
+
+
 def attn_prefill(q, k_pool, v_pool, page_table, cu_seqlens, pos0, max_new: int, scale: float,
-                 window: int = 0) -> torch.Tensor:
-    """Causal attention of new tokens over the cache.  q [T, Hq, hd]; returns [T, Hq * hd]."""
+                 window: int = 0, impl: str = "auto") -> torch.Tensor:
+    """Causal attention of new tokens over the cache.  q [T, Hq, hd]; returns [T, Hq * hd].
+    impl: "auto" (tensor cores where they fit), "mma", or "plain"."""
     _need(q, "q", k_pool.dtype, 3)
     _need(k_pool, "k_pool", ndim=4)
     _need(v_pool, "v_pool", k_pool.dtype, 4)
@@ -187,6 +193,14 @@ def attn_prefill(q, k_pool, v_pool, page_table, cu_seqlens, pos0, max_new: int, 
     if cu_seqlens.numel() != B + 1 or page_table.shape[0] < B:
         raise KernelError("attn_prefill: cu_seqlens / page_table do not fit the batch")
     out = torch.empty((T, Hq * hd), dtype=q.dtype, device=q.device)
+    use_mma = impl == "mma" or (impl == "auto" and mma_attention_fits(q.dtype, hd, k_pool.shape[2]))
+    if use_mma:
+        if q.dtype != torch.bfloat16:
+            raise KernelError("attn_prefill: the tensor-core kernel takes bfloat16 only")
+        _call("attention_mma", "qwb_attn_mma_prefill", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table),
+              _ptr(cu_seqlens), _ptr(pos0), _ptr(out), _i(B), _i(max_new), _i(Hq), _i(k_pool.shape[1]), _i(hd),
+              _i(k_pool.shape[2]), _i(page_table.shape[1]), _f(scale), _i(window), _stream())
+        return out
     _call("attention", "qwb_attn_prefill", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _ptr(cu_seqlens),
           _ptr(pos0), _ptr(out), _i(_dt(q.dtype)), _i(B), _i(max_new), _i(Hq), _i(k_pool.shape[1]), _i(hd),
           _i(k_pool.shape[2]), _i(page_table.shape[1]), _f(scale), _i(window), _stream())
@@ -198,7 +212,7 @@ def attn_decode_scratch_floats(B: int, Hq: int, hd: int, max_runs: int) -> int:
 
 
 def attn_decode(q, k_pool, v_pool, page_table, seq_len, scale: float, max_len: int, window: int = 0,
-                split_tokens: int = 256, scratch: torch.Tensor | None = None) -> torch.Tensor:
+                split_tokens: int = 256, scratch: torch.Tensor | None = None, impl: str = "auto") -> torch.Tensor:
     """Attention of one new token per sequence over the cache.  q [B, Hq, hd]; ``seq_len`` counts
     the new token; ``max_len`` bounds every entry of ``seq_len``.  Returns [B, Hq * hd]."""
     _need(q, "q", k_pool.dtype, 3)
@@ -214,6 +228,15 @@ def attn_decode(q, k_pool, v_pool, page_table, seq_len, scale: float, max_len: i
     if scratch is not None:
         _need(scratch, "scratch", torch.float32)
     out = torch.empty((B, Hq * hd), dtype=q.dtype, device=q.device)
+    use_mma = impl == "mma" or (impl == "auto" and mma_attention_fits(q.dtype, hd, k_pool.shape[2]))
+    if use_mma:
+        if q.dtype != torch.bfloat16:
+            raise KernelError("attn_decode: the tensor-core kernel takes bfloat16 only")
+        _call("attention_mma", "qwb_attn_mma_decode", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table),
+              _ptr(seq_len), _ptr(scratch), _ptr(out), _i(B), _i(Hq), _i(k_pool.shape[1]), _i(hd), _i(k_pool.shape[2]),
+              _i(page_table.shape[1]), _f(scale), _i(window), _i(split_tokens), _i(max_runs), _stream(),
+              kernels=2 if max_runs > 1 else 1)
+        return out
     _call("attention", "qwb_attn_decode", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _ptr(seq_len),
           _ptr(scratch), _ptr(out), _i(_dt(q.dtype)), _i(B), _i(Hq), _i(k_pool.shape[1]), _i(hd),
           _i(k_pool.shape[2]), _i(page_table.shape[1]), _f(scale), _i(window), _i(split_tokens), _i(max_runs),
@@ -241,6 +264,29 @@ def gemm_small(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor | N
         _need(residual, "residual", torch.float32, 2)
     _call("gemm_small", "qwb_gemm_small", _ptr(x), _ptr(weight), _ptr(residual), _ptr(out), _i(_dt(x.dtype)),
           _i(M), _i(N), _i(K), _stream(), kernels=(M + 7) // 8)
+    return out
+
+
+STREAM_M = 16           # at most this many bfloat16 rows go to the tensor-core weight-streaming kernel
+                        # (it takes up to 64, but beyond 16 the library product is faster)
+
+
+def gemm_stream(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor | None = None,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+    """bfloat16 x [M, K] times bfloat16 weight [N, K] transposed, as float32 [M, N] (+ residual), M <= 64."""
+    _need(x, "x", torch.bfloat16, 2)
+    _need(weight, "weight", torch.bfloat16, 2)
+    M, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K:
+        raise KernelError(f"gemm_stream: x has {K} columns, the weight {weight.shape[1]}")
+    if out is None:
+        out = residual if residual is not None else torch.empty((M, N), dtype=torch.float32, device=x.device)
+    _need(out, "out", torch.float32, 2)
+    if residual is not None:
+        _need(residual, "residual", torch.float32, 2)
+    _call("gemm_stream", "qwb_gemm_stream", _ptr(x), _ptr(weight), _ptr(residual), _ptr(out), _i(M), _i(N), _i(K),
+          _stream())
     return out
 
 

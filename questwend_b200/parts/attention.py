@@ -64,7 +64,10 @@ class GroupedQueryAttention(Mixer):
             self.k_norm_w = weights[px + n["k_norm"]].to(torch.float32).contiguous()
 
     def kernel_modules(self):
-        return ("rope_kv", "attention", "gemm_small")
+        mods = ["rope_kv", "gemm_small", "gemm_stream"]
+        mods.append("attention_mma" if ops.mma_attention_fits(self.runtime.dtype, self.head_dim, ops.PAGE_SIZE)
+                    else "attention")
+        return tuple(mods)
 
     def kv_spec(self):
         return KVSpec(self.n_kv_heads, self.head_dim, self.window)

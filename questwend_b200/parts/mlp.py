@@ -34,7 +34,7 @@ class GatedMLP(FeedForward):
         self.w_down = weights[px + n["down"]]
 
     def kernel_modules(self):
-        return ("elementwise", "gemm_small")
+        return ("elementwise", "gemm_small", "gemm_stream")
 
     def forward(self, x, ctx):
         gate_up = linear(x, self.w_gate_up)

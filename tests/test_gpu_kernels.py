@@ -186,6 +186,16 @@ def rounded(arrs, dtype):
 @pytest.mark.parametrize("Hq,Hkv,hd", ATTN_SHAPES)
 @pytest.mark.parametrize("window", [0, 37])
 def test_attn_prefill(dtype, Hq, Hkv, hd, window):
+    _attn_prefill_case(dtype, Hq, Hkv, hd, window, "plain")
+
+
+@pytest.mark.parametrize("Hq,Hkv,hd", [(8, 2, 64), (8, 1, 128), (4, 4, 128), (12, 1, 64), (32, 1, 128), (6, 2, 128)])
+@pytest.mark.parametrize("window", [0, 37])
+def test_attn_prefill_tensor_cores(Hq, Hkv, hd, window):
+    _attn_prefill_case(torch.bfloat16, Hq, Hkv, hd, window, "mma")
+
+
+def _attn_prefill_case(dtype, Hq, Hkv, hd, window, impl):
     lens = [1, 17, 70, 150, 64]
     new = [1, 17, 33, 22, 64]                       # the last `new` tokens of each sequence are this step's
     q, k, v = (rounded(a, dtype) for a in make_qkv(lens, Hq, Hkv, hd, hd + Hq))
@@ -194,7 +204,7 @@ def test_attn_prefill(dtype, Hq, Hkv, hd, window):
     q_new = torch.cat([torch.as_tensor(qq[n - m:]) for qq, n, m in zip(q, lens, new)]).to(dtype).to(DEV)
     cu = torch.tensor(np.cumsum([0] + new), dtype=torch.int32, device=DEV)
     pos0 = torch.tensor([n - m for n, m in zip(lens, new)], dtype=torch.int32, device=DEV)
-    out = ops.attn_prefill(q_new, k_pool, v_pool, table, cu, pos0, max(new), 1 / math.sqrt(hd), window=window)
+    out = ops.attn_prefill(q_new, k_pool, v_pool, table, cu, pos0, max(new), 1 / math.sqrt(hd), window=window, impl=impl)
     ref = np.concatenate([pm.attention_causal(qq, kk, vv, window=window or None)[n - m:].reshape(m, Hq * hd)
                           for qq, kk, vv, n, m in zip(q, k, v, lens, new)])
     close(out, ref, dtype)
@@ -205,6 +215,16 @@ def test_attn_prefill(dtype, Hq, Hkv, hd, window):
 @pytest.mark.parametrize("window,split,page", [(0, 128, 64), (100, 64, 64), (0, 256, 64), (0, 128, 32), (50, 64, 16),
                                                (0, 128, 128)])
 def test_attn_decode(dtype, Hq, Hkv, hd, window, split, page):
+    _attn_decode_case(dtype, Hq, Hkv, hd, window, split, page, "plain")
+
+
+@pytest.mark.parametrize("Hq,Hkv,hd", [(8, 2, 64), (8, 1, 128), (4, 4, 128), (12, 1, 64), (32, 1, 128), (6, 2, 128)])
+@pytest.mark.parametrize("window,split", [(0, 128), (100, 64), (0, 256), (0, 512), (300, 256)])
+def test_attn_decode_tensor_cores(Hq, Hkv, hd, window, split):
+    _attn_decode_case(torch.bfloat16, Hq, Hkv, hd, window, split, 64, "mma")
+
+
+def _attn_decode_case(dtype, Hq, Hkv, hd, window, split, page, impl):
     if page == 128 and hd == 256 and dtype == torch.float32:
         pytest.skip("refused: see test_attention_refusals")
     lens = [1, 64, 65, 300, 129, 700]
@@ -214,17 +234,17 @@ def test_attn_decode(dtype, Hq, Hkv, hd, window, split, page):
     q_last = torch.stack([torch.as_tensor(qq[-1]) for qq in q]).to(dtype).to(DEV)
     seq_len = torch.tensor(lens, dtype=torch.int32, device=DEV)
     out = ops.attn_decode(q_last, k_pool, v_pool, table, seq_len, 1 / math.sqrt(hd), max(lens), window=window,
-                          split_tokens=split)
+                          split_tokens=split, impl=impl)
     ref = np.stack([pm.attention_causal(qq, kk, vv, window=window or None)[-1].reshape(Hq * hd)
                     for qq, kk, vv in zip(q, k, v)])
     close(out, ref, dtype)
     # more runs than the longest sequence needs (a graph's bucket) change nothing
     again = ops.attn_decode(q_last, k_pool, v_pool, table, seq_len, 1 / math.sqrt(hd), max(lens) + 3 * split,
-                            window=window, split_tokens=split)
+                            window=window, split_tokens=split, impl=impl)
     assert torch.equal(out, again)
     # a sequence's result does not depend on the rest of the batch
     alone = ops.attn_decode(q_last[3:4], k_pool, v_pool, table[3:4], seq_len[3:4], 1 / math.sqrt(hd), lens[3],
-                            window=window, split_tokens=split)
+                            window=window, split_tokens=split, impl=impl)
     assert torch.equal(alone[0], out[3])
 
 
@@ -316,6 +336,23 @@ def test_gemm_small(dtype, M, N, K):
     close(ops.gemm_small(x, w, residual=res.clone()), want, torch.float32, scale=np.abs(want).max() * 4)
     # a row's result does not depend on how many rows come with it
     assert torch.equal(ops.gemm_small(x[:1], w)[0], out[0])
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 17, 33, 64])
+@pytest.mark.parametrize("N,K", [(37, 96), (200, 200), (16, 4104), (129, 1024)])
+def test_gemm_stream(M, N, K):
+    g = torch.Generator().manual_seed(M * 1000 + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(N, K, generator=g).to(torch.bfloat16).to(DEV)
+    ref = f64(x) @ f64(w).T
+    out = ops.gemm_stream(x, w)
+    close(out, ref, torch.float32, scale=np.abs(ref).max() * 4)          # 32-bit sums of exact products
+    res = torch.randn(M, N, generator=g).to(DEV)
+    want = f64(res) + ref
+    close(ops.gemm_stream(x, w, residual=res.clone()), want, torch.float32, scale=np.abs(want).max() * 4)
+    assert torch.equal(ops.gemm_stream(x[:1], w)[0], out[0])             # a row does not depend on the others
+    with pytest.raises(KernelError, match="multiple of 8"):
+        ops.gemm_stream(x[:, :K - 4].contiguous(), w[:, :K - 4].contiguous())
 
 
 # ----------------------------------------------------------------------------- sampling

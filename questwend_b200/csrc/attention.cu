@@ -27,6 +27,8 @@ __global__ void attn_prefill_kernel(const T* __restrict__ q, const T* __restrict
                                     const int* __restrict__ page_table, const int* __restrict__ cu_seqlens,
                                     const int* __restrict__ pos0, T* __restrict__ out, int Hq, int Hkv, int hd,
                                     int page_size, int table_width, float scale, int window) {
+    pdl_wait();
+    pdl_launch_dependents();
     constexpr int BQ = 16, BK = 32, QPW = 4;
     extern __shared__ float smem[];
     float* Qs = smem;                         // [BQ][hd], already scaled
@@ -143,7 +145,7 @@ static int launch_prefill(const void* q, const void* k_pool, const void* v_pool,
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
             if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "attn_prefill: %s", cudaGetErrorString(e));      \
         }                                                                                                        \
-        attn_prefill_kernel<T, NC><<<grid, 128, smem, stream>>>((const T*)q, (const T*)k_pool, (const T*)v_pool, \
+        qwb_launch(attn_prefill_kernel<T, NC>, grid, 128, smem, stream, (const T*)q, (const T*)k_pool, (const T*)v_pool, \
             page_table, cu_seqlens, pos0, (T*)out, Hq, Hkv, hd, page_size, table_width, scale, window);          \
     } while (0)
     if (nc <= 2) QWB_LAUNCH_PREFILL(2);
@@ -198,6 +200,8 @@ __global__ void attn_decode_split_kernel(const T* __restrict__ q, const T* __res
                                          float* __restrict__ part_acc, float* __restrict__ part_m, float* __restrict__ part_l,
                                          T* __restrict__ out, int Hq, int Hkv, int hd, int page_size, int table_width,
                                          float scale, int window, int split_tokens, int max_runs) {
+    pdl_wait();
+    pdl_launch_dependents();
     constexpr int GT = QWB_DECODE_GT, VEC = Vec16<T>::N;
     const int b = blockIdx.z, run = blockIdx.x;
     const int len = seq_len[b];
@@ -346,6 +350,8 @@ template <typename T>
 __global__ void attn_decode_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_m,
                                            const float* __restrict__ part_l, const int* __restrict__ seq_len,
                                            T* __restrict__ out, int Hq, int hd, int window, int split_tokens, int max_runs) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int h = blockIdx.x, b = blockIdx.y;
     int run_first, run_end;
     decode_run_range(seq_len[b], window, split_tokens, &run_first, &run_end);
@@ -385,11 +391,11 @@ static int launch_decode(const void* q, const void* k_pool, const void* v_pool, 
     float* part_l = part_m + (size_t)B * Hq * max_runs;
     const int G = Hq / Hkv, slices = (G + GT - 1) / GT;
     dim3 grid(max_runs, Hkv * slices, B);
-    attn_decode_split_kernel<T><<<grid, 128, smem, stream>>>((const T*)q, (const T*)k_pool, (const T*)v_pool, page_table,
+    qwb_launch(attn_decode_split_kernel<T>, grid, 128, smem, stream, (const T*)q, (const T*)k_pool, (const T*)v_pool, page_table,
         seq_len, part_acc, part_m, part_l, (T*)out, Hq, Hkv, hd, page_size, table_width, scale, window, split_tokens, max_runs);
     if (int rc = qwb_check_launch("attn_decode_split")) return rc;
     if (max_runs > 1) {
-        attn_decode_combine_kernel<T><<<dim3(Hq, B), 128, 0, stream>>>(part_acc, part_m, part_l, seq_len, (T*)out, Hq, hd,
+        qwb_launch(attn_decode_combine_kernel<T>, dim3(Hq, B), 128, 0, stream, part_acc, part_m, part_l, seq_len, (T*)out, Hq, hd,
                                                                      window, split_tokens, max_runs);
         return qwb_check_launch("attn_decode_combine");
     }

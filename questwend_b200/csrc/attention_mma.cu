@@ -168,6 +168,8 @@ __global__ void __launch_bounds__(AM_WARPS * 32)
 attn_mma_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                         const int* __restrict__ page_table, const int* __restrict__ cu_seqlens, const int* __restrict__ pos0,
                         bf16* __restrict__ out, int Hq, int Hkv, int table_width, float scale, int window, int Gc, int chunks) {
+    pdl_wait();
+    pdl_launch_dependents();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* tiles = reinterpret_cast<bf16*>(smem_raw);                 // [2 buffers][K, V][64][HD]
     const int b = blockIdx.z;
@@ -253,6 +255,8 @@ attn_mma_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
                        const int* __restrict__ page_table, const int* __restrict__ seq_len, float* __restrict__ part_acc,
                        float* __restrict__ part_m, float* __restrict__ part_l, bf16* __restrict__ out, int Hq, int Hkv,
                        int table_width, float scale, int window, int split_tokens, int max_runs, int Gc, int chunks) {
+    pdl_wait();
+    pdl_launch_dependents();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int b = blockIdx.z, run = blockIdx.x;
     const int len = seq_len[b];
@@ -341,6 +345,8 @@ attn_mma_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
 __global__ void attn_mma_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_m,
                                         const float* __restrict__ part_l, const int* __restrict__ seq_len,
                                         bf16* __restrict__ out, int Hq, int hd, int window, int split_tokens, int max_runs) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int h = blockIdx.x, b = blockIdx.y;
     const int len = seq_len[b];
     const int k_lo = window > 0 ? max(0, len - window) : 0;
@@ -370,7 +376,7 @@ static int launch_prefill(const void* q, const void* k_pool, const void* v_pool,
     cudaError_t e = cudaFuncSetAttribute(attn_mma_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "attn_mma_prefill: %s", cudaGetErrorString(e));
     dim3 grid((max_new + tok_per_block - 1) / tok_per_block, Hkv * chunks, B);
-    attn_mma_prefill_kernel<HD><<<grid, AM_WARPS * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
+    qwb_launch(attn_mma_prefill_kernel<HD>, grid, AM_WARPS * 32, smem, stream, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
         page_table, cu_seqlens, pos0, (bf16*)out, Hq, Hkv, table_width, scale, window, Gc, chunks);
     return qwb_check_launch("attn_mma_prefill");
 }
@@ -407,12 +413,12 @@ static int launch_decode(const void* q, const void* k_pool, const void* v_pool, 
     float* part_m = scratch + (size_t)B * Hq * max_runs * HD;
     float* part_l = part_m + (size_t)B * Hq * max_runs;
     dim3 grid(max_runs, Hkv * chunks, B);
-    attn_mma_decode_kernel<HD><<<grid, AM_WARPS * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
+    qwb_launch(attn_mma_decode_kernel<HD>, grid, AM_WARPS * 32, smem, stream, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
         page_table, seq_len, part_acc, part_m, part_l, (bf16*)out, Hq, Hkv, table_width, scale, window, split_tokens, max_runs,
         Gc, chunks);
     if (int rc = qwb_check_launch("attn_mma_decode")) return rc;
     if (max_runs > 1) {
-        attn_mma_combine_kernel<<<dim3(Hq, B), 128, 0, stream>>>(part_acc, part_m, part_l, seq_len, (bf16*)out, Hq, HD, window,
+        qwb_launch(attn_mma_combine_kernel, dim3(Hq, B), 128, 0, stream, part_acc, part_m, part_l, seq_len, (bf16*)out, Hq, HD, window,
                                                                  split_tokens, max_runs);
         return qwb_check_launch("attn_mma_combine");
     }

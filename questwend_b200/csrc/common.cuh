@@ -9,6 +9,7 @@
 #include <stdarg.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #define QWB_DT_F32 0
 #define QWB_DT_BF16 1
@@ -35,6 +36,40 @@ static int qwb_check_launch(const char* what) {
 }
 
 typedef __nv_bfloat16 bf16;
+
+// Programmatic dependent launch.  Every kernel of this library is launched with the
+// programmatic-serialization attribute and begins with pdl_wait(): the kernel may be
+// scheduled while its predecessor in the stream is still draining, and waits here until the
+// predecessor has finished and its writes are visible.  What a kernel does before pdl_wait()
+// must not depend on the predecessor (weights may be prefetched, nothing may be written).
+// pdl_launch_dependents() lets the successor be scheduled early in the same way.  (The
+// reference's CUDA back end has the same hooks, ggml-cuda/common.cuh:123-129.)
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static bool qwb_pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("QWB200_NO_PDL");
+        on = (e && e[0] && e[0] != '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static cudaError_t qwb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = qwb_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(bf16 x) { return __bfloat162float(x); }

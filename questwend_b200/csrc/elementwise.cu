@@ -10,6 +10,8 @@
 template <typename T>
 __global__ void embed_gather_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                     float* __restrict__ out, int D, int V, int* bad_token) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * D;
@@ -28,9 +30,9 @@ extern "C" int qwb_embed_gather(const int* ids, const void* table, int table_dty
     if (D <= 0 || V <= 0) return qwb_fail(QWB_ERR_ARG, "embed_gather: bad sizes D=%d V=%d", D, V);
     const int block = D >= 1024 ? 256 : 128;
     if (table_dtype == QWB_DT_F32)
-        embed_gather_kernel<float><<<T, block, 0, stream>>>(ids, (const float*)table, out, D, V, bad_token);
+        qwb_launch(embed_gather_kernel<float>, T, block, 0, stream, ids, (const float*)table, out, D, V, bad_token);
     else if (table_dtype == QWB_DT_BF16)
-        embed_gather_kernel<bf16><<<T, block, 0, stream>>>(ids, (const bf16*)table, out, D, V, bad_token);
+        qwb_launch(embed_gather_kernel<bf16>, T, block, 0, stream, ids, (const bf16*)table, out, D, V, bad_token);
     else
         return qwb_fail(QWB_ERR_ARG, "embed_gather: unknown dtype %d", table_dtype);
     return qwb_check_launch("embed_gather");
@@ -50,6 +52,8 @@ template <typename TOut>
 __global__ void rmsnorm_kernel(const float* x, const float* __restrict__ delta,
                                float* sum_out, const float* __restrict__ w, TOut* __restrict__ out,
                                const int* __restrict__ rows, int D, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
     extern __shared__ float row_cache[];
     __shared__ float red[32];
     const int r = blockIdx.x;
@@ -80,11 +84,11 @@ extern "C" int qwb_rmsnorm(const float* x, const float* delta, float* sum_out, c
     if (out_dtype == QWB_DT_F32) {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "rmsnorm: %s", cudaGetErrorString(e));
-        rmsnorm_kernel<float><<<n_rows, block, smem, stream>>>(x, delta, sum_out, w, (float*)out, rows, D, eps);
+        qwb_launch(rmsnorm_kernel<float>, n_rows, block, smem, stream, x, delta, sum_out, w, (float*)out, rows, D, eps);
     } else if (out_dtype == QWB_DT_BF16) {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "rmsnorm: %s", cudaGetErrorString(e));
-        rmsnorm_kernel<bf16><<<n_rows, block, smem, stream>>>(x, delta, sum_out, w, (bf16*)out, rows, D, eps);
+        qwb_launch(rmsnorm_kernel<bf16>, n_rows, block, smem, stream, x, delta, sum_out, w, (bf16*)out, rows, D, eps);
     } else {
         return qwb_fail(QWB_ERR_ARG, "rmsnorm: unknown dtype %d", out_dtype);
     }
@@ -98,6 +102,8 @@ extern "C" int qwb_rmsnorm(const float* x, const float* delta, float* sum_out, c
 // ---------------------------------------------------------------------------------
 template <typename TOut>
 __global__ void silu_mul_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int T, int F) {
+    pdl_wait();
+    pdl_launch_dependents();
     const size_t n = (size_t)T * F;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const size_t t = i / F, f = i - t * F;
@@ -114,9 +120,9 @@ extern "C" int qwb_silu_mul(const float* gate_up, void* out, int out_dtype, int 
     const int block = 256;
     const int grid = (int)((n + block - 1) / block < 148 * 16 ? (n + block - 1) / block : 148 * 16);
     if (out_dtype == QWB_DT_F32)
-        silu_mul_kernel<float><<<grid, block, 0, stream>>>(gate_up, (float*)out, T, F);
+        qwb_launch(silu_mul_kernel<float>, grid, block, 0, stream, gate_up, (float*)out, T, F);
     else if (out_dtype == QWB_DT_BF16)
-        silu_mul_kernel<bf16><<<grid, block, 0, stream>>>(gate_up, (bf16*)out, T, F);
+        qwb_launch(silu_mul_kernel<bf16>, grid, block, 0, stream, gate_up, (bf16*)out, T, F);
     else
         return qwb_fail(QWB_ERR_ARG, "silu_mul: unknown dtype %d", out_dtype);
     return qwb_check_launch("silu_mul");
@@ -124,6 +130,8 @@ extern "C" int qwb_silu_mul(const float* gate_up, void* out, int out_dtype, int 
 
 // out[i] += delta[i]: the residual sum on its own, for blocks that end without a norm.
 __global__ void add_inplace_kernel(float* __restrict__ out, const float* __restrict__ delta, size_t n) {
+    pdl_wait();
+    pdl_launch_dependents();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
         out[i] += delta[i];
 }
@@ -133,7 +141,7 @@ extern "C" int qwb_add_inplace(float* out, const float* delta, long long n, cuda
     const int block = 256;
     const long long want = (n + block - 1) / block;
     const int grid = (int)(want < 148 * 16 ? want : 148 * 16);
-    add_inplace_kernel<<<grid, block, 0, stream>>>(out, delta, (size_t)n);
+    qwb_launch(add_inplace_kernel, grid, block, 0, stream, out, delta, (size_t)n);
     return qwb_check_launch("add_inplace");
 }
 
@@ -143,6 +151,8 @@ extern "C" int qwb_add_inplace(float* out, const float* delta, long long n, cuda
 __global__ void decode_advance_kernel(const int* __restrict__ sampled, int* token_ids, int* tok_pos, int* pos0,
                                       int* seq_len, unsigned int* step_counter, int* recent, int* n_seen,
                                       int window, int B) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b == 0 && step_counter) *step_counter += 1;
     if (b >= B) return;
@@ -161,7 +171,7 @@ extern "C" int qwb_decode_advance(const int* sampled, int* token_ids, int* tok_p
                                   unsigned int* step_counter, int* recent, int* n_seen, int window, int B,
                                   cudaStream_t stream) {
     if (B <= 0) return 0;
-    decode_advance_kernel<<<(B + 127) / 128, 128, 0, stream>>>(sampled, token_ids, tok_pos, pos0, seq_len,
+    qwb_launch(decode_advance_kernel, (B + 127) / 128, 128, 0, stream, sampled, token_ids, tok_pos, pos0, seq_len,
                                                                step_counter, recent, n_seen, window, B);
     return qwb_check_launch("decode_advance");
 }

@@ -9,6 +9,8 @@
 template <typename T, int MT, bool VECTOR>
 __global__ void gemm_small_kernel(const T* __restrict__ x, const T* __restrict__ W, const float* residual,
                                   float* y, int M0, int M, int N, int K) {
+    pdl_wait();
+    pdl_launch_dependents();
     constexpr int VEC = Vec16<T>::N;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -63,8 +65,8 @@ static int launch_small(const void* x, const void* W, const float* residual, flo
         const int left = M - m0;
 #define QWB_SMALL(MT)                                                                                             \
     do {                                                                                                          \
-        if (vec) gemm_small_kernel<T, MT, true><<<grid, warps * 32, 0, stream>>>((const T*)x, (const T*)W, residual, y, m0, M, N, K); \
-        else gemm_small_kernel<T, MT, false><<<grid, warps * 32, 0, stream>>>((const T*)x, (const T*)W, residual, y, m0, M, N, K);    \
+        if (vec) qwb_launch(gemm_small_kernel<T, MT, true>, grid, warps * 32, 0, stream, (const T*)x, (const T*)W, residual, y, m0, M, N, K); \
+        else qwb_launch(gemm_small_kernel<T, MT, false>, grid, warps * 32, 0, stream, (const T*)x, (const T*)W, residual, y, m0, M, N, K);    \
     } while (0)
         if (left >= 5) QWB_SMALL(8);
         else if (left >= 3) QWB_SMALL(4);

@@ -36,6 +36,7 @@ __global__ void __launch_bounds__(GS_WARPS * 32)
 gemm_stream_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const float* residual, float* y,
                    int M, int N, int K) {
     __shared__ float part[GS_WARPS][NT][4][32];          // [warp][tile][c register][lane]
+    constexpr int U = 4;                                  // blocks of 32 k whose loads are in flight together
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * GS_ROWS;
@@ -47,6 +48,20 @@ gemm_stream_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const
     const int r_lo = n0 + g, r_hi = n0 + g + 8;
     const uint4* w_lo = reinterpret_cast<const uint4*>(W + (size_t)min(r_lo, N - 1) * K);
     const uint4* w_hi = reinterpret_cast<const uint4*>(W + (size_t)min(r_hi, N - 1) * K);
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+
+    // The weights do not depend on the kernel before this one: their first loads go out before the wait.
+    uint4 lo[U], hi[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int c = (kb0 + u) * 4 + t;
+        const bool in = kb0 + u < kb1 && c < chunks;
+        lo[u] = in ? ld_stream16(w_lo + c) : zero;
+        hi[u] = in ? ld_stream16(w_hi + c) : zero;
+    }
+    pdl_wait();
+    pdl_launch_dependents();
+
     const uint4* xr[NT];
     bool x_ok[NT];
 #pragma unroll
@@ -59,19 +74,28 @@ gemm_stream_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const
 #pragma unroll
     for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
 
-    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll 4
-    for (int kb = kb0; kb < kb1; ++kb) {
-        const int c = kb * 4 + t;
-        const bool in = c < chunks;
-        const uint4 lo = in ? ld_stream16(w_lo + c) : zero;
-        const uint4 hi = in ? ld_stream16(w_hi + c) : zero;
+    for (int kb = kb0; kb < kb1; kb += U) {
+        uint4 nlo[U], nhi[U];                             // the next U blocks, in flight while these are used
 #pragma unroll
-        for (int j = 0; j < NT; ++j) {
-            const uint4 xv = (in && x_ok[j]) ? __ldg(xr[j] + c) : zero;
-            mma_bf16_16816(acc[j], lo.x, hi.x, lo.y, hi.y, xv.x, xv.y);
-            mma_bf16_16816(acc[j], lo.z, hi.z, lo.w, hi.w, xv.z, xv.w);
+        for (int u = 0; u < U; ++u) {
+            const int c = (kb + U + u) * 4 + t;
+            const bool in = kb + U + u < kb1 && c < chunks;
+            nlo[u] = in ? ld_stream16(w_lo + c) : zero;
+            nhi[u] = in ? ld_stream16(w_hi + c) : zero;
         }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int c = (kb + u) * 4 + t;
+            const bool in = kb + u < kb1 && c < chunks;
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const uint4 xv = (in && x_ok[j]) ? __ldg(xr[j] + c) : zero;
+                mma_bf16_16816(acc[j], lo[u].x, hi[u].x, lo[u].y, hi[u].y, xv.x, xv.y);
+                mma_bf16_16816(acc[j], lo[u].z, hi[u].z, lo[u].w, hi[u].w, xv.z, xv.w);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) { lo[u] = nlo[u]; hi[u] = nhi[u]; }
     }
 #pragma unroll
     for (int j = 0; j < NT; ++j)
@@ -105,9 +129,9 @@ extern "C" int qwb_gemm_stream(const void* x, const void* W, const float* residu
     const int grid = (N + GS_ROWS - 1) / GS_ROWS;
     const bf16* xp = (const bf16*)x;
     const bf16* wp = (const bf16*)W;
-    if (M <= 8) gemm_stream_kernel<1><<<grid, GS_WARPS * 32, 0, stream>>>(xp, wp, residual, y, M, N, K);
-    else if (M <= 16) gemm_stream_kernel<2><<<grid, GS_WARPS * 32, 0, stream>>>(xp, wp, residual, y, M, N, K);
-    else if (M <= 32) gemm_stream_kernel<4><<<grid, GS_WARPS * 32, 0, stream>>>(xp, wp, residual, y, M, N, K);
-    else gemm_stream_kernel<8><<<grid, GS_WARPS * 32, 0, stream>>>(xp, wp, residual, y, M, N, K);
+    if (M <= 8) qwb_launch(gemm_stream_kernel<1>, grid, GS_WARPS * 32, 0, stream, xp, wp, residual, y, M, N, K);
+    else if (M <= 16) qwb_launch(gemm_stream_kernel<2>, grid, GS_WARPS * 32, 0, stream, xp, wp, residual, y, M, N, K);
+    else if (M <= 32) qwb_launch(gemm_stream_kernel<4>, grid, GS_WARPS * 32, 0, stream, xp, wp, residual, y, M, N, K);
+    else qwb_launch(gemm_stream_kernel<8>, grid, GS_WARPS * 32, 0, stream, xp, wp, residual, y, M, N, K);
     return qwb_check_launch("gemm_stream");
 }

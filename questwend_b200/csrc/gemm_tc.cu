@@ -1,0 +1,330 @@
+// Matrix product on the fifth-generation tensor cores (tcgen05) for many rows of bfloat16 x:
+//     y[M,N] = x[M,K] W[N,K]^T, 32-bit sums in tensor memory, with the epilogue fused:
+//       EPI_STORE   y float                               (the q/k/v projection)
+//       EPI_ADD     y += product, y float                 (o and down projections onto the residual stream)
+//       EPI_SWIGLU  a = silu(gate) * up as bfloat16       (gate/up projection; W holds the F gate rows, then the F up rows)
+//
+// One block makes one 128 x BN tile of y.  Six warps with fixed roles:
+//   warp 0  one lane issues the TMA loads: per 64 columns of k a 128 x 64 tile of x and a BN x 64 tile of W, into a ring
+//           of shared-memory stages in the 128-byte swizzle that the tensor core reads; each stage has a "full" mbarrier
+//           that the loads complete and an "empty" mbarrier that the tensor core releases;
+//   warp 1  allocates BN columns of tensor memory; one lane issues four tcgen05.mma (128 x BN x 16) per stage straight
+//           from shared memory, commits the stage's "empty" barrier after them and, at the end, the accumulator's barrier;
+//   warps 2-5  wait for the accumulator, read it with tcgen05.ld (each warp its own 32 lanes = 32 rows of the tile) and
+//           write y.  A thread owns a row, so the SwiGLU epilogue finds gate and up of one feature in the same thread.
+// Rows and columns beyond M, N and K are zero-filled by TMA and masked at the store.  No wait is unbounded: each mbarrier
+// wait gives up after a fixed number of polls, raises *error and lets the block run to its end, where outstanding loads are
+// awaited (bounded) and the tensor memory is freed.  (The reference has only a library call here: cuBLAS above 16 rows,
+// ggml-cuda/ggml-cuda.cu:1405-1617.)
+#include "common.cuh"
+
+#include <cuda.h>
+
+#define TC_BM 128
+#define TC_BK 64
+#define TC_THREADS 192
+#define TC_SPIN_LIMIT (1u << 22)
+
+#define EPI_STORE 0
+#define EPI_ADD 1
+#define EPI_SWIGLU 2
+
+// ------------------------------------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false if the barrier did not flip within the poll limit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < TC_SPIN_LIMIT; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory operand descriptor of a K-major tile whose rows are 64 bfloat16 = 128 bytes, in the 128-byte swizzle:
+// start address / 16, leading offset 1 (unused for swizzled K-major), stride between groups of 8 rows = 1024 bytes,
+// descriptor version 1, layout type 2 (128-byte swizzle).
+__device__ __forceinline__ uint64_t make_smem_desc(const void* tile) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor: D float (bits 4-5 = 1), A and B bfloat16 (bits 7-9, 10-12 = 1), both K-major (bits 15, 16 = 0),
+// N / 8 in bits 17-22, M / 16 in bits 24-28.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <int BN> struct TcStages { static constexpr int value = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8); };
+
+template <int BN>
+struct TcSmem {
+    static constexpr int STAGES = TcStages<BN>::value;
+    static constexpr size_t A_BYTES = (size_t)TC_BM * TC_BK * 2, B_BYTES = (size_t)BN * TC_BK * 2;
+    static constexpr size_t BYTES = 1024 + STAGES * (A_BYTES + B_BYTES) + 256;      // 1024: room to align the tiles
+};
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, void* out_ptr,
+               int M, int N, int K, int up_row0, int* error) {
+    constexpr int STAGES = TcSmem<BN>::STAGES;
+    constexpr uint32_t A_BYTES = TcSmem<BN>::A_BYTES, B_BYTES = TcSmem<BN>::B_BYTES;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* a_tiles = tiles;
+    unsigned char* b_tiles = tiles + STAGES * A_BYTES;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(b_tiles + STAGES * B_BYTES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* acc_bar = empty_bar + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * (EPI == EPI_SWIGLU ? BN / 2 : BN);          // first output column (feature) of the tile
+    const int m0 = blockIdx.y * TC_BM;
+    const int k_blocks = (K + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(acc_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, BN);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_acc = *tmem_slot;
+
+    pdl_wait();                 // x comes from the kernel before this one
+    pdl_launch_dependents();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int issued = 0;
+            bool ok = true;
+            for (int kb = 0; kb < k_blocks && ok; ++kb) {
+                const int s = kb % STAGES;
+                if (kb >= STAGES) ok = mbar_wait(&empty_bar[s], ((kb / STAGES) - 1) & 1);
+                if (!ok) break;
+                mbar_expect_tx(&full_bar[s], A_BYTES + B_BYTES);
+                tma_load_2d(a_tiles + (size_t)s * A_BYTES, &map_x, &full_bar[s], kb * TC_BK, m0);
+                if (EPI == EPI_SWIGLU) {
+                    tma_load_2d(b_tiles + (size_t)s * B_BYTES, &map_w, &full_bar[s], kb * TC_BK, n0);
+                    tma_load_2d(b_tiles + (size_t)s * B_BYTES + B_BYTES / 2, &map_w, &full_bar[s], kb * TC_BK, up_row0 + n0);
+                } else {
+                    tma_load_2d(b_tiles + (size_t)s * B_BYTES, &map_w, &full_bar[s], kb * TC_BK, n0);
+                }
+                issued = kb + 1;
+            }
+            if (!ok) {
+                atomicExch(error, 1);
+                // loads already issued still write shared memory: wait for them (bounded) before the block ends
+                for (int kb = max(0, issued - STAGES); kb < issued; ++kb) mbar_wait(&full_bar[kb % STAGES], (kb / STAGES) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(TC_BM, BN);
+            bool ok = true;
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                const int s = kb % STAGES;
+                ok = mbar_wait(&full_bar[s], (kb / STAGES) & 1);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t da = make_smem_desc(a_tiles + (size_t)s * A_BYTES);
+                const uint64_t db = make_smem_desc(b_tiles + (size_t)s * B_BYTES);
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; ++k)          // 16 columns of k = 32 bytes = 2 units of the start address
+                    umma_bf16(tmem_acc, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                umma_commit(&empty_bar[s]);                   // arrives when these MMAs have read the stage
+            }
+            if (!ok) atomicExch(error, 2);
+            umma_commit(acc_bar);                             // arrives when every MMA issued so far is done
+        }
+    } else {
+        const bool ok = mbar_wait(acc_bar, 0);
+        tc_fence_after();
+        if (!ok) {
+            if (lane == 0) atomicExch(error, 3);
+        } else {
+            const int lane_group = warp & 3;                  // a warp reads tensor-memory lanes [32 * (warp % 4), + 32)
+            const int row = m0 + 32 * lane_group + lane;
+            const uint32_t taddr = tmem_acc + ((uint32_t)(32 * lane_group) << 16);
+            if (EPI == EPI_SWIGLU) {
+                constexpr int HALF = BN / 2;
+                bf16* out = reinterpret_cast<bf16*>(out_ptr);
+                const int F = N;                              // N counts the features (columns of the output)
+#pragma unroll 1
+                for (int c = 0; c < HALF; c += 32) {
+                    uint32_t g[32], u[32];
+                    tmem_ld32(taddr + c, g);
+                    tmem_ld32(taddr + HALF + c, u);
+                    if (row < M) {
+                        bf16* dst = out + (size_t)row * F + n0 + c;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            const float g0 = __uint_as_float(g[i]), g1 = __uint_as_float(g[i + 1]);
+                            const float a0 = g0 / (1.f + __expf(-g0)) * __uint_as_float(u[i]);
+                            const float a1 = g1 / (1.f + __expf(-g1)) * __uint_as_float(u[i + 1]);
+                            if (n0 + c + i + 1 < F) {
+                                *reinterpret_cast<__nv_bfloat162*>(dst + i) = __floats2bfloat162_rn(a0, a1);
+                            } else if (n0 + c + i < F) {
+                                dst[i] = __float2bfloat16_rn(a0);
+                            }
+                        }
+                    }
+                }
+            } else {
+                float* out = reinterpret_cast<float*>(out_ptr);
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(taddr + c, v);
+                    if (row < M) {
+                        float* dst = out + (size_t)row * N + n0 + c;
+                        if (n0 + c + 32 <= N && (N & 3) == 0) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 4) {
+                                float4 o = make_float4(__uint_as_float(v[i]), __uint_as_float(v[i + 1]),
+                                                       __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+                                if (EPI == EPI_ADD) {
+                                    const float4 old = *reinterpret_cast<const float4*>(dst + i);
+                                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                                }
+                                *reinterpret_cast<float4*>(dst + i) = o;
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (n0 + c + i < N) dst[i] = (EPI == EPI_ADD ? dst[i] : 0.f) + __uint_as_float(v[i]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_acc, BN);
+    }
+}
+
+// ------------------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// A [rows, K] bfloat16 row-major matrix, read in boxes of box_rows x 64 in the 128-byte swizzle; outside the matrix reads zero.
+static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows, const char* what) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return qwb_fail(QWB_ERR_CUDA, "gemm_tc: cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return qwb_fail(QWB_ERR_CUDA, "gemm_tc: cuTensorMapEncodeTiled(%s) failed with %d", what, (int)r);
+    return 0;
+}
+
+template <int BN, int EPI>
+static int launch_tc(const void* x, const void* W, void* out, int M, int N, int K, int w_rows, int* error, cudaStream_t stream) {
+    CUtensorMap map_x, map_w;
+    if (int rc = make_map(&map_x, x, M, K, TC_BM, "x")) return rc;
+    if (int rc = make_map(&map_w, W, w_rows, K, EPI == EPI_SWIGLU ? BN / 2 : BN, "W")) return rc;
+    const size_t smem = TcSmem<BN>::BYTES;
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "gemm_tc: %s", cudaGetErrorString(e));
+    const int cols_per_block = EPI == EPI_SWIGLU ? BN / 2 : BN;
+    dim3 grid((N + cols_per_block - 1) / cols_per_block, (M + TC_BM - 1) / TC_BM);
+    e = qwb_launch(gemm_tc_kernel<BN, EPI>, grid, TC_THREADS, smem, stream, map_x, map_w, out, M, N, K, N, error);
+    if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "gemm_tc: launch failed: %s", cudaGetErrorString(e));
+    return qwb_check_launch("gemm_tc");
+}
+
+// x [M, K] and W bfloat16, 16-byte aligned, K a multiple of 8.  `error` is one int on the device, 0 before the call; a
+// value other than 0 afterwards means a wait inside the kernel gave up (the result is then not valid).
+//   epilogue 0: W [N, K], out float [M, N]          1: the same, out += product
+//   epilogue 2: W [2 N, K] (N gate rows, then N up rows), out bfloat16 [M, N] = silu(gate) * up
+extern "C" int qwb_gemm_tc(const void* x, const void* W, void* out, int epilogue, int M, int N, int K, int tile_n, int* error,
+                           cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8) return qwb_fail(QWB_ERR_ARG, "gemm_tc: inner size %d is not a multiple of 8", K);
+    if ((uintptr_t)x % 16 || (uintptr_t)W % 16 || (uintptr_t)out % 16) return qwb_fail(QWB_ERR_ARG, "gemm_tc: operands must be 16-byte aligned");
+    if (!error) return qwb_fail(QWB_ERR_ARG, "gemm_tc: an error word on the device is required");
+    if (epilogue == EPI_SWIGLU) {
+        if (tile_n == 128) return launch_tc<128, EPI_SWIGLU>(x, W, out, M, N, K, 2 * N, error, stream);
+        if (tile_n == 256) return launch_tc<256, EPI_SWIGLU>(x, W, out, M, N, K, 2 * N, error, stream);
+        return qwb_fail(QWB_ERR_ARG, "gemm_tc: tile width %d is not 128 or 256", tile_n);
+    }
+    if (epilogue != EPI_STORE && epilogue != EPI_ADD) return qwb_fail(QWB_ERR_ARG, "gemm_tc: unknown epilogue %d", epilogue);
+#define TC_CASE(BN)                                                                                          \
+    if (tile_n == BN)                                                                                        \
+        return epilogue == EPI_STORE ? launch_tc<BN, EPI_STORE>(x, W, out, M, N, K, N, error, stream)        \
+                                     : launch_tc<BN, EPI_ADD>(x, W, out, M, N, K, N, error, stream);
+    TC_CASE(64) TC_CASE(128) TC_CASE(256)
+#undef TC_CASE
+    return qwb_fail(QWB_ERR_ARG, "gemm_tc: tile width %d is not 64, 128 or 256", tile_n);
+}

@@ -12,6 +12,8 @@
 // angle[t,i] = pos[t] * inv_freq[i], in double: positions of thousands keep their digits.
 __global__ void rope_table_kernel(const int* __restrict__ pos, const double* __restrict__ inv_freq,
                                   float* __restrict__ cos_out, float* __restrict__ sin_out, int T, int half) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int n = T * half;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         const int t = i / half, j = i - t * half;
@@ -28,7 +30,7 @@ extern "C" int qwb_rope_table(const int* pos, const double* inv_freq, float* cos
     const int n = T * half, block = 128;
     int grid = (n + block - 1) / block;
     if (grid > 148 * 8) grid = 148 * 8;
-    rope_table_kernel<<<grid, block, 0, stream>>>(pos, inv_freq, cos_out, sin_out, T, half);
+    qwb_launch(rope_table_kernel, grid, block, 0, stream, pos, inv_freq, cos_out, sin_out, T, half);
     return qwb_check_launch("rope_table");
 }
 
@@ -49,6 +51,8 @@ __global__ void qk_norm_rope_store_kernel(const float* __restrict__ qkv, const f
                                           TOut* __restrict__ q_out, TOut* __restrict__ k_pool, TOut* __restrict__ v_pool,
                                           int Hq, int Hkv, int hd, int rot, float eps, int page_size,
                                           int table_width, int store_kv) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int t = blockIdx.x;
     const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
@@ -111,11 +115,11 @@ extern "C" int qwb_qk_norm_rope_store(const float* qkv, const float* q_weight, c
     dim3 grid(T, (Hq + 2 * Hkv + warps - 1) / warps);
     if (grid.y > 65535) return qwb_fail(QWB_ERR_ARG, "qk_norm_rope_store: too many heads (%d)", Hq + 2 * Hkv);
     if (dtype == QWB_DT_F32)
-        qk_norm_rope_store_kernel<float><<<grid, warps * 32, 0, stream>>>(
+        qwb_launch(qk_norm_rope_store_kernel<float>, grid, warps * 32, 0, stream, 
             qkv, q_weight, k_weight, cos_t, sin_t, tok_seq, tok_pos, page_table, (float*)q_out, (float*)k_pool,
             (float*)v_pool, Hq, Hkv, hd, rot, eps, page_size, table_width, store_kv);
     else if (dtype == QWB_DT_BF16)
-        qk_norm_rope_store_kernel<bf16><<<grid, warps * 32, 0, stream>>>(
+        qwb_launch(qk_norm_rope_store_kernel<bf16>, grid, warps * 32, 0, stream, 
             qkv, q_weight, k_weight, cos_t, sin_t, tok_seq, tok_pos, page_table, (bf16*)q_out, (bf16*)k_pool,
             (bf16*)v_pool, Hq, Hkv, hd, rot, eps, page_size, table_width, store_kv);
     else

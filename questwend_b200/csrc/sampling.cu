@@ -133,6 +133,8 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
               float presence_penalty, float frequency_penalty, float temperature, int top_k, float top_p,
               unsigned long long seed, const int* __restrict__ sequence_index, unsigned int step,
               const unsigned int* __restrict__ step_add, int* __restrict__ out_ids, double* out_u) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ double hist[256];
     __shared__ int hist_n[256];
     __shared__ double sh_above;
@@ -274,7 +276,7 @@ extern "C" int qwb_sample(float* logits, int B, int V, const int* recent, int wi
     if (V <= 0) return qwb_fail(QWB_ERR_ARG, "sample: bad vocabulary size %d", V);
     if (temperature > 0.f && !(top_p > 0.f)) return qwb_fail(QWB_ERR_ARG, "sample: top_p must be > 0, got %g", (double)top_p);
     if (repeat_penalty <= 0.f) return qwb_fail(QWB_ERR_ARG, "sample: repeat_penalty must be > 0, got %g", (double)repeat_penalty);
-    sample_kernel<<<B, SAMPLE_THREADS, 0, stream>>>(logits, V, recent, window, repeat_penalty, presence_penalty,
+    qwb_launch(sample_kernel, B, SAMPLE_THREADS, 0, stream, logits, V, recent, window, repeat_penalty, presence_penalty,
                                                    frequency_penalty, temperature, top_k, top_p, seed, sequence_index,
                                                    step, step_add, out_ids, out_u);
     return qwb_check_launch("sample");

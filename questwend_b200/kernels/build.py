@@ -23,8 +23,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(os.path.dirname(_HERE), "csrc")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "--shared", "-Xcompiler", "-fPIC"]
-EXTRA_FLAGS: dict[str, list[str]] = {"gemm_tc": ["-lcuda"]}
-MODULES = ("elementwise", "rope_kv", "attention", "attention_mma", "gemm_small", "gemm_stream", "sampling")
+EXTRA_FLAGS: dict[str, list[str]] = {}
+MODULES = ("elementwise", "rope_kv", "attention", "attention_mma", "gemm_small", "gemm_stream", "gemm_tc", "sampling")
 
 _lock = threading.Lock()
 _loaded: dict[str, ctypes.CDLL] = {}

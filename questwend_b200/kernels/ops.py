@@ -290,6 +290,64 @@ def gemm_stream(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor | 
     return out
 
 
+_TC_ERROR: dict = {}    # device -> one int32 that a gemm_tc kernel sets when one of its waits gives up
+TC_EPILOGUES = {"store": 0, "add": 1, "swiglu": 2}
+
+
+def gemm_tc_error_word(device) -> torch.Tensor:
+    key = torch.device(device).index or 0
+    if key not in _TC_ERROR:
+        _TC_ERROR[key] = torch.zeros((1,), dtype=torch.int32, device=device)
+    return _TC_ERROR[key]
+
+
+def gemm_tc_check(device) -> None:
+    """Raise if a tcgen05 product on this device gave up a wait since the last check (reads one int: synchronises)."""
+    word = gemm_tc_error_word(device)
+    code = int(word.item())
+    if code:
+        word.zero_()
+        where = {1: "the loader waiting for a free stage", 2: "the tensor-core issuer waiting for a loaded stage",
+                 3: "the epilogue waiting for the accumulator"}.get(code, f"code {code}")
+        raise KernelError(f"gemm_tc: a bounded wait ran out ({where}); the result of that product is not valid")
+
+
+def gemm_tc(x: torch.Tensor, weight: torch.Tensor, epilogue: str = "store", out: torch.Tensor | None = None,
+            tile_n: int | None = None) -> torch.Tensor:
+    """bfloat16 x [M, K] times bfloat16 weight transposed on the tcgen05 tensor cores.
+
+    "store": weight [N, K] -> float32 [M, N].  "add": the same, added onto ``out``.
+    "swiglu": weight [2F, K] (F gate rows, then F up rows) -> bfloat16 [M, F] = silu(gate) * up.
+    """
+    _need(x, "x", torch.bfloat16, 2)
+    _need(weight, "weight", torch.bfloat16, 2)
+    M, K = x.shape
+    if weight.shape[1] != K:
+        raise KernelError(f"gemm_tc: x has {K} columns, the weight {weight.shape[1]}")
+    if epilogue not in TC_EPILOGUES:
+        raise KernelError(f"gemm_tc: unknown epilogue '{epilogue}'")
+    if epilogue == "swiglu":
+        if weight.shape[0] % 2:
+            raise KernelError(f"gemm_tc: {weight.shape[0]} rows cannot be split into gate and up")
+        N = weight.shape[0] // 2
+        out_dtype = torch.bfloat16
+    else:
+        N = weight.shape[0]
+        out_dtype = torch.float32
+    if out is None:
+        if epilogue == "add":
+            raise KernelError("gemm_tc: the 'add' epilogue needs the tensor to add onto")
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    _need(out, "out", out_dtype, 2)
+    if tuple(out.shape) != (M, N):
+        raise KernelError(f"gemm_tc: out is {tuple(out.shape)}, expected {(M, N)}")
+    if tile_n is None:
+        tile_n = 128 if epilogue == "swiglu" else (128 if N >= 1024 else 64)
+    _call("gemm_tc", "qwb_gemm_tc", _ptr(x), _ptr(weight), _ptr(out), _i(TC_EPILOGUES[epilogue]), _i(M), _i(N), _i(K),
+          _i(tile_n), _ptr(gemm_tc_error_word(x.device)), _stream())
+    return out
+
+
 # ----------------------------------------------------------------------------- sampling
 def sample(logits: torch.Tensor, temperature: float, top_k: int = 0, top_p: float = 1.0, seed: int = 0,
            sequence_index: torch.Tensor | None = None, step: int = 0, recent: torch.Tensor | None = None,

@@ -355,6 +355,37 @@ def test_gemm_stream(M, N, K):
         ops.gemm_stream(x[:, :K - 4].contiguous(), w[:, :K - 4].contiguous())
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 256), (300, 200, 200), (17, 96, 1032), (512, 1024, 4096),
+                                   (1, 64, 64), (129, 130, 72)])
+@pytest.mark.parametrize("tile_n", [64, 128, 256])
+def test_gemm_tc(M, N, K, tile_n):
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(N, K, generator=g).to(torch.bfloat16).to(DEV)
+    ref = f64(x) @ f64(w).T
+    out = ops.gemm_tc(x, w, tile_n=tile_n)
+    ops.gemm_tc_check(DEV)
+    close(out, ref, torch.float32, scale=np.abs(ref).max() * 4)          # 32-bit sums of exact products
+    base = torch.randn(M, N, generator=g).to(DEV)
+    added = ops.gemm_tc(x, w, epilogue="add", out=base.clone(), tile_n=tile_n)
+    ops.gemm_tc_check(DEV)
+    close(added, f64(base) + ref, torch.float32, scale=np.abs(ref).max() * 4)
+
+
+@pytest.mark.parametrize("M,F,K", [(128, 128, 64), (200, 200, 96), (64, 1000, 512), (300, 64, 4096)])
+@pytest.mark.parametrize("tile_n", [128, 256])
+def test_gemm_tc_swiglu(M, F, K, tile_n):
+    g = torch.Generator().manual_seed(M + F + K)
+    x = (torch.randn(M, K, generator=g) * 0.3).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(2 * F, K, generator=g) * 0.3).to(torch.bfloat16).to(DEV)
+    gu = f64(x) @ f64(w).T
+    ref = pm.swiglu(gu[:, :F], gu[:, F:])
+    out = ops.gemm_tc(x, w, epilogue="swiglu", tile_n=tile_n)
+    ops.gemm_tc_check(DEV)
+    assert out.dtype == torch.bfloat16
+    close(out, ref, torch.bfloat16)
+
+
 # ----------------------------------------------------------------------------- sampling
 def test_greedy_takes_the_lowest_id_among_equals():
     lg = torch.zeros(3, 1000, device=DEV)

@@ -10,9 +10,10 @@
 //           that the loads complete and an "empty" mbarrier that the tensor core releases;
 //   warp 1  allocates BN columns of tensor memory; one lane issues four tcgen05.mma (128 x BN x 16) per stage straight
 //           from shared memory, commits the stage's "empty" barrier after them and, at the end, the accumulator's barrier;
-//   warps 2-5  wait for the accumulator, read it with tcgen05.ld (each warp its own 32 lanes = 32 rows of the tile) and
-//           write y.  A thread owns a row, so the SwiGLU epilogue finds gate and up of one feature in the same thread.
-// Rows and columns beyond M, N and K are zero-filled by TMA and masked at the store.  No wait is unbounded: each mbarrier
+//   warps 2-5  wait for the accumulator, read it with tcgen05.ld (each warp its own 32 lanes = 32 rows of the tile), stage
+//           it in shared memory and hand it to TMA: a store, or a reduce-add onto y for the residual sum.  A thread owns a
+//           row, so the SwiGLU epilogue finds gate and up of one feature in the same thread.
+// Rows and columns beyond M, N and K are zero-filled by the TMA loads and dropped by the TMA stores.  No wait is unbounded: each mbarrier
 // wait gives up after a fixed number of polls, raises *error and lets the block run to its end, where outstanding loads are
 // awaited (bounded) and the tensor memory is freed.  (The reference has only a library call here: cuBLAS above 16 rows,
 // ggml-cuda/ggml-cuda.cu:1405-1617.)
@@ -24,6 +25,7 @@
 #define TC_BK 64
 #define TC_THREADS 192
 #define TC_SPIN_LIMIT (1u << 22)
+#define TC_STAGING_BYTES 4096      // one warp's staging tile of the epilogue: 32 rows of 128 bytes
 
 #define EPI_STORE 0
 #define EPI_ADD 1
@@ -108,27 +110,30 @@ template <int BN>
 struct TcSmem {
     static constexpr int STAGES = TcStages<BN>::value;
     static constexpr size_t A_BYTES = (size_t)TC_BM * TC_BK * 2, B_BYTES = (size_t)BN * TC_BK * 2;
-    static constexpr size_t BYTES = 1024 + STAGES * (A_BYTES + B_BYTES) + 256;      // 1024: room to align the tiles
+    static constexpr size_t BYTES = 1024 + STAGES * (A_BYTES + B_BYTES) + 8 * TC_STAGING_BYTES + 256;   // 1024: to align
 };
 
 template <int BN, int EPI>
 __global__ void __launch_bounds__(TC_THREADS)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, void* out_ptr,
-               int M, int N, int K, int up_row0, int* error) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+               const __grid_constant__ CUtensorMap map_out, int M, int N, int K, int up_row0, int* error) {
     constexpr int STAGES = TcSmem<BN>::STAGES;
     constexpr uint32_t A_BYTES = TcSmem<BN>::A_BYTES, B_BYTES = TcSmem<BN>::B_BYTES;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* a_tiles = tiles;
     unsigned char* b_tiles = tiles + STAGES * A_BYTES;
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(b_tiles + STAGES * B_BYTES);
+    unsigned char* staging = b_tiles + STAGES * B_BYTES;              // [4 warps][2][32 rows][128 bytes]
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(staging + 4 * 2 * TC_STAGING_BYTES);
     uint64_t* empty_bar = full_bar + STAGES;
     uint64_t* acc_bar = empty_bar + STAGES;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * (EPI == EPI_SWIGLU ? BN / 2 : BN);          // first output column (feature) of the tile
-    const int m0 = blockIdx.y * TC_BM;
+    // Blocks that run together share a tile of W: the row tiles are the fast index, so W streams from HBM once and the
+    // (much smaller) x stays in L2.
+    const int n0 = blockIdx.y * (EPI == EPI_SWIGLU ? BN / 2 : BN);          // first output column (feature) of the tile
+    const int m0 = blockIdx.x * TC_BM;
     const int k_blocks = (K + TC_BK - 1) / TC_BK;
 
     if (threadIdx.x == 0) {
@@ -194,60 +199,66 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         if (!ok) {
             if (lane == 0) atomicExch(error, 3);
         } else {
+            // Each warp owns 32 rows.  Per chunk of output columns it moves its accumulator lanes into a staging tile in
+            // shared memory (rows of 128 bytes, 16-byte pieces XOR-swizzled by the row so that neither these writes nor
+            // the TMA unit meet bank conflicts) and one lane hands the tile to TMA: a store, or an add onto global memory
+            // for the residual sum.  Two staging tiles per warp let the next chunk be prepared while the last one drains.
             const int lane_group = warp & 3;                  // a warp reads tensor-memory lanes [32 * (warp % 4), + 32)
-            const int row = m0 + 32 * lane_group + lane;
+            const int row0 = m0 + 32 * lane_group;
             const uint32_t taddr = tmem_acc + ((uint32_t)(32 * lane_group) << 16);
-            if (EPI == EPI_SWIGLU) {
-                constexpr int HALF = BN / 2;
-                bf16* out = reinterpret_cast<bf16*>(out_ptr);
-                const int F = N;                              // N counts the features (columns of the output)
+            unsigned char* stage0 = staging + (size_t)lane_group * 2 * TC_STAGING_BYTES;
+            constexpr int CHUNKS = EPI == EPI_SWIGLU ? BN / 2 / 64 : BN / 32;
 #pragma unroll 1
-                for (int c = 0; c < HALF; c += 32) {
-                    uint32_t g[32], u[32];
-                    tmem_ld32(taddr + c, g);
-                    tmem_ld32(taddr + HALF + c, u);
-                    if (row < M) {
-                        bf16* dst = out + (size_t)row * F + n0 + c;
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            const float g0 = __uint_as_float(g[i]), g1 = __uint_as_float(g[i + 1]);
-                            const float a0 = g0 / (1.f + __expf(-g0)) * __uint_as_float(u[i]);
-                            const float a1 = g1 / (1.f + __expf(-g1)) * __uint_as_float(u[i + 1]);
-                            if (n0 + c + i + 1 < F) {
-                                *reinterpret_cast<__nv_bfloat162*>(dst + i) = __floats2bfloat162_rn(a0, a1);
-                            } else if (n0 + c + i < F) {
-                                dst[i] = __float2bfloat16_rn(a0);
-                            }
-                        }
-                    }
+            for (int ch = 0; ch < CHUNKS; ++ch) {
+                unsigned char* st = stage0 + (size_t)(ch & 1) * TC_STAGING_BYTES;
+                if (ch >= 2) {                                // the store that read this tile two chunks ago must be done
+                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    __syncwarp();
                 }
-            } else {
-                float* out = reinterpret_cast<float*>(out_ptr);
-#pragma unroll 1
-                for (int c = 0; c < BN; c += 32) {
-                    uint32_t v[32];
-                    tmem_ld32(taddr + c, v);
-                    if (row < M) {
-                        float* dst = out + (size_t)row * N + n0 + c;
-                        if (n0 + c + 32 <= N && (N & 3) == 0) {
+                uint4* my_row = reinterpret_cast<uint4*>(st + lane * 128);
+                if (EPI == EPI_SWIGLU) {
+                    constexpr int HALF = BN / 2;
 #pragma unroll
-                            for (int i = 0; i < 32; i += 4) {
-                                float4 o = make_float4(__uint_as_float(v[i]), __uint_as_float(v[i + 1]),
-                                                       __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
-                                if (EPI == EPI_ADD) {
-                                    const float4 old = *reinterpret_cast<const float4*>(dst + i);
-                                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                                }
-                                *reinterpret_cast<float4*>(dst + i) = o;
+                    for (int half = 0; half < 2; ++half) {    // 2 x 32 features -> 64 bfloat16 = one 128-byte row
+                        uint32_t g[32], u[32];
+                        tmem_ld32(taddr + ch * 64 + half * 32, g);
+                        tmem_ld32(taddr + HALF + ch * 64 + half * 32, u);
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            uint32_t pk[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const float g0 = __uint_as_float(g[i + 2 * j]), g1 = __uint_as_float(g[i + 2 * j + 1]);
+                                const float a0 = g0 / (1.f + __expf(-g0)) * __uint_as_float(u[i + 2 * j]);
+                                const float a1 = g1 / (1.f + __expf(-g1)) * __uint_as_float(u[i + 2 * j + 1]);
+                                __nv_bfloat162 v = __floats2bfloat162_rn(a0, a1);
+                                pk[j] = *reinterpret_cast<uint32_t*>(&v);
                             }
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i)
-                                if (n0 + c + i < N) dst[i] = (EPI == EPI_ADD ? dst[i] : 0.f) + __uint_as_float(v[i]);
+                            const int piece = half * 4 + i / 8;
+                            my_row[piece ^ (lane & 7)] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                         }
                     }
+                } else {
+                    uint32_t v[32];
+                    tmem_ld32(taddr + ch * 32, v);
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) my_row[(i / 4) ^ (lane & 7)] = make_uint4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    const int col = n0 + ch * (EPI == EPI_SWIGLU ? 64 : 32);
+                    if (EPI == EPI_ADD)
+                        asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                                     ::"l"(&map_out), "r"(smem_u32(st)), "r"(col), "r"(row0) : "memory");
+                    else
+                        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+                                     ::"l"(&map_out), "r"(smem_u32(st)), "r"(col), "r"(row0) : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
             }
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // shared memory is read, global is written
+            __syncwarp();
         }
     }
     tc_fence_before();
@@ -274,15 +285,18 @@ static EncodeTiledFn get_encode() {
     return fn;
 }
 
-// A [rows, K] bfloat16 row-major matrix, read in boxes of box_rows x 64 in the 128-byte swizzle; outside the matrix reads zero.
-static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows, const char* what) {
+// A [rows, cols] row-major matrix of bfloat16 (or float), moved in boxes of box_rows x 128 bytes in the 128-byte swizzle;
+// reads outside the matrix give zero, writes outside are dropped.
+static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int box_rows, const char* what, bool is_float = false) {
     EncodeTiledFn enc = get_encode();
     if (!enc) return qwb_fail(QWB_ERR_CUDA, "gemm_tc: cuTensorMapEncodeTiled is not available from this driver");
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    const int elem_bytes = is_float ? 4 : 2;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * elem_bytes};
+    cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), (cuuint32_t)box_rows};
     cuuint32_t elem[2] = {1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+    CUresult r = enc(map, is_float ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                     const_cast<void*>(base), dims, strides, box, elem,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return qwb_fail(QWB_ERR_CUDA, "gemm_tc: cuTensorMapEncodeTiled(%s) failed with %d", what, (int)r);
@@ -291,15 +305,17 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box
 
 template <int BN, int EPI>
 static int launch_tc(const void* x, const void* W, void* out, int M, int N, int K, int w_rows, int* error, cudaStream_t stream) {
-    CUtensorMap map_x, map_w;
+    CUtensorMap map_x, map_w, map_out;
     if (int rc = make_map(&map_x, x, M, K, TC_BM, "x")) return rc;
     if (int rc = make_map(&map_w, W, w_rows, K, EPI == EPI_SWIGLU ? BN / 2 : BN, "W")) return rc;
+    if (int rc = make_map(&map_out, out, M, N, 32, "out", EPI != EPI_SWIGLU)) return rc;
     const size_t smem = TcSmem<BN>::BYTES;
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "gemm_tc: %s", cudaGetErrorString(e));
     const int cols_per_block = EPI == EPI_SWIGLU ? BN / 2 : BN;
-    dim3 grid((N + cols_per_block - 1) / cols_per_block, (M + TC_BM - 1) / TC_BM);
-    e = qwb_launch(gemm_tc_kernel<BN, EPI>, grid, TC_THREADS, smem, stream, map_x, map_w, out, M, N, K, N, error);
+    dim3 grid((M + TC_BM - 1) / TC_BM, (N + cols_per_block - 1) / cols_per_block);
+    if (grid.y > 65535) return qwb_fail(QWB_ERR_ARG, "gemm_tc: %d column tiles are more than a grid takes", (int)grid.y);
+    e = qwb_launch(gemm_tc_kernel<BN, EPI>, grid, TC_THREADS, smem, stream, map_x, map_w, map_out, M, N, K, N, error);
     if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "gemm_tc: launch failed: %s", cudaGetErrorString(e));
     return qwb_check_launch("gemm_tc");
 }
@@ -312,6 +328,7 @@ extern "C" int qwb_gemm_tc(const void* x, const void* W, void* out, int epilogue
                            cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8) return qwb_fail(QWB_ERR_ARG, "gemm_tc: inner size %d is not a multiple of 8", K);
+    if (N % 8) return qwb_fail(QWB_ERR_ARG, "gemm_tc: %d output columns are not a multiple of 8", N);
     if ((uintptr_t)x % 16 || (uintptr_t)W % 16 || (uintptr_t)out % 16) return qwb_fail(QWB_ERR_ARG, "gemm_tc: operands must be 16-byte aligned");
     if (!error) return qwb_fail(QWB_ERR_ARG, "gemm_tc: an error word on the device is required");
     if (epilogue == EPI_SWIGLU) {

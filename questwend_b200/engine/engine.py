@@ -23,6 +23,7 @@ from ..cache.manager import CacheManager, pages_for
 from ..config.base import ModelConfig
 from ..config.registry import get_architecture, load_config
 from ..kernels import build as kernel_build
+from ..kernels import ops
 from ..kernels.ops import PAGE_SIZE
 from ..parts.base import Runtime, StepContext
 from ..parts.linear import require_true_fp32
@@ -190,6 +191,8 @@ class Engine:
         with torch.cuda.device(self.device):
             ctx, want_rows = self.build_context(entries)
             logits = self.model.forward(ctx, self.unit_caches, want_rows)
+            if self.dtype == torch.bfloat16 and ctx.n_tokens > 128:
+                ops.gemm_tc_check(self.device)       # a tcgen05 product that gave up a wait must not pass unseen
         for e in entries:
             self.cache.advance(e.slot, len(e.tokens))
         self.steps_run += 1

@@ -48,7 +48,7 @@ def _time(fn, n_variants: int, iters: int, warmup: int = 3, burst: int = 10) -> 
     return statistics.median(times)
 
 
-def bench_gemm(M: int, N: int, K: int, impl: str, iters: int, dtype=torch.bfloat16) -> dict:
+def bench_gemm(M: int, N: int, K: int, impl: str, iters: int, dtype=torch.bfloat16, tile_n=None) -> dict:
     elem = 2 if dtype == torch.bfloat16 else 4
     copies = max(2, math.ceil(2 * L2_BYTES / (N * K * elem)))
     ws = [torch.randn(N, K, device="cuda", dtype=torch.float32).mul_(0.02).to(dtype) for _ in range(copies)]
@@ -58,7 +58,12 @@ def bench_gemm(M: int, N: int, K: int, impl: str, iters: int, dtype=torch.bfloat
     elif impl == "small":
         fn = lambda i: ops.gemm_small(x, ws[i])
     elif impl == "tc":
-        fn = lambda i: ops.gemm_tc(x, ws[i])
+        fn = lambda i: ops.gemm_tc(x, ws[i], tile_n=tile_n)
+    elif impl == "tc_add":
+        acc = torch.zeros(M, N, device="cuda")
+        fn = lambda i: ops.gemm_tc(x, ws[i], epilogue="add", out=acc, tile_n=tile_n)
+    elif impl == "tc_swiglu":
+        fn = lambda i: ops.gemm_tc(x, ws[i], epilogue="swiglu", tile_n=tile_n)
     else:
         fn = (lambda i: torch.mm(x, ws[i].t(), out_dtype=torch.float32)) if dtype == torch.bfloat16 else \
              (lambda i: torch.mm(x, ws[i].t()))
@@ -121,7 +126,7 @@ def main() -> int:
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=24576)
     ap.add_argument("--k", type=int, default=4096)
-    ap.add_argument("--impl", default="stream", choices=["stream", "small", "library", "tc"])
+    ap.add_argument("--impl", default="stream", choices=["stream", "small", "library", "tc", "tc_add", "tc_swiglu"])
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=1152)
@@ -130,14 +135,15 @@ def main() -> int:
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--tile-n", type=int, default=None)
     args = ap.parse_args()
     dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
     if args.what == "gemm":
-        print(json.dumps(bench_gemm(args.m, args.n, args.k, args.impl, args.iters, dtype)))
+        print(json.dumps(bench_gemm(args.m, args.n, args.k, args.impl, args.iters, dtype, args.tile_n)))
     elif args.what == "decode_shapes":
         for name, n, k in (("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 24576, 4096), ("down", 4096, 12288),
                            ("lm_head", 151936, 4096)):
-            r = bench_gemm(args.m, n, k, args.impl, args.iters, dtype)
+            r = bench_gemm(args.m, n, k, args.impl, args.iters, dtype, args.tile_n)
             r["name"] = name
             print(json.dumps(r))
     elif args.what == "attn_decode":

@@ -64,7 +64,7 @@ class GroupedQueryAttention(Mixer):
             self.k_norm_w = weights[px + n["k_norm"]].to(torch.float32).contiguous()
 
     def kernel_modules(self):
-        mods = ["rope_kv", "gemm_small", "gemm_stream"]
+        mods = ["rope_kv", "gemm_small", "gemm_stream", "gemm_tc"]
         mods.append("attention_mma" if ops.mma_attention_fits(self.runtime.dtype, self.head_dim, ops.PAGE_SIZE)
                     else "attention")
         return tuple(mods)
@@ -72,7 +72,9 @@ class GroupedQueryAttention(Mixer):
     def kv_spec(self):
         return KVSpec(self.n_kv_heads, self.head_dim, self.window)
 
-    def forward(self, x, ctx, cache):
+    adds_to_residual = True
+
+    def forward(self, x, ctx, cache, residual=None):
         qkv = linear(x, self.w_qkv)
         cos = sin = None
         if self.position is not None:
@@ -87,6 +89,9 @@ class GroupedQueryAttention(Mixer):
         else:
             att = ops.attn_prefill(q, cache.k_pool, cache.v_pool, table, ctx.cu_seqlens, ctx.pos0, ctx.max_new,
                                    self.scale, window=self.window)
+        if residual is not None:
+            linear(att, self.w_o, add_to=residual)      # the residual sum, in the product's epilogue
+            return None
         return linear(att, self.w_o)
 
 

@@ -133,12 +133,16 @@ class Mixer(Part):
     def state_spec(self) -> StateSpec | None:
         return None
 
+    adds_to_residual = False    # True: forward(..., residual=h) adds its output onto h in place and returns None
+
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: UnitCache) -> torch.Tensor:
         raise NotImplementedError
 
 
 class FeedForward(Part):
     """Position-wise: x [T, D] in the engine's dtype -> float32 [T, D]."""
+
+    adds_to_residual = False    # as for Mixer
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError

@@ -1,7 +1,8 @@
 """Pre-norm residual block: h += mixer(norm1(h)); h += feed_forward(norm2(h))
 (the reference: core/runtime.cpp:1015-1081; for this arrangement the second norm reads the
 same tensor that the second residual sum starts from, :1066-1067).  The sums are folded into
-the norms: each norm takes (h, delta), writes h + delta back and norms it."""
+the norms (each norm takes (h, delta), writes h + delta back and norms it) or, for parts that say
+``adds_to_residual``, into the epilogue of the part's last matrix product (delta is then None)."""
 from __future__ import annotations
 
 from dataclasses import replace
@@ -38,9 +39,15 @@ class PreNormBlock(Block):
 
     def forward(self, h, delta, ctx, cache):
         x = self.norm1.forward(h, delta, write_sum=True)
-        delta = self.mixer.forward(x, ctx, cache)
+        if self.mixer.adds_to_residual:
+            delta = self.mixer.forward(x, ctx, cache, residual=h)
+        else:
+            delta = self.mixer.forward(x, ctx, cache)
         x = self.norm2.forward(h, delta, write_sum=True)
-        delta = self.ffn.forward(x, ctx)
+        if self.ffn.adds_to_residual:
+            delta = self.ffn.forward(x, ctx, residual=h)
+        else:
+            delta = self.ffn.forward(x, ctx)
         return h, delta
 
 

@@ -59,7 +59,7 @@ class OutputHead(Part):
             self.weight = weights[self.name]
 
     def kernel_modules(self):
-        return ("gemm_small", "gemm_stream")
+        return ("gemm_small", "gemm_stream", "gemm_tc")
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return linear(x, self.weight)

@@ -1,9 +1,12 @@
 """Matrix products y = x W^T with 32-bit sums and a 32-bit result.
 
 Few rows (a decode step) go to the hand-written weight-streaming kernels: bfloat16
-with up to 64 rows to the tensor-core one, float32 (and odd inner sizes) with up to
-16 rows to the plain one.  More rows go to the library product, as in the reference,
-whose dispatcher sends up to 16 rows to its own kernels and the rest to cuBLAS
+with up to 16 rows to the tensor-core one (mma.sync), float32 (and odd inner sizes)
+with up to 16 rows to the plain one.  More bfloat16 rows go to the tcgen05 kernel
+(TMA-fed, accumulators in tensor memory), which also folds the residual sum or the
+gated SiLU into its epilogue.  What is left (float32 with many rows, inner sizes
+that are no multiple of 8) goes to the library product, as in the reference, whose
+dispatcher sends up to 16 rows to its own kernels and the rest to cuBLAS
 (ggml-cuda/ggml-cuda.cu:1812-1866).  In the 32-bit engine the library product
 runs in plain float32: the reduced-precision (TF32) mode is switched off and
 checked at every call.
@@ -21,16 +24,38 @@ def require_true_fp32() -> None:
     torch.set_float32_matmul_precision("highest")
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-    """x [M, K] (the weight's dtype) times weight [N, K] transposed -> float32 [M, N]."""
+TC_MIN_ROWS = 129       # the tcgen05 kernel's tiles have 128 rows; below that the library's split-K products are faster
+
+
+def _tc_fits(x: torch.Tensor, weight: torch.Tensor, n_out: int | None = None) -> bool:
+    n_out = weight.shape[0] if n_out is None else n_out
+    return (weight.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and n_out % 8 == 0 and x.shape[0] >= TC_MIN_ROWS)
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, add_to: torch.Tensor | None = None) -> torch.Tensor:
+    """x [M, K] (the weight's dtype) times weight [N, K] transposed -> float32 [M, N].
+    With ``add_to`` (float32 [M, N]) the product is added onto it in place and it is returned."""
     M, K = x.shape
     if weight.dtype == torch.bfloat16 and M <= ops.STREAM_M and K % 8 == 0:
-        return ops.gemm_stream(x, weight)
+        return ops.gemm_stream(x, weight, residual=add_to)
     if M <= ops.SMALL_M:
-        return ops.gemm_small(x, weight)
+        return ops.gemm_small(x, weight, residual=add_to)
+    if _tc_fits(x, weight):
+        if add_to is not None:
+            return ops.gemm_tc(x, weight, epilogue="add", out=add_to, tile_n=256)
+        return ops.gemm_tc(x, weight, tile_n=256)
+    if add_to is not None:
+        return ops.add_inplace(add_to, linear(x, weight))
     if weight.dtype == torch.bfloat16:
         return torch.mm(x, weight.t(), out_dtype=torch.float32)
     if torch.backends.cuda.matmul.allow_tf32 or torch.get_float32_matmul_precision() != "highest":
         raise RuntimeError("the 32-bit engine needs plain float32 matrix products; a reduced-precision "
                            "mode was switched on after the engine was made")
     return torch.mm(x, weight.t())
+
+
+def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) for the stacked weight [2F, K] (gate rows first) -> [M, F] in ``out_dtype``."""
+    if _tc_fits(x, weight_gate_up, weight_gate_up.shape[0] // 2) and out_dtype == torch.bfloat16:
+        return ops.gemm_tc(x, weight_gate_up, epilogue="swiglu", tile_n=256)
+    return ops.silu_mul(linear(x, weight_gate_up), out_dtype)

@@ -6,7 +6,7 @@ import torch
 from ..kernels import ops
 from ..weights.manifest import MATRIX, TensorSpec
 from .base import FeedForward
-from .linear import linear
+from .linear import linear, linear_swiglu
 from .registry import register_feed_forward
 
 
@@ -34,11 +34,15 @@ class GatedMLP(FeedForward):
         self.w_down = weights[px + n["down"]]
 
     def kernel_modules(self):
-        return ("elementwise", "gemm_small", "gemm_stream")
+        return ("elementwise", "gemm_small", "gemm_stream", "gemm_tc")
 
-    def forward(self, x, ctx):
-        gate_up = linear(x, self.w_gate_up)
-        act = ops.silu_mul(gate_up, self.runtime.dtype)
+    adds_to_residual = True
+
+    def forward(self, x, ctx, residual=None):
+        act = linear_swiglu(x, self.w_gate_up, self.runtime.dtype)
+        if residual is not None:
+            linear(act, self.w_down, add_to=residual)
+            return None
         return linear(act, self.w_down)
 
 

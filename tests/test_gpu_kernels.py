@@ -356,7 +356,7 @@ def test_gemm_stream(M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 256), (300, 200, 200), (17, 96, 1032), (512, 1024, 4096),
-                                   (1, 64, 64), (129, 130, 72)])
+                                   (1, 64, 64), (129, 136, 72)])
 @pytest.mark.parametrize("tile_n", [64, 128, 256])
 def test_gemm_tc(M, N, K, tile_n):
     g = torch.Generator().manual_seed(M + N + K)

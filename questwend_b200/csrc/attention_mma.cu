@@ -70,8 +70,8 @@ __device__ __forceinline__ void load_tile(bf16* tile, const bf16* src, int n_val
 //   key0   position of the tile's first key; row_pos[2]: positions of rows g and g + 8 (-1: row unused)
 //   len    keys of the sequence; window (0: none)
 //   m, l   running maximum and (this thread's share of the) sum for rows g and g + 8;  o: [HD/8][4]
-template <int HD>
-__device__ __forceinline__ void tile_step(const uint32_t (*qf)[4], const bf16* Kt, const bf16* Vt, int key0, const int* row_pos,
+template <int HD, bool SPLIT_WAIT>
+__device__ __forceinline__ void tile_step_impl(const uint32_t (*qf)[4], const bf16* Kt, const bf16* Vt, int key0, const int* row_pos,
                                           int len, int window, float sl2, float* m, float* l, float (*o)[4], int lane) {
     constexpr int KS = HD / 16, NT = AM_TILE / 8, DT = HD / 8;
     const int t = lane & 3;
@@ -79,6 +79,7 @@ __device__ __forceinline__ void tile_step(const uint32_t (*qf)[4], const bf16* K
 #pragma unroll
     for (int j = 0; j < NT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
     const int mi = lane >> 3, mr = lane & 7;          // ldmatrix: which matrix this lane addresses, and its row
+    if (SPLIT_WAIT) { cp_async_wait<1>(); __syncwarp(); }     // K has landed; V may still be on its way
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks) {
 #pragma unroll
@@ -119,6 +120,7 @@ __device__ __forceinline__ void tile_step(const uint32_t (*qf)[4], const bf16* K
         o[d][0] *= alpha[0]; o[d][1] *= alpha[0];
         o[d][2] *= alpha[1]; o[d][3] *= alpha[1];
     }
+    if (SPLIT_WAIT) { cp_async_wait<0>(); __syncwarp(); }     // V has landed
     // probabilities, then O += P V
 #pragma unroll
     for (int kk = 0; kk < AM_TILE / 16; ++kk) {
@@ -144,6 +146,18 @@ __device__ __forceinline__ void tile_step(const uint32_t (*qf)[4], const bf16* K
             mma_16816(o[jd + 1], pf, b[2], b[3]);
         }
     }
+}
+
+template <int HD>
+__device__ __forceinline__ void tile_step(const uint32_t (*qf)[4], const bf16* Kt, const bf16* Vt, int key0, const int* row_pos,
+                                          int len, int window, float sl2, float* m, float* l, float (*o)[4], int lane) {
+    tile_step_impl<HD, false>(qf, Kt, Vt, key0, row_pos, len, window, sl2, m, l, o, lane);
+}
+// The same for a warp that issued the tile's K and V copies itself, as two cp.async groups: it waits for each where it is needed.
+template <int HD>
+__device__ __forceinline__ void tile_step_split(const uint32_t (*qf)[4], const bf16* Kt, const bf16* Vt, int key0, const int* row_pos,
+                                                int len, int window, float sl2, float* m, float* l, float (*o)[4], int lane) {
+    tile_step_impl<HD, true>(qf, Kt, Vt, key0, row_pos, len, window, sl2, m, l, o, lane);
 }
 
 // Q fragments of rows (g, g + 8) of a warp; q_lo / q_hi point at the rows' hd values (or null).
@@ -247,10 +261,13 @@ attn_mma_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
 }
 
 // ---------------------------------------------------------------------------------
-// decode: block = (run, key/value head and head chunk, sequence); warp w takes the run's pages w, w + 4, ...
+// decode: block = (run of keys, key/value head and head chunk, sequence) with WARPS warps; warp w takes the run's
+// pages w, w + WARPS, ...  With runs of one page (the engine's choice) a block is a single warp that holds
+// 32 KB of shared memory, so seven of them share an SM and one's loads overlap another's arithmetic; its partial
+// result goes straight from registers to the scratch that the combine kernel reads.
 // ---------------------------------------------------------------------------------
-template <int HD>
-__global__ void __launch_bounds__(AM_WARPS * 32)
+template <int HD, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
 attn_mma_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                        const int* __restrict__ page_table, const int* __restrict__ seq_len, float* __restrict__ part_acc,
                        float* __restrict__ part_m, float* __restrict__ part_l, bf16* __restrict__ out, int Hq, int Hkv,
@@ -286,24 +303,48 @@ attn_mma_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
     const int tok_begin = run * split_tokens, tok_end = min(len, tok_begin + split_tokens);
     const int* pages = page_table + (size_t)b * table_width;
     const float sl2 = scale * 1.4426950408889634f;
-    for (int base = tok_begin + warp * AM_TILE; base < tok_end; base += AM_WARPS * AM_TILE) {
+    for (int base = tok_begin + warp * AM_TILE; base < tok_end; base += WARPS * AM_TILE) {
         if (base + AM_TILE <= k_lo) continue;                                  // a page wholly before the window
         const size_t src = ((size_t)pages[base / AM_TILE] * Hkv + kvh) * AM_TILE * HD;
         const int n_valid = min(AM_TILE, len - base);
         __syncwarp();
         load_tile<HD>(my_tiles, k_pool + src, n_valid, lane, 32);
+        cp_async_commit();
         load_tile<HD>(my_tiles + AM_TILE * HD, v_pool + src, n_valid, lane, 32);
         cp_async_commit();
-        cp_async_wait<0>();
-        __syncwarp();
-        tile_step<HD>(qf, my_tiles, my_tiles + AM_TILE * HD, base, row_pos, len, window, sl2, m, l, o, lane);
+        tile_step_split<HD>(qf, my_tiles, my_tiles + AM_TILE * HD, base, row_pos, len, window, sl2, m, l, o, lane);
     }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
         l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
     }
-    // the warps' partial results meet in shared memory: [warp][16 rows][HD + 2]
+    const bool single = (run_end - run_first) == 1;
+    if (WARPS == 1) {
+        // one warp: its registers are the run's result
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = g + 8 * h, head_in = chunk * Gc + r;
+            if (r >= Gc || head_in >= G) continue;
+            const int head = kvh * G + head_in;
+            if (single) {
+                const float inv = 1.f / l[h];
+                bf16* dst = out + ((size_t)b * Hq + head) * HD;
+#pragma unroll
+                for (int d = 0; d < HD / 8; ++d)
+                    *reinterpret_cast<uint32_t*>(dst + 8 * d + 2 * t) = pack_bf16(o[d][2 * h] * inv, o[d][2 * h + 1] * inv);
+            } else {
+                const size_t at = ((size_t)b * Hq + head) * max_runs + run;
+                float* dst = part_acc + at * HD;
+#pragma unroll
+                for (int d = 0; d < HD / 8; ++d)
+                    *reinterpret_cast<float2*>(dst + 8 * d + 2 * t) = make_float2(o[d][2 * h], o[d][2 * h + 1]);
+                if (t == 0) { part_m[at] = m[h] * scale; part_l[at] = l[h]; }   // the combine kernel works with scaled scores
+            }
+        }
+        return;
+    }
+    // several warps: their partial results meet in shared memory, [warp][16 rows][HD + 2]
     __syncthreads();
     float* merge = reinterpret_cast<float*>(smem_raw);
     constexpr int RS = HD + 2;
@@ -315,16 +356,15 @@ attn_mma_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
         if (t == 0) { row[HD] = m[h]; row[HD + 1] = l[h]; }
     }
     __syncthreads();
-    const bool single = (run_end - run_first) == 1;
     for (int idx = threadIdx.x; idx < Gc * HD; idx += blockDim.x) {
         const int r = idx / HD, d = idx - r * HD, head_in = chunk * Gc + r;
         if (head_in >= G) continue;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < AM_WARPS; ++w) M = fmaxf(M, merge[((size_t)w * 16 + r) * RS + HD]);
+        for (int w = 0; w < WARPS; ++w) M = fmaxf(M, merge[((size_t)w * 16 + r) * RS + HD]);
         float L = 0.f, acc = 0.f;
 #pragma unroll
-        for (int w = 0; w < AM_WARPS; ++w) {
+        for (int w = 0; w < WARPS; ++w) {
             const float* row = merge + ((size_t)w * 16 + r) * RS;
             const float f = row[HD] == -INFINITY ? 0.f : exp2f((row[HD] - M) * sl2);
             L += row[HD + 1] * f;
@@ -399,21 +439,21 @@ extern "C" int qwb_attn_mma_prefill(const void* q, const void* k_pool, const voi
     return launch_prefill<128>(q, k_pool, v_pool, page_table, cu_seqlens, pos0, out, B, max_new, Hq, Hkv, table_width, scale, window, stream);
 }
 
-template <int HD>
+template <int HD, int WARPS>
 static int launch_decode(const void* q, const void* k_pool, const void* v_pool, const int* page_table, const int* seq_len,
                          float* scratch, void* out, int B, int Hq, int Hkv, int table_width, float scale, int window,
                          int split_tokens, int max_runs, cudaStream_t stream) {
     const int G = Hq / Hkv, Gc = group_chunk(G), chunks = (G + Gc - 1) / Gc;
-    size_t smem = (size_t)AM_WARPS * 2 * AM_TILE * HD * sizeof(bf16);
-    const size_t merge = (size_t)AM_WARPS * 16 * (HD + 2) * sizeof(float);
+    size_t smem = (size_t)WARPS * 2 * AM_TILE * HD * sizeof(bf16);
+    const size_t merge = (size_t)WARPS * 16 * (HD + 2) * sizeof(float);
     if (merge > smem) smem = merge;
-    cudaError_t e = cudaFuncSetAttribute(attn_mma_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_mma_decode_kernel<HD, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "attn_mma_decode: %s", cudaGetErrorString(e));
     float* part_acc = scratch;
     float* part_m = scratch + (size_t)B * Hq * max_runs * HD;
     float* part_l = part_m + (size_t)B * Hq * max_runs;
     dim3 grid(max_runs, Hkv * chunks, B);
-    qwb_launch(attn_mma_decode_kernel<HD>, grid, AM_WARPS * 32, smem, stream, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
+    qwb_launch(attn_mma_decode_kernel<HD, WARPS>, grid, WARPS * 32, smem, stream, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
         page_table, seq_len, part_acc, part_m, part_l, (bf16*)out, Hq, Hkv, table_width, scale, window, split_tokens, max_runs,
         Gc, chunks);
     if (int rc = qwb_check_launch("attn_mma_decode")) return rc;
@@ -425,6 +465,18 @@ static int launch_decode(const void* q, const void* k_pool, const void* v_pool, 
     return 0;
 }
 
+template <int HD>
+static int launch_decode_warps(const void* q, const void* k_pool, const void* v_pool, const int* page_table, const int* seq_len,
+                               float* scratch, void* out, int B, int Hq, int Hkv, int table_width, float scale, int window,
+                               int split_tokens, int max_runs, cudaStream_t stream) {
+    const int pages = split_tokens / AM_TILE;
+#define AM_ARGS q, k_pool, v_pool, page_table, seq_len, scratch, out, B, Hq, Hkv, table_width, scale, window, split_tokens, max_runs, stream
+    if (pages <= 1) return launch_decode<HD, 1>(AM_ARGS);
+    if (pages == 2) return launch_decode<HD, 2>(AM_ARGS);
+    return launch_decode<HD, 4>(AM_ARGS);
+#undef AM_ARGS
+}
+
 // bfloat16 only.  Arguments as qwb_attn_decode (scratch of the same size).
 extern "C" int qwb_attn_mma_decode(const void* q, const void* k_pool, const void* v_pool, const int* page_table,
                                    const int* seq_len, float* scratch, void* out, int B, int Hq, int Hkv, int hd, int page_size,
@@ -434,6 +486,6 @@ extern "C" int qwb_attn_mma_decode(const void* q, const void* k_pool, const void
     if (split_tokens <= 0 || split_tokens % AM_TILE || max_runs <= 0)
         return qwb_fail(QWB_ERR_ARG, "attn_mma_decode: run of %d keys is not a multiple of %d, or %d runs", split_tokens, AM_TILE, max_runs);
     if (max_runs > 1 && !scratch) return qwb_fail(QWB_ERR_ARG, "attn_mma_decode: %d runs need scratch memory", max_runs);
-    if (hd == 64) return launch_decode<64>(q, k_pool, v_pool, page_table, seq_len, scratch, out, B, Hq, Hkv, table_width, scale, window, split_tokens, max_runs, stream);
-    return launch_decode<128>(q, k_pool, v_pool, page_table, seq_len, scratch, out, B, Hq, Hkv, table_width, scale, window, split_tokens, max_runs, stream);
+    if (hd == 64) return launch_decode_warps<64>(q, k_pool, v_pool, page_table, seq_len, scratch, out, B, Hq, Hkv, table_width, scale, window, split_tokens, max_runs, stream);
+    return launch_decode_warps<128>(q, k_pool, v_pool, page_table, seq_len, scratch, out, B, Hq, Hkv, table_width, scale, window, split_tokens, max_runs, stream);
 }

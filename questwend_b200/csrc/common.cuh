@@ -37,21 +37,24 @@ static int qwb_check_launch(const char* what) {
 
 typedef __nv_bfloat16 bf16;
 
-// Programmatic dependent launch.  Every kernel of this library is launched with the
-// programmatic-serialization attribute and begins with pdl_wait(): the kernel may be
-// scheduled while its predecessor in the stream is still draining, and waits here until the
-// predecessor has finished and its writes are visible.  What a kernel does before pdl_wait()
-// must not depend on the predecessor (weights may be prefetched, nothing may be written).
-// pdl_launch_dependents() lets the successor be scheduled early in the same way.  (The
-// reference's CUDA back end has the same hooks, ggml-cuda/common.cuh:123-129.)
+// Programmatic dependent launch.  Every kernel of this library begins with pdl_wait() and can be
+// launched with the programmatic-serialization attribute: the kernel may then be scheduled while
+// its predecessor in the stream is still draining, and waits at pdl_wait() until the predecessor
+// has finished and its writes are visible.  What a kernel does before pdl_wait() must not depend
+// on the predecessor (weights may be prefetched, nothing may be written).  pdl_launch_dependents()
+// lets the successor be scheduled early in the same way.  Without the attribute both instructions
+// do nothing.  The attribute is off unless QWB200_PDL=1 is set: on a Qwen3-8B-sized decode step
+// (batch 8) the step took 4.77 ms with it and 4.49 ms without, because the early blocks of the next
+// kernel take room on the SMs from the running one.  (The reference's CUDA back end has the same
+// hooks, ggml-cuda/common.cuh:123-129.)
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 static bool qwb_pdl_enabled() {
     static int on = -1;
     if (on < 0) {
-        const char* e = getenv("QWB200_NO_PDL");
-        on = (e && e[0] && e[0] != '0') ? 0 : 1;
+        const char* e = getenv("QWB200_PDL");
+        on = (e && e[0] && e[0] != '0') ? 1 : 0;
     }
     return on == 1;
 }

@@ -73,7 +73,7 @@ def bench_gemm(M: int, N: int, K: int, impl: str, iters: int, dtype=torch.bfloat
             "GBps": nbytes / us / 1e3, "TFLOPs": 2.0 * M * N * K / us / 1e6}
 
 
-def bench_attn_decode(B, ctx, Hq, Hkv, hd, iters, dtype=torch.bfloat16, split=256) -> dict:
+def bench_attn_decode(B, ctx, Hq, Hkv, hd, iters, dtype=torch.bfloat16, split=64) -> dict:
     page = ops.PAGE_SIZE
     pages_per = math.ceil(ctx / page)
     per_copy = B * pages_per
@@ -136,6 +136,7 @@ def main() -> int:
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--tile-n", type=int, default=None)
+    ap.add_argument("--split", type=int, default=64, help="keys per run of the decode attention kernel")
     args = ap.parse_args()
     dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
     if args.what == "gemm":
@@ -147,7 +148,7 @@ def main() -> int:
             r["name"] = name
             print(json.dumps(r))
     elif args.what == "attn_decode":
-        print(json.dumps(bench_attn_decode(args.batch, args.ctx, args.heads, args.kv_heads, args.head_dim, args.iters, dtype)))
+        print(json.dumps(bench_attn_decode(args.batch, args.ctx, args.heads, args.kv_heads, args.head_dim, args.iters, dtype, args.split)))
     elif args.what == "attn_prefill":
         print(json.dumps(bench_attn_prefill(args.tokens, args.heads, args.kv_heads, args.head_dim, args.iters, dtype)))
     else:

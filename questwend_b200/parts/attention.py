@@ -14,7 +14,8 @@ from .base import KVSpec, Mixer
 from .linear import linear
 from .registry import register_mixer
 
-DECODE_SPLIT_TOKENS = 256     # keys per run of the decode kernel; fixed, so results do not depend on the batch
+DECODE_SPLIT_TOKENS = 256     # keys per run of the plain decode kernel; fixed, so results do not depend on the batch
+DECODE_SPLIT_TOKENS_MMA = 64  # the same for the tensor-core kernel: one page, one warp, one block
 
 
 class GroupedQueryAttention(Mixer):
@@ -84,8 +85,10 @@ class GroupedQueryAttention(Mixer):
                                    cache.k_pool, cache.v_pool, self.n_heads, self.n_kv_heads, self.head_dim,
                                    self.rotary_dim, self.eps, store_kv=cache.writable)
         if ctx.single_token:
+            mma = ops.mma_attention_fits(q.dtype, self.head_dim, cache.k_pool.shape[2])
             att = ops.attn_decode(q, cache.k_pool, cache.v_pool, table, ctx.seq_len, self.scale, ctx.max_len,
-                                  window=self.window, split_tokens=DECODE_SPLIT_TOKENS)
+                                  window=self.window,
+                                  split_tokens=DECODE_SPLIT_TOKENS_MMA if mma else DECODE_SPLIT_TOKENS)
         else:
             att = ops.attn_prefill(q, cache.k_pool, cache.v_pool, table, ctx.cu_seqlens, ctx.pos0, ctx.max_new,
                                    self.scale, window=self.window)

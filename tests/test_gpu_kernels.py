@@ -219,7 +219,7 @@ def test_attn_decode(dtype, Hq, Hkv, hd, window, split, page):
 
 
 @pytest.mark.parametrize("Hq,Hkv,hd", [(8, 2, 64), (8, 1, 128), (4, 4, 128), (12, 1, 64), (32, 1, 128), (6, 2, 128)])
-@pytest.mark.parametrize("window,split", [(0, 128), (100, 64), (0, 256), (0, 512), (300, 256)])
+@pytest.mark.parametrize("window,split", [(0, 128), (100, 64), (0, 64), (0, 256), (0, 512), (300, 256)])
 def test_attn_decode_tensor_cores(Hq, Hkv, hd, window, split):
     _attn_decode_case(torch.bfloat16, Hq, Hkv, hd, window, split, 64, "mma")
 

@@ -43,24 +43,28 @@ typedef __nv_bfloat16 bf16;
 // has finished and its writes are visible.  What a kernel does before pdl_wait() must not depend
 // on the predecessor (weights may be prefetched, nothing may be written).  pdl_launch_dependents()
 // lets the successor be scheduled early in the same way.  Without the attribute both instructions
-// do nothing.  The attribute is off unless QWB200_PDL=1 is set: on a Qwen3-8B-sized decode step
-// (batch 8) the step took 4.77 ms with it and 4.49 ms without, because the early blocks of the next
-// kernel take room on the SMs from the running one.  (The reference's CUDA back end has the same
-// hooks, ggml-cuda/common.cuh:123-129.)
+// do nothing.  Giving the attribute to every kernel made a Qwen3-8B-sized decode step (batch 8)
+// slower, 4.77 ms against 4.49 ms: the early blocks of the next kernel take room on the SMs from the
+// running one.  So only kernels that gain from an early start get it (qwb_launch_early).  (The
+// reference's CUDA back end has the same hooks, ggml-cuda/common.cuh:123-129.)
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-static bool qwb_pdl_enabled() {
-    static int on = -1;
-    if (on < 0) {
+// QWB200_PDL: unset or "some" = only the kernels that ask for it (qwb_launch_early: the weight-streaming
+// product, whose first loads do not depend on the kernel before it); "all" = every kernel; "0" = none.
+static int qwb_pdl_mode() {
+    static int mode = -1;
+    if (mode < 0) {
         const char* e = getenv("QWB200_PDL");
-        on = (e && e[0] && e[0] != '0') ? 1 : 0;
+        if (!e || !e[0] || e[0] == 's') mode = 1;
+        else if (e[0] == 'a') mode = 2;
+        else mode = 0;
     }
-    return on == 1;
+    return mode;
 }
 
 template <typename... KArgs, typename... Args>
-static cudaError_t qwb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+static cudaError_t qwb_launch_attr(bool early, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -70,8 +74,19 @@ static cudaError_t qwb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = qwb_pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = early ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+static cudaError_t qwb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    return qwb_launch_attr(qwb_pdl_mode() == 2, kernel, grid, block, smem, stream, args...);
+}
+
+// For a kernel that has useful work before pdl_wait(): it may start while the kernel before it still runs.
+template <typename... KArgs, typename... Args>
+static cudaError_t qwb_launch_early(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    return qwb_launch_attr(qwb_pdl_mode() >= 1, kernel, grid, block, smem, stream, args...);
 }
 
 __device__ __forceinline__ float to_f32(float x) { return x; }

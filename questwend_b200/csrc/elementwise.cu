@@ -48,28 +48,88 @@ extern "C" int qwb_embed_gather(const int* ids, const void* table, int table_dty
 //   out    [n_rows, D]  float or bfloat16
 // One block per output row; the row is kept in shared memory between the two passes.
 // ---------------------------------------------------------------------------------
-template <typename TOut>
+template <typename TOut> struct Pack4;
+template <> struct Pack4<float> {
+    static __device__ __forceinline__ void store(float* p, float a, float b, float c, float d) {
+        *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+    }
+};
+template <> struct Pack4<bf16> {
+    static __device__ __forceinline__ void store(bf16* p, float a, float b, float c, float d) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+        uint2 v;
+        v.x = *reinterpret_cast<uint32_t*>(&lo);
+        v.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p) = v;
+    }
+};
+
+// VEC: rows are a multiple of 4 wide and 16-byte aligned, so everything moves four values at a time.
+template <typename TOut, bool VEC>
 __global__ void rmsnorm_kernel(const float* x, const float* __restrict__ delta,
                                float* sum_out, const float* __restrict__ w, TOut* __restrict__ out,
                                const int* __restrict__ rows, int D, float eps) {
     pdl_wait();
     pdl_launch_dependents();
-    extern __shared__ float row_cache[];
+    extern __shared__ __align__(16) float row_cache[];
     __shared__ float red[32];
     const int r = blockIdx.x;
     const size_t src = (size_t)(rows ? rows[r] : r) * D;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) {
-        float v = x[src + i];
-        if (delta) v += delta[src + i];
-        if (sum_out) sum_out[src + i] = v;
-        row_cache[i] = v;
-        ss += v * v;
+    if (VEC) {
+        const float4* x4 = reinterpret_cast<const float4*>(x + src);
+        const float4* d4 = delta ? reinterpret_cast<const float4*>(delta + src) : nullptr;
+        float4* s4 = sum_out ? reinterpret_cast<float4*>(sum_out + src) : nullptr;
+        float4* c4 = reinterpret_cast<float4*>(row_cache);
+        for (int i = threadIdx.x; i < D / 4; i += blockDim.x) {
+            float4 v = x4[i];
+            if (d4) { const float4 d = d4[i]; v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w; }
+            if (s4) s4[i] = v;
+            c4[i] = v;
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    } else {
+        for (int i = threadIdx.x; i < D; i += blockDim.x) {
+            float v = x[src + i];
+            if (delta) v += delta[src + i];
+            if (sum_out) sum_out[src + i] = v;
+            row_cache[i] = v;
+            ss += v * v;
+        }
     }
     const float total = block_sum(ss, red);
     const float scale = rsqrtf(total / (float)D + eps);
     TOut* o = out + (size_t)r * D;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = from_f32<TOut>(row_cache[i] * scale * w[i]);
+    if (VEC) {
+        const float4* c4 = reinterpret_cast<const float4*>(row_cache);
+        const float4* w4 = reinterpret_cast<const float4*>(w);
+        for (int i = threadIdx.x; i < D / 4; i += blockDim.x) {
+            const float4 v = c4[i], g = w4[i];
+            Pack4<TOut>::store(o + 4 * i, v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z, v.w * scale * g.w);
+        }
+    } else {
+        for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = from_f32<TOut>(row_cache[i] * scale * w[i]);
+    }
+}
+
+template <typename TOut>
+static int launch_rmsnorm(const float* x, const float* delta, float* sum_out, const float* w, TOut* out, const int* rows,
+                          int n_rows, int D, float eps, size_t smem, cudaStream_t stream) {
+    const bool vec = D % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0 &&
+                     (!delta || (uintptr_t)delta % 16 == 0) && (!sum_out || (uintptr_t)sum_out % 16 == 0);
+    const int work = vec ? D / 4 : D;
+    const int block = work >= 1024 ? 256 : (work >= 256 ? 128 : 64);
+    cudaError_t e = cudaSuccess;
+    if (vec) {
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_kernel<TOut, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "rmsnorm: %s", cudaGetErrorString(e));
+        qwb_launch(rmsnorm_kernel<TOut, true>, n_rows, block, smem, stream, x, delta, sum_out, w, out, rows, D, eps);
+    } else {
+        if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_kernel<TOut, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "rmsnorm: %s", cudaGetErrorString(e));
+        qwb_launch(rmsnorm_kernel<TOut, false>, n_rows, block, smem, stream, x, delta, sum_out, w, out, rows, D, eps);
+    }
+    return qwb_check_launch("rmsnorm");
 }
 
 extern "C" int qwb_rmsnorm(const float* x, const float* delta, float* sum_out, const float* w,
@@ -79,20 +139,9 @@ extern "C" int qwb_rmsnorm(const float* x, const float* delta, float* sum_out, c
     if (D <= 0) return qwb_fail(QWB_ERR_ARG, "rmsnorm: bad width %d", D);
     const size_t smem = (size_t)D * sizeof(float);
     if (smem > 200 * 1024) return qwb_fail(QWB_ERR_ARG, "rmsnorm: width %d does not fit in shared memory (max %d)", D, 200 * 1024 / 4);
-    const int block = D >= 2048 ? 512 : (D >= 512 ? 256 : 128);
-    cudaError_t e = cudaSuccess;
-    if (out_dtype == QWB_DT_F32) {
-        if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "rmsnorm: %s", cudaGetErrorString(e));
-        qwb_launch(rmsnorm_kernel<float>, n_rows, block, smem, stream, x, delta, sum_out, w, (float*)out, rows, D, eps);
-    } else if (out_dtype == QWB_DT_BF16) {
-        if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "rmsnorm: %s", cudaGetErrorString(e));
-        qwb_launch(rmsnorm_kernel<bf16>, n_rows, block, smem, stream, x, delta, sum_out, w, (bf16*)out, rows, D, eps);
-    } else {
-        return qwb_fail(QWB_ERR_ARG, "rmsnorm: unknown dtype %d", out_dtype);
-    }
-    return qwb_check_launch("rmsnorm");
+    if (out_dtype == QWB_DT_F32) return launch_rmsnorm<float>(x, delta, sum_out, w, (float*)out, rows, n_rows, D, eps, smem, stream);
+    if (out_dtype == QWB_DT_BF16) return launch_rmsnorm<bf16>(x, delta, sum_out, w, (bf16*)out, rows, n_rows, D, eps, smem, stream);
+    return qwb_fail(QWB_ERR_ARG, "rmsnorm: unknown dtype %d", out_dtype);
 }
 
 // ---------------------------------------------------------------------------------

@@ -129,9 +129,9 @@ extern "C" int qwb_gemm_stream(const void* x, const void* W, const float* residu
     const int grid = (N + GS_ROWS - 1) / GS_ROWS;
     const bf16* xp = (const bf16*)x;
     const bf16* wp = (const bf16*)W;
-    if (M <= 8) qwb_launch(gemm_stream_kernel<1>, grid, GS_WARPS * 32, 0, stream, xp, wp, residual, y, M, N, K);
-    else if (M <= 16) qwb_launch(gemm_stream_kernel<2>, grid, GS_WARPS * 32, 0, stream, xp, wp, residual, y, M, N, K);
-    else if (M <= 32) qwb_launch(gemm_stream_kernel<4>, grid, GS_WARPS * 32, 0, stream, xp, wp, residual, y, M, N, K);
-    else qwb_launch(gemm_stream_kernel<8>, grid, GS_WARPS * 32, 0, stream, xp, wp, residual, y, M, N, K);
+    if (M <= 8) qwb_launch_early(gemm_stream_kernel<1>, grid, GS_WARPS * 32, 0, stream, xp, wp, residual, y, M, N, K);
+    else if (M <= 16) qwb_launch_early(gemm_stream_kernel<2>, grid, GS_WARPS * 32, 0, stream, xp, wp, residual, y, M, N, K);
+    else if (M <= 32) qwb_launch_early(gemm_stream_kernel<4>, grid, GS_WARPS * 32, 0, stream, xp, wp, residual, y, M, N, K);
+    else qwb_launch_early(gemm_stream_kernel<8>, grid, GS_WARPS * 32, 0, stream, xp, wp, residual, y, M, N, K);
     return qwb_check_launch("gemm_stream");
 }

@@ -4,12 +4,13 @@
 //       EPI_ADD     y += product, y float                 (o and down projections onto the residual stream)
 //       EPI_SWIGLU  a = silu(gate) * up as bfloat16       (gate/up projection; W holds the F gate rows, then the F up rows)
 //
-// One block makes one 128 x BN tile of y.  Six warps with fixed roles:
+// One block per SM walks over 128 x BN tiles of y (tile t, t + blocks, ...).  Six warps with fixed roles:
 //   warp 0  one lane issues the TMA loads: per 64 columns of k a 128 x 64 tile of x and a BN x 64 tile of W, into a ring
 //           of shared-memory stages in the 128-byte swizzle that the tensor core reads; each stage has a "full" mbarrier
 //           that the loads complete and an "empty" mbarrier that the tensor core releases;
-//   warp 1  allocates BN columns of tensor memory; one lane issues four tcgen05.mma (128 x BN x 16) per stage straight
-//           from shared memory, commits the stage's "empty" barrier after them and, at the end, the accumulator's barrier;
+//   warp 1  allocates 2 x BN columns of tensor memory (two accumulators, so that one tile's epilogue runs under the next
+//           tile's products); one lane issues four tcgen05.mma (128 x BN x 16) per stage straight from shared memory,
+//           commits the stage's "empty" barrier after them and, after a tile's last stage, the accumulator's "full" barrier;
 //   warps 2-5  wait for the accumulator, read it with tcgen05.ld (each warp its own 32 lanes = 32 rows of the tile), stage
 //           it in shared memory and hand it to TMA: a store, or a reduce-add onto y for the residual sum.  A thread owns a
 //           row, so the SwiGLU epilogue finds gate and up of one feature in the same thread.
@@ -110,7 +111,7 @@ template <int BN>
 struct TcSmem {
     static constexpr int STAGES = TcStages<BN>::value;
     static constexpr size_t A_BYTES = (size_t)TC_BM * TC_BK * 2, B_BYTES = (size_t)BN * TC_BK * 2;
-    static constexpr size_t BYTES = 1024 + STAGES * (A_BYTES + B_BYTES) + 8 * TC_STAGING_BYTES + 256;   // 1024: to align
+    static constexpr size_t BYTES = 1024 + STAGES * (A_BYTES + B_BYTES) + 8 * TC_STAGING_BYTES + 512;   // 1024: to align
 };
 
 template <int BN, int EPI>
@@ -119,6 +120,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                const __grid_constant__ CUtensorMap map_out, int M, int N, int K, int up_row0, int* error) {
     constexpr int STAGES = TcSmem<BN>::STAGES;
     constexpr uint32_t A_BYTES = TcSmem<BN>::A_BYTES, B_BYTES = TcSmem<BN>::B_BYTES;
+    constexpr int COLS_PER_TILE = EPI == EPI_SWIGLU ? BN / 2 : BN;     // output columns of one tile
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* a_tiles = tiles;
@@ -126,92 +128,113 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     unsigned char* staging = b_tiles + STAGES * B_BYTES;              // [4 warps][2][32 rows][128 bytes]
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(staging + 4 * 2 * TC_STAGING_BYTES);
     uint64_t* empty_bar = full_bar + STAGES;
-    uint64_t* acc_bar = empty_bar + STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+    uint64_t* acc_full = empty_bar + STAGES;                          // [2]: the tensor core has finished a tile
+    uint64_t* acc_empty = acc_full + 2;                               // [2]: the epilogue has read a tile out
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // Blocks that run together share a tile of W: the row tiles are the fast index, so W streams from HBM once and the
-    // (much smaller) x stays in L2.
-    const int n0 = blockIdx.y * (EPI == EPI_SWIGLU ? BN / 2 : BN);          // first output column (feature) of the tile
-    const int m0 = blockIdx.x * TC_BM;
     const int k_blocks = (K + TC_BK - 1) / TC_BK;
+    // The block walks over tiles first, first + gridDim.x, ...  Tiles are numbered with the row tile as the fast index:
+    // blocks that run together share tiles of W, so W streams from HBM once and the (much smaller) x stays in L2.
+    const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + COLS_PER_TILE - 1) / COLS_PER_TILE;
+    const int n_total = m_tiles * n_tiles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        mbar_init(acc_bar, 1);
+        for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) tmem_alloc(tmem_slot, BN);
+    if (warp == 1) tmem_alloc(tmem_slot, 2 * BN);                     // two accumulators: one fills while the other drains
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_acc = *tmem_slot;
+    const uint32_t tmem_base = *tmem_slot;
 
     pdl_wait();                 // x comes from the kernel before this one
     pdl_launch_dependents();
 
     if (warp == 0) {
         if (lane == 0) {
-            int issued = 0;
+            int it = 0;                                               // k blocks issued so far, over all tiles
             bool ok = true;
-            for (int kb = 0; kb < k_blocks && ok; ++kb) {
-                const int s = kb % STAGES;
-                if (kb >= STAGES) ok = mbar_wait(&empty_bar[s], ((kb / STAGES) - 1) & 1);
-                if (!ok) break;
-                mbar_expect_tx(&full_bar[s], A_BYTES + B_BYTES);
-                tma_load_2d(a_tiles + (size_t)s * A_BYTES, &map_x, &full_bar[s], kb * TC_BK, m0);
-                if (EPI == EPI_SWIGLU) {
-                    tma_load_2d(b_tiles + (size_t)s * B_BYTES, &map_w, &full_bar[s], kb * TC_BK, n0);
-                    tma_load_2d(b_tiles + (size_t)s * B_BYTES + B_BYTES / 2, &map_w, &full_bar[s], kb * TC_BK, up_row0 + n0);
-                } else {
-                    tma_load_2d(b_tiles + (size_t)s * B_BYTES, &map_w, &full_bar[s], kb * TC_BK, n0);
+            for (int tile = blockIdx.x; tile < n_total && ok; tile += gridDim.x) {
+                const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * COLS_PER_TILE;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (it >= STAGES) ok = mbar_wait(&empty_bar[s], ((it / STAGES) - 1) & 1);
+                    if (!ok) break;
+                    mbar_expect_tx(&full_bar[s], A_BYTES + B_BYTES);
+                    tma_load_2d(a_tiles + (size_t)s * A_BYTES, &map_x, &full_bar[s], kb * TC_BK, m0);
+                    if (EPI == EPI_SWIGLU) {
+                        tma_load_2d(b_tiles + (size_t)s * B_BYTES, &map_w, &full_bar[s], kb * TC_BK, n0);
+                        tma_load_2d(b_tiles + (size_t)s * B_BYTES + B_BYTES / 2, &map_w, &full_bar[s], kb * TC_BK, up_row0 + n0);
+                    } else {
+                        tma_load_2d(b_tiles + (size_t)s * B_BYTES, &map_w, &full_bar[s], kb * TC_BK, n0);
+                    }
                 }
-                issued = kb + 1;
             }
             if (!ok) {
                 atomicExch(error, 1);
                 // loads already issued still write shared memory: wait for them (bounded) before the block ends
-                for (int kb = max(0, issued - STAGES); kb < issued; ++kb) mbar_wait(&full_bar[kb % STAGES], (kb / STAGES) & 1);
+                for (int j = max(0, it - STAGES); j < it; ++j) mbar_wait(&full_bar[j % STAGES], (j / STAGES) & 1);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc(TC_BM, BN);
+            int it = 0, local = 0;
             bool ok = true;
-            for (int kb = 0; kb < k_blocks; ++kb) {
-                const int s = kb % STAGES;
-                ok = mbar_wait(&full_bar[s], (kb / STAGES) & 1);
+            for (int tile = blockIdx.x; tile < n_total && ok; tile += gridDim.x, ++local) {
+                const int buf = local & 1;
+                if (local >= 2) ok = mbar_wait(&acc_empty[buf], ((local >> 1) - 1) & 1);   // the epilogue is done with it
                 if (!ok) break;
                 tc_fence_after();
-                const uint64_t da = make_smem_desc(a_tiles + (size_t)s * A_BYTES);
-                const uint64_t db = make_smem_desc(b_tiles + (size_t)s * B_BYTES);
+                const uint32_t tmem_acc = tmem_base + (uint32_t)(buf * BN);
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(&full_bar[s], (it / STAGES) & 1);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t da = make_smem_desc(a_tiles + (size_t)s * A_BYTES);
+                    const uint64_t db = make_smem_desc(b_tiles + (size_t)s * B_BYTES);
 #pragma unroll
-                for (int k = 0; k < TC_BK / 16; ++k)          // 16 columns of k = 32 bytes = 2 units of the start address
-                    umma_bf16(tmem_acc, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-                umma_commit(&empty_bar[s]);                   // arrives when these MMAs have read the stage
+                    for (int k = 0; k < TC_BK / 16; ++k)      // 16 columns of k = 32 bytes = 2 units of the start address
+                        umma_bf16(tmem_acc, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(&empty_bar[s]);               // arrives when these MMAs have read the stage
+                }
+                umma_commit(&acc_full[buf]);                  // arrives when every MMA issued so far is done
             }
-            if (!ok) atomicExch(error, 2);
-            umma_commit(acc_bar);                             // arrives when every MMA issued so far is done
+            if (!ok) {
+                atomicExch(error, 2);
+                umma_commit(&acc_full[0]);                    // let the epilogue warps run out instead of timing out one by one
+                umma_commit(&acc_full[1]);
+            }
         }
     } else {
-        const bool ok = mbar_wait(acc_bar, 0);
-        tc_fence_after();
-        if (!ok) {
-            if (lane == 0) atomicExch(error, 3);
-        } else {
-            // Each warp owns 32 rows.  Per chunk of output columns it moves its accumulator lanes into a staging tile in
-            // shared memory (rows of 128 bytes, 16-byte pieces XOR-swizzled by the row so that neither these writes nor
-            // the TMA unit meet bank conflicts) and one lane hands the tile to TMA: a store, or an add onto global memory
-            // for the residual sum.  Two staging tiles per warp let the next chunk be prepared while the last one drains.
-            const int lane_group = warp & 3;                  // a warp reads tensor-memory lanes [32 * (warp % 4), + 32)
+        // Each warp owns 32 rows.  Per chunk of output columns it moves its accumulator lanes into a staging tile in
+        // shared memory (rows of 128 bytes, 16-byte pieces XOR-swizzled by the row so that neither these writes nor
+        // the TMA unit meet bank conflicts) and one lane hands the tile to TMA: a store, or an add onto global memory
+        // for the residual sum.  Two staging tiles per warp let the next chunk be prepared while the last one drains.
+        const int lane_group = warp & 3;                      // a warp reads tensor-memory lanes [32 * (warp % 4), + 32)
+        unsigned char* stage0 = staging + (size_t)lane_group * 2 * TC_STAGING_BYTES;
+        constexpr int CHUNKS = EPI == EPI_SWIGLU ? BN / 2 / 64 : BN / 32;
+        int local = 0, stores = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_total && ok; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            const int m0 = (tile % m_tiles) * TC_BM, n0 = (tile / m_tiles) * COLS_PER_TILE;
+            ok = mbar_wait(&acc_full[buf], (local >> 1) & 1);
+            tc_fence_after();
+            if (!ok) {
+                if (lane == 0) atomicExch(error, 3);
+                break;
+            }
             const int row0 = m0 + 32 * lane_group;
-            const uint32_t taddr = tmem_acc + ((uint32_t)(32 * lane_group) << 16);
-            unsigned char* stage0 = staging + (size_t)lane_group * 2 * TC_STAGING_BYTES;
-            constexpr int CHUNKS = EPI == EPI_SWIGLU ? BN / 2 / 64 : BN / 32;
+            const uint32_t taddr = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(32 * lane_group) << 16);
 #pragma unroll 1
-            for (int ch = 0; ch < CHUNKS; ++ch) {
-                unsigned char* st = stage0 + (size_t)(ch & 1) * TC_STAGING_BYTES;
-                if (ch >= 2) {                                // the store that read this tile two chunks ago must be done
+            for (int ch = 0; ch < CHUNKS; ++ch, ++stores) {
+                unsigned char* st = stage0 + (size_t)(stores & 1) * TC_STAGING_BYTES;
+                if (stores >= 2) {                            // the store that read this tile two chunks ago must be done
                     if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
                     __syncwarp();
                 }
@@ -244,6 +267,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 #pragma unroll
                     for (int i = 0; i < 32; i += 4) my_row[(i / 4) ^ (lane & 7)] = make_uint4(v[i], v[i + 1], v[i + 2], v[i + 3]);
                 }
+                if (ch == CHUNKS - 1) {                       // the accumulator is read out: the tensor core may have it back
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
+                }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) {
@@ -257,15 +285,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
             }
-            if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // shared memory is read, global is written
-            __syncwarp();
         }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // shared memory is read, global is written
+        __syncwarp();
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_acc, BN);
+        tmem_dealloc(tmem_base, 2 * BN);
     }
 }
 
@@ -313,8 +341,14 @@ static int launch_tc(const void* x, const void* W, void* out, int M, int N, int 
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "gemm_tc: %s", cudaGetErrorString(e));
     const int cols_per_block = EPI == EPI_SWIGLU ? BN / 2 : BN;
-    dim3 grid((M + TC_BM - 1) / TC_BM, (N + cols_per_block - 1) / cols_per_block);
-    if (grid.y > 65535) return qwb_fail(QWB_ERR_ARG, "gemm_tc: %d column tiles are more than a grid takes", (int)grid.y);
+    const long long n_tiles = (long long)((M + TC_BM - 1) / TC_BM) * ((N + cols_per_block - 1) / cols_per_block);
+    static int n_sm = 0;
+    if (!n_sm) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
+    }
+    dim3 grid((unsigned)(n_tiles < n_sm ? n_tiles : n_sm));          // one block per SM, each walks over its tiles
     e = qwb_launch(gemm_tc_kernel<BN, EPI>, grid, TC_THREADS, smem, stream, map_x, map_w, map_out, M, N, K, N, error);
     if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "gemm_tc: launch failed: %s", cudaGetErrorString(e));
     return qwb_check_launch("gemm_tc");

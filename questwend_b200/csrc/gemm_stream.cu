@@ -1,7 +1,7 @@
-// Weight-streaming matrix product on the tensor cores, for up to 64 rows of bfloat16 x:
+// Weight-streaming matrix product on the tensor cores, for up to 16 rows of bfloat16 x:
 //     y[M,N] = x[M,K] W[N,K]^T (+ residual),  32-bit sums, y float.
 // A decode step reads every weight once and does little arithmetic per byte, so the only
-// goal is to keep HBM busy: each block owns 16 rows of W, its 8 warps split K between
+// goal is to keep HBM busy: each block owns 16 rows of W, its 8 or 16 warps split K between
 // them, every thread pulls its part of W straight from global memory into registers with
 // 16-byte loads that bypass L1 (W is used once; x stays cached), and feeds
 // mma.m16n8k16 with W as the 16-row operand and 8 rows of x as the 8-column operand
@@ -9,11 +9,11 @@
 // instruction wants pairs (2t, 2t+1) and (2t+8, 2t+9).  The sum over k does not care about
 // the order, so both operands use the same renumbering of k inside each block of 32 and
 // no shuffle is needed.  The warps' partial sums meet in shared memory and are added in
-// warp order, so a row's result depends neither on the batch nor on timing.
+// warp order; how K is split depends on N and K only, so a row's result depends neither on the
+// batch nor on timing.
 // (The reference's counterpart for few rows: ggml-cuda/mmvf.cu and mmf.cuh.)
 #include "common.cuh"
 
-#define GS_WARPS 8
 #define GS_ROWS 16
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
@@ -31,12 +31,11 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, uint32_t a0, uint32_t a
 }
 
 // NT = number of 8-row tiles of x handled at once (M <= 8 * NT).
-template <int NT>
+template <int NT, int U, int GS_WARPS>
 __global__ void __launch_bounds__(GS_WARPS * 32)
 gemm_stream_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const float* residual, float* y,
                    int M, int N, int K) {
     __shared__ float part[GS_WARPS][NT][4][32];          // [warp][tile][c register][lane]
-    constexpr int U = 4;                                  // blocks of 32 k whose loads are in flight together
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * GS_ROWS;
@@ -124,14 +123,23 @@ extern "C" int qwb_gemm_stream(const void* x, const void* W, const float* residu
                                cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8) return qwb_fail(QWB_ERR_ARG, "gemm_stream: inner size %d is not a multiple of 8", K);
-    if (M > 64) return qwb_fail(QWB_ERR_ARG, "gemm_stream: %d rows; this kernel is for at most 64", M);
+    if (M > 16) return qwb_fail(QWB_ERR_ARG, "gemm_stream: %d rows; this kernel is for at most 16", M);
     if ((uintptr_t)x % 16 || (uintptr_t)W % 16) return qwb_fail(QWB_ERR_ARG, "gemm_stream: operands must be 16-byte aligned");
     const int grid = (N + GS_ROWS - 1) / GS_ROWS;
     const bf16* xp = (const bf16*)x;
     const bf16* wp = (const bf16*)W;
-    if (M <= 8) qwb_launch_early(gemm_stream_kernel<1>, grid, GS_WARPS * 32, 0, stream, xp, wp, residual, y, M, N, K);
-    else if (M <= 16) qwb_launch_early(gemm_stream_kernel<2>, grid, GS_WARPS * 32, 0, stream, xp, wp, residual, y, M, N, K);
-    else if (M <= 32) qwb_launch_early(gemm_stream_kernel<4>, grid, GS_WARPS * 32, 0, stream, xp, wp, residual, y, M, N, K);
-    else qwb_launch_early(gemm_stream_kernel<8>, grid, GS_WARPS * 32, 0, stream, xp, wp, residual, y, M, N, K);
+    // How deep each warp prefetches (U blocks of 32 k) and how many warps split K, by what measured best at the sizes of
+    // a Qwen3-8B decode step: long rows want deep prefetch; short rows with few blocks want more warps; else shallow.
+#define GS_GO(NT, U, WARPS) qwb_launch_early(gemm_stream_kernel<NT, U, WARPS>, grid, WARPS * 32, 0, stream, xp, wp, residual, y, M, N, K)
+#define GS_PICK(NT)                                      \
+    do {                                                 \
+        if (K >= 8192) GS_GO(NT, 8, 8);                  \
+        else if (N <= 4096) GS_GO(NT, 2, 16);            \
+        else GS_GO(NT, 2, 8);                            \
+    } while (0)
+    if (M <= 8) GS_PICK(1);
+    else GS_PICK(2);
+#undef GS_PICK
+#undef GS_GO
     return qwb_check_launch("gemm_stream");
 }

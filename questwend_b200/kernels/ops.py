@@ -268,12 +268,11 @@ def gemm_small(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor | N
 
 
 STREAM_M = 16           # at most this many bfloat16 rows go to the tensor-core weight-streaming kernel
-                        # (it takes up to 64, but beyond 16 the library product is faster)
 
 
 def gemm_stream(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor | None = None,
                 out: torch.Tensor | None = None) -> torch.Tensor:
-    """bfloat16 x [M, K] times bfloat16 weight [N, K] transposed, as float32 [M, N] (+ residual), M <= 64."""
+    """bfloat16 x [M, K] times bfloat16 weight [N, K] transposed, as float32 [M, N] (+ residual), M <= 16."""
     _need(x, "x", torch.bfloat16, 2)
     _need(weight, "weight", torch.bfloat16, 2)
     M, K = x.shape

@@ -14,8 +14,10 @@ state for layers that have it (:115-116, 493-494), zeroed at start (:614-630).  
   page pool of its own and a page table of its own (one page id is valid in every
   unit of its group).  ``max_tokens`` sizes each pool: the most tokens that live
   sequences may hold together, each sequence's count rounded up to whole pages.
-* Nothing is zeroed when a page or slot is handed out again: kernels never read
-  beyond a sequence's length.  State tensors are the exception (a recurrent state
+* The pools are zeroed once, when they are made.  Nothing is zeroed when a page or
+  slot is handed out again: kernels never use what lies beyond a sequence's length
+  (the tensor-core kernels multiply it by probability 0, so it must be finite: it is
+  zero or an earlier sequence's keys and values).  State tensors are the exception (a recurrent state
   starts from zero), so a slot's state rows are zeroed when the slot is handed out.
 
 All bookkeeping is on the host; the device sees page tables and lengths.
@@ -129,8 +131,10 @@ class CacheManager:
                 self._unit_state[i] = _StateUnit(state, storage)
         for gid, (spec, members) in enumerate(by_spec.items()):
             shape = (len(members), self.n_pages, spec.n_kv_heads, PAGE_SIZE, spec.head_dim)
-            k = torch.empty(shape, dtype=dtype, device=self.device)
-            v = torch.empty(shape, dtype=dtype, device=self.device)
+            # zeroed once (the reference zeroes its cache too, core/runtime.cpp:614-630): a page's unused tail is
+            # multiplied by probability 0 in the tensor-core kernels and must hold finite numbers
+            k = torch.zeros(shape, dtype=dtype, device=self.device)
+            v = torch.zeros(shape, dtype=dtype, device=self.device)
             self._groups.append(_KVGroup(spec, members, FreeList(self.n_pages, "page"), k, v, {}))
             for j, u in enumerate(members):
                 self._unit_group[u] = (gid, j)

@@ -1,0 +1,428 @@
+// Prefill attention on the fifth-generation tensor cores (tcgen05), bfloat16, head sizes 64 and 128, groups of
+// 1, 2, 4, 8 or 16 query heads per key/value head, pages of 64 keys.  Same contract as attn_prefill in attention.cu.
+//
+// A block serves 128 rows = (128 / G tokens) x (the G query heads of one key/value head).  Per tile of 64 keys (one
+// cache page of that head):
+//     S = Q K^T      tcgen05.mma, Q and K from shared memory (TMA, 128-byte swizzle), S in tensor memory (64 columns)
+//     P = softmax    four warps, one thread per row: read S, mask, running maximum and sum in 32-bit, write P as
+//                    bfloat16 into shared memory in the layout the tensor core reads
+//     O += P V       tcgen05.mma, P and V from shared memory, O accumulates in tensor memory (HD columns).  V is read as
+//                    it lies in the cache ([key][d], d contiguous): the "MN-major" operand form.
+// O lives in tensor memory across the tiles.  It carries a reference maximum per row; when a tile raises a row's
+// maximum by more than 2^8 the row's O and sum are rescaled (read, scale, write back), else the old reference stays
+// and the probabilities are simply larger than 1 for a while: the result is the same, most tiles need no rescale.
+// Warp 0 loads (one lane), warp 1 issues the products (one lane) and owns the tensor memory, warps 2-5 do the softmax
+// and the final write.  Every wait is bounded; a wait that runs out raises *error and the block runs to its end.
+//
+// Keys of the last page beyond the sequence's length are masked in S; their V rows are multiplied by P = 0, so the
+// cache must hold finite numbers there (the cache is zeroed when it is made, and later holds only values that were
+// keys and values once).
+#include "common.cuh"
+
+#include <cuda.h>
+
+#define AT_ROWS 128
+#define AT_KEYS 64
+#define AT_THREADS 192
+#define AT_KV_STAGES 2
+#define AT_SPIN_LIMIT (1u << 22)
+#define AT_RESCALE_LOG2 8.f
+
+__device__ __forceinline__ uint32_t at_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void at_bar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(at_smem(bar)), "r"(count));
+}
+__device__ __forceinline__ void at_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(at_smem(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void at_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(at_smem(bar)) : "memory");
+}
+__device__ __forceinline__ bool at_wait(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < AT_SPIN_LIMIT; ++i) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(at_smem(bar)), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void at_tma_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(at_smem(dst)), "l"(map), "r"(at_smem(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void at_tma_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(at_smem(dst)), "l"(map), "r"(at_smem(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void at_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void at_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(at_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void at_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void at_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void at_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void at_st32(uint32_t taddr, const uint32_t* r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+                 "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                   "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                   "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                 : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// Operand descriptors, 128-byte swizzle, descriptor version 1.
+//   K-major (rows of 64 bfloat16 = 128 bytes, the contraction runs along the row): groups of 8 rows are 1024 bytes apart.
+__device__ __forceinline__ uint64_t at_desc_kmajor(const void* tile) {
+    return (uint64_t)((at_smem(tile) & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+//   MN-major (each row of 128 bytes holds 64 consecutive values of the non-contracted dimension for one index of the
+//   contraction): the next 64 values of the non-contracted dimension are `lbo_bytes` away, the next 8 indices of the
+//   contraction 1024 bytes.
+__device__ __forceinline__ uint64_t at_desc_mnmajor(const void* tile, uint32_t lbo_bytes) {
+    return (uint64_t)((at_smem(tile) & 0x3FFFF) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// D float, A and B bfloat16; b_mn: B is MN-major.
+__host__ __device__ constexpr uint32_t at_idesc(int m, int n, bool b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <int HD>
+struct AtSmem {
+    static constexpr int ATOMS = HD / 64;                                  // 128-byte pieces of a row of Q, K or V
+    static constexpr size_t Q_BYTES = (size_t)AT_ROWS * HD * 2;            // ATOMS blocks of [128 rows][128 bytes]
+    static constexpr size_t KV_BYTES = (size_t)AT_KEYS * HD * 2;           // ATOMS blocks of [64 keys][128 bytes]
+    static constexpr size_t P_BYTES = (size_t)AT_ROWS * AT_KEYS * 2;       // [128 rows][128 bytes]
+    static constexpr size_t BYTES = 1024 + Q_BYTES + 2 * AT_KV_STAGES * KV_BYTES + P_BYTES + 256;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(AT_THREADS)
+attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const int* __restrict__ page_table,
+                       const int* __restrict__ cu_seqlens, const int* __restrict__ pos0, bf16* __restrict__ out, int Hq, int Hkv,
+                       int table_width, float scale, int window, int G, int* error) {
+    constexpr int ATOMS = AtSmem<HD>::ATOMS;
+    constexpr uint32_t KV_BYTES = AtSmem<HD>::KV_BYTES;
+    constexpr uint32_t TMEM_COLS = HD == 128 ? 256 : 128;                   // S: 64 columns, O: HD columns
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* q_tile = base;
+    unsigned char* k_tiles = q_tile + AtSmem<HD>::Q_BYTES;
+    unsigned char* v_tiles = k_tiles + AT_KV_STAGES * KV_BYTES;
+    unsigned char* p_tile = v_tiles + AT_KV_STAGES * KV_BYTES;
+    uint64_t* q_full = reinterpret_cast<uint64_t*>(p_tile + AtSmem<HD>::P_BYTES);
+    uint64_t* kv_full = q_full + 1;
+    uint64_t* kv_empty = kv_full + AT_KV_STAGES;
+    uint64_t* s_full = kv_empty + AT_KV_STAGES;
+    uint64_t* p_full = s_full + 1;
+    uint64_t* o_full = p_full + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.z, kvh = blockIdx.y;
+    const int tok_per_block = AT_ROWS / G;
+    const int t0 = cu_seqlens[b], n_new = cu_seqlens[b + 1] - t0;
+    const int q0 = blockIdx.x * tok_per_block;
+    if (q0 >= n_new) return;
+    const int p0 = pos0[b];
+    const int len = p0 + n_new;
+    const int last_tok = min(n_new, q0 + tok_per_block) - 1;
+    const int k_last = p0 + last_tok;
+    const int k_first = window > 0 ? max(0, p0 + q0 - window + 1) : 0;
+    const int tile_first = k_first / AT_KEYS, tile_last = k_last / AT_KEYS;
+    const int n_tiles = tile_last - tile_first + 1;
+    const int* pages = page_table + (size_t)b * table_width;
+
+    if (threadIdx.x == 0) {
+        at_bar_init(q_full, 1);
+        for (int s = 0; s < AT_KV_STAGES; ++s) { at_bar_init(&kv_full[s], 1); at_bar_init(&kv_empty[s], 1); }
+        at_bar_init(s_full, 1);
+        at_bar_init(p_full, 4);
+        at_bar_init(o_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(at_smem(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    at_fence_before();
+    __syncthreads();
+    at_fence_after();
+    const uint32_t tmem_s = *tmem_slot;                 // S: columns [0, 64)
+    const uint32_t tmem_o = tmem_s + 64;                // O: columns [64, 64 + HD)
+
+    pdl_wait();
+    pdl_launch_dependents();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            at_expect_tx(q_full, (uint32_t)AtSmem<HD>::Q_BYTES);
+            for (int a = 0; a < ATOMS; ++a)             // rows (token, head of the group): a box of [128 / G tokens][G heads][64 d]
+                at_tma_3d(q_tile + (size_t)a * AT_ROWS * 128, &map_q, q_full, a * 64, kvh * G, t0 + q0);
+            bool ok = true;
+            int issued = 0;
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j % AT_KV_STAGES;
+                if (j >= AT_KV_STAGES) ok = at_wait(&kv_empty[s], ((j / AT_KV_STAGES) - 1) & 1);
+                if (!ok) break;
+                const int row0 = (pages[tile_first + j] * Hkv + kvh) * AT_KEYS;      // the (page, head) block's first row
+                at_expect_tx(&kv_full[s], 2 * KV_BYTES);
+                for (int a = 0; a < ATOMS; ++a) {
+                    at_tma_2d(k_tiles + (size_t)s * KV_BYTES + (size_t)a * AT_KEYS * 128, &map_k, &kv_full[s], a * 64, row0);
+                    at_tma_2d(v_tiles + (size_t)s * KV_BYTES + (size_t)a * AT_KEYS * 128, &map_v, &kv_full[s], a * 64, row0);
+                }
+                issued = j + 1;
+            }
+            if (!ok) {
+                atomicExch(error, 1);
+                for (int j = max(0, issued - AT_KV_STAGES); j < issued; ++j) at_wait(&kv_full[j % AT_KV_STAGES], (j / AT_KV_STAGES) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = at_idesc(AT_ROWS, AT_KEYS, false);           // S [128 x 64] = Q [128 x HD] K[64 x HD]^T
+            constexpr uint32_t idesc_o = at_idesc(AT_ROWS, HD, true);                  // O [128 x HD] += P [128 x 64] V [64 x HD]
+            bool ok = at_wait(q_full, 0);
+            auto issue_s = [&](int j) {
+                const int s = j % AT_KV_STAGES;
+                const unsigned char* kt = k_tiles + (size_t)s * KV_BYTES;
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k) {                                    // 16 values of d per product
+                    const uint64_t da = at_desc_kmajor(q_tile + (size_t)(k / 4) * AT_ROWS * 128) + 2 * (k % 4);
+                    const uint64_t db = at_desc_kmajor(kt + (size_t)(k / 4) * AT_KEYS * 128) + 2 * (k % 4);
+                    at_mma(tmem_s, da, db, idesc_s, k > 0 ? 1u : 0u);
+                }
+                at_commit(s_full);
+            };
+            if (ok) ok = at_wait(&kv_full[0], 0);
+            if (ok) { at_fence_after(); issue_s(0); }
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                const int s = j % AT_KV_STAGES;
+                ok = at_wait(p_full, j & 1);                                           // P of this tile is in shared memory
+                if (!ok) break;
+                at_fence_after();
+                const unsigned char* vt = v_tiles + (size_t)s * KV_BYTES;
+#pragma unroll
+                for (int k = 0; k < AT_KEYS / 16; ++k) {                               // 16 keys per product
+                    const uint64_t da = at_desc_kmajor(p_tile) + 2 * k;
+                    const uint64_t db = at_desc_mnmajor(vt + (size_t)k * 16 * 128, AT_KEYS * 128);
+                    at_mma(tmem_o, da, db, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+                }
+                at_commit(&kv_empty[s]);                                               // K and V of this tile are read
+                at_commit(o_full);
+                if (j + 1 < n_tiles) {
+                    ok = at_wait(&kv_full[(j + 1) % AT_KV_STAGES], ((j + 1) / AT_KV_STAGES) & 1);
+                    if (!ok) break;
+                    at_fence_after();
+                    issue_s(j + 1);
+                }
+            }
+            if (!ok) {
+                atomicExch(error, 2);
+                at_commit(s_full);
+                at_commit(o_full);
+            }
+        }
+    } else {
+        const int lane_group = warp & 3;
+        const int r = 32 * lane_group + lane;                                          // this thread's row = tensor-memory lane
+        const int tok = q0 + r / G, head = kvh * G + r % G;
+        const bool row_ok = tok < n_new;
+        const int qp = row_ok ? p0 + tok : -1;
+        const uint32_t lane_off = (uint32_t)(32 * lane_group) << 16;
+        const float sl2 = scale * 1.4426950408889634f;
+        float m_ref = -INFINITY, l = 0.f;                                              // reference maximum (raw score) and sum
+        uint4* p_row = reinterpret_cast<uint4*>(p_tile + (size_t)r * 128);
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            ok = at_wait(s_full, j & 1);
+            at_fence_after();
+            if (!ok) { if (lane == 0) atomicExch(error, 3); break; }
+            const int key0 = (tile_first + j) * AT_KEYS;
+            uint32_t sv[2][32];
+            at_ld32(tmem_s + lane_off, sv[0]);
+            at_ld32(tmem_s + lane_off + 32, sv[1]);
+            float mx = -INFINITY;
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int key = key0 + 32 * h + i;
+                    const bool vis = key <= qp && key < len && (window <= 0 || key > qp - window);
+                    const float s = vis ? __uint_as_float(sv[h][i]) : -INFINITY;
+                    sv[h][i] = __float_as_uint(s);
+                    mx = fmaxf(mx, s);
+                }
+            // keep the old reference unless this tile's maximum is far above it
+            const bool rescale = mx > m_ref + AT_RESCALE_LOG2 / sl2;
+            const float m_new = rescale ? mx : m_ref;
+            const float alpha = rescale ? exp2f((m_ref - m_new) * sl2) : 1.f;        // m_ref = -inf gives 0
+            const float base = m_new == -INFINITY ? 0.f : m_new * sl2;
+            if (j > 0) {                                                               // the product before this one has read P and written O
+                ok = at_wait(o_full, (j - 1) & 1);
+                at_fence_after();
+                if (!ok) { if (lane == 0) atomicExch(error, 4); break; }
+                if (__any_sync(0xffffffffu, rescale)) {                                 // some row of this warp moves its reference: rescale O
+#pragma unroll 1
+                    for (int c = 0; c < HD; c += 32) {
+                        uint32_t ov[32];
+                        at_ld32(tmem_o + lane_off + c, ov);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+                        at_st32(tmem_o + lane_off + c, ov);
+                    }
+                }
+            }
+            l *= alpha;
+            m_ref = m_new;
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                    uint32_t pk[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const float p0v = exp2f(__uint_as_float(sv[h][i + 2 * u]) * sl2 - base);
+                        const float p1v = exp2f(__uint_as_float(sv[h][i + 2 * u + 1]) * sl2 - base);
+                        l += p0v + p1v;
+                        __nv_bfloat162 v = __floats2bfloat162_rn(p0v, p1v);
+                        pk[u] = *reinterpret_cast<uint32_t*>(&v);
+                    }
+                    const int piece = h * 4 + i / 8;
+                    p_row[piece ^ (r & 7)] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                }
+            at_fence_before();                                                          // S (and O) are read; P is written
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) at_arrive(p_full);
+        }
+        if (ok) {
+            ok = at_wait(o_full, (n_tiles - 1) & 1);
+            at_fence_after();
+            if (!ok && lane == 0) atomicExch(error, 5);
+        }
+        if (ok) {
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            bf16* dst = out + ((size_t)(t0 + tok) * Hq + head) * HD;
+#pragma unroll 1
+            for (int c = 0; c < HD; c += 32) {
+                uint32_t ov[32];
+                at_ld32(tmem_o + lane_off + c, ov);
+                if (row_ok) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint32_t pk[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(ov[i + 2 * u]) * inv, __uint_as_float(ov[i + 2 * u + 1]) * inv);
+                            pk[u] = *reinterpret_cast<uint32_t*>(&v);
+                        }
+                        *reinterpret_cast<uint4*>(dst + c + i) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    }
+                }
+            }
+        }
+    }
+    at_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        at_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_s), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------- host side
+typedef CUresult (*AtEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static AtEncodeFn at_encode() {
+    static AtEncodeFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<AtEncodeFn>(p);
+    }
+    return fn;
+}
+
+template <int HD>
+static int launch_attn_tc(const void* q, const void* k_pool, const void* v_pool, const int* page_table, const int* cu_seqlens,
+                          const int* pos0, void* out, int B, int T, int max_new, int n_pages, int Hq, int Hkv, int table_width,
+                          float scale, int window, int* error, cudaStream_t stream) {
+    AtEncodeFn enc = at_encode();
+    if (!enc) return qwb_fail(QWB_ERR_CUDA, "attn_tc_prefill: cuTensorMapEncodeTiled is not available from this driver");
+    const int G = Hq / Hkv;
+    CUtensorMap map_q, map_k, map_v;
+    {   // q [T, Hq, HD]: boxes of [128 / G tokens][G heads][64 d]
+        cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)Hq, (cuuint64_t)T};
+        cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)Hq * HD * 2};
+        cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)(AT_ROWS / G)};
+        cuuint32_t elem[3] = {1, 1, 1};
+        CUresult r = enc(&map_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, elem,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return qwb_fail(QWB_ERR_CUDA, "attn_tc_prefill: cuTensorMapEncodeTiled(q) failed with %d", (int)r);
+    }
+    const void* pools[2] = {k_pool, v_pool};
+    CUtensorMap* maps[2] = {&map_k, &map_v};
+    for (int i = 0; i < 2; ++i) {   // a pool [pages, Hkv, 64, HD] as rows of HD: boxes of [64 keys][64 d]
+        cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)n_pages * Hkv * AT_KEYS};
+        cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+        cuuint32_t box[2] = {64, AT_KEYS};
+        cuuint32_t elem[2] = {1, 1};
+        CUresult r = enc(maps[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pools[i]), dims, strides, box, elem,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return qwb_fail(QWB_ERR_CUDA, "attn_tc_prefill: cuTensorMapEncodeTiled(cache) failed with %d", (int)r);
+    }
+    const size_t smem = AtSmem<HD>::BYTES;
+    cudaError_t e = cudaFuncSetAttribute(attn_tc_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "attn_tc_prefill: %s", cudaGetErrorString(e));
+    const int tok_per_block = AT_ROWS / G;
+    dim3 grid((max_new + tok_per_block - 1) / tok_per_block, Hkv, B);
+    e = qwb_launch(attn_tc_prefill_kernel<HD>, grid, AT_THREADS, smem, stream, map_q, map_k, map_v, page_table, cu_seqlens, pos0,
+                   (bf16*)out, Hq, Hkv, table_width, scale, window, G, error);
+    if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "attn_tc_prefill: launch failed: %s", cudaGetErrorString(e));
+    return qwb_check_launch("attn_tc_prefill");
+}
+
+// bfloat16.  q [T, Hq, hd] with T the packed tokens of all B sequences; pools of n_pages pages; `error` as for qwb_gemm_tc.
+extern "C" int qwb_attn_tc_prefill(const void* q, const void* k_pool, const void* v_pool, const int* page_table,
+                                   const int* cu_seqlens, const int* pos0, void* out, int B, int T, int max_new, int n_pages,
+                                   int Hq, int Hkv, int hd, int page_size, int table_width, float scale, int window, int* error,
+                                   cudaStream_t stream) {
+    if (B <= 0 || max_new <= 0 || T <= 0) return 0;
+    if (hd != 64 && hd != 128) return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: head size %d is not 64 or 128", hd);
+    if (page_size != AT_KEYS) return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: page size %d is not %d", page_size, AT_KEYS);
+    if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: %d query heads are not a multiple of %d key/value heads", Hq, Hkv);
+    const int G = Hq / Hkv;
+    if (G != 1 && G != 2 && G != 4 && G != 8 && G != 16) return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: %d query heads per key/value head; this kernel takes 1, 2, 4, 8 or 16", G);
+    if (B > 65535 || Hkv > 65535) return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: batch %d or heads %d above 65535", B, Hkv);
+    if (!error) return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: an error word on the device is required");
+    if ((uintptr_t)q % 16 || (uintptr_t)k_pool % 16 || (uintptr_t)v_pool % 16 || (uintptr_t)out % 16)
+        return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: operands must be 16-byte aligned");
+    if (hd == 64) return launch_attn_tc<64>(q, k_pool, v_pool, page_table, cu_seqlens, pos0, out, B, T, max_new, n_pages, Hq, Hkv, table_width, scale, window, error, stream);
+    return launch_attn_tc<128>(q, k_pool, v_pool, page_table, cu_seqlens, pos0, out, B, T, max_new, n_pages, Hq, Hkv, table_width, scale, window, error, stream);
+}

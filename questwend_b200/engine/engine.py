@@ -191,7 +191,7 @@ class Engine:
         with torch.cuda.device(self.device):
             ctx, want_rows = self.build_context(entries)
             logits = self.model.forward(ctx, self.unit_caches, want_rows)
-            if self.dtype == torch.bfloat16 and ctx.n_tokens > 128:
+            if self.dtype == torch.bfloat16 and not ctx.single_token:
                 ops.gemm_tc_check(self.device)       # a tcgen05 product that gave up a wait must not pass unseen
         for e in entries:
             self.cache.advance(e.slot, len(e.tokens))

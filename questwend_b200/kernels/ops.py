@@ -178,10 +178,15 @@ def mma_attention_fits(dtype: torch.dtype, head_dim: int, page_size: int) -> boo
     return dtype == torch.bfloat16 and head_dim in (64, 128) and page_size == 64
 
 
+def tc_attention_fits(dtype: torch.dtype, head_dim: int, page_size: int, group: int) -> bool:
+    """Whether the tcgen05 prefill attention kernel takes this case."""
+    return mma_attention_fits(dtype, head_dim, page_size) and group in (1, 2, 4, 8, 16)
+
+
 def attn_prefill(q, k_pool, v_pool, page_table, cu_seqlens, pos0, max_new: int, scale: float,
                  window: int = 0, impl: str = "auto") -> torch.Tensor:
     """Causal attention of new tokens over the cache.  q [T, Hq, hd]; returns [T, Hq * hd].
-    impl: "auto" (tensor cores where they fit), "mma", or "plain"."""
+    impl: "auto" (the fastest that fits), "tc" (tcgen05), "mma" (mma.sync), or "plain"."""
     _need(q, "q", k_pool.dtype, 3)
     _need(k_pool, "k_pool", ndim=4)
     _need(v_pool, "v_pool", k_pool.dtype, 4)
@@ -193,6 +198,18 @@ def attn_prefill(q, k_pool, v_pool, page_table, cu_seqlens, pos0, max_new: int, 
     if cu_seqlens.numel() != B + 1 or page_table.shape[0] < B:
         raise KernelError("attn_prefill: cu_seqlens / page_table do not fit the batch")
     out = torch.empty((T, Hq * hd), dtype=q.dtype, device=q.device)
+    group = Hq // max(1, k_pool.shape[1])
+    # the tcgen05 kernel works on tiles of 128 rows: it pays from a few dozen new tokens per sequence on
+    use_tc = impl == "tc" or (impl == "auto" and max_new * group >= 64 and
+                              tc_attention_fits(q.dtype, hd, k_pool.shape[2], group))
+    if use_tc:
+        if q.dtype != torch.bfloat16:
+            raise KernelError("attn_prefill: the tensor-core kernel takes bfloat16 only")
+        _call("attention_tc", "qwb_attn_tc_prefill", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table),
+              _ptr(cu_seqlens), _ptr(pos0), _ptr(out), _i(B), _i(T), _i(max_new), _i(k_pool.shape[0]), _i(Hq),
+              _i(k_pool.shape[1]), _i(hd), _i(k_pool.shape[2]), _i(page_table.shape[1]), _f(scale), _i(window),
+              _ptr(gemm_tc_error_word(q.device)), _stream())
+        return out
     use_mma = impl == "mma" or (impl == "auto" and mma_attention_fits(q.dtype, hd, k_pool.shape[2]))
     if use_mma:
         if q.dtype != torch.bfloat16:
@@ -301,14 +318,15 @@ def gemm_tc_error_word(device) -> torch.Tensor:
 
 
 def gemm_tc_check(device) -> None:
-    """Raise if a tcgen05 product on this device gave up a wait since the last check (reads one int: synchronises)."""
+    """Raise if a tcgen05 kernel (product or attention) on this device gave up a wait since the last check (reads one
+    int: synchronises)."""
     word = gemm_tc_error_word(device)
     code = int(word.item())
     if code:
         word.zero_()
-        where = {1: "the loader waiting for a free stage", 2: "the tensor-core issuer waiting for a loaded stage",
-                 3: "the epilogue waiting for the accumulator"}.get(code, f"code {code}")
-        raise KernelError(f"gemm_tc: a bounded wait ran out ({where}); the result of that product is not valid")
+        where = {1: "the loader waiting for a free stage", 2: "the tensor-core issuer waiting for its operands",
+                 3: "the epilogue or softmax warps waiting for the tensor core"}.get(code, f"code {code}")
+        raise KernelError(f"a bounded wait in a tcgen05 kernel ran out ({where}); that kernel's result is not valid")
 
 
 def gemm_tc(x: torch.Tensor, weight: torch.Tensor, epilogue: str = "store", out: torch.Tensor | None = None,

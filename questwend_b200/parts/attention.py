@@ -66,8 +66,12 @@ class GroupedQueryAttention(Mixer):
 
     def kernel_modules(self):
         mods = ["rope_kv", "gemm_small", "gemm_stream", "gemm_tc"]
-        mods.append("attention_mma" if ops.mma_attention_fits(self.runtime.dtype, self.head_dim, ops.PAGE_SIZE)
-                    else "attention")
+        if ops.mma_attention_fits(self.runtime.dtype, self.head_dim, ops.PAGE_SIZE):
+            mods.append("attention_mma")
+            if ops.tc_attention_fits(self.runtime.dtype, self.head_dim, ops.PAGE_SIZE, self.n_heads // self.n_kv_heads):
+                mods.append("attention_tc")
+        else:
+            mods.append("attention")
         return tuple(mods)
 
     def kv_spec(self):

@@ -195,6 +195,13 @@ def test_attn_prefill_tensor_cores(Hq, Hkv, hd, window):
     _attn_prefill_case(torch.bfloat16, Hq, Hkv, hd, window, "mma")
 
 
+@pytest.mark.parametrize("Hq,Hkv,hd", [(8, 2, 64), (8, 1, 128), (4, 4, 128), (16, 1, 64), (32, 8, 128), (4, 2, 128)])
+@pytest.mark.parametrize("window", [0, 37])
+def test_attn_prefill_tcgen05(Hq, Hkv, hd, window):
+    _attn_prefill_case(torch.bfloat16, Hq, Hkv, hd, window, "tc")
+    ops.gemm_tc_check(DEV)
+
+
 def _attn_prefill_case(dtype, Hq, Hkv, hd, window, impl):
     lens = [1, 17, 70, 150, 64]
     new = [1, 17, 33, 22, 64]                       # the last `new` tokens of each sequence are this step's

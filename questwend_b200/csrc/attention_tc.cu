@@ -3,7 +3,8 @@
 //
 // A block serves 128 rows = (128 / G tokens) x (the G query heads of one key/value head).  Per tile of 64 keys (one
 // cache page of that head):
-//     S = Q K^T      tcgen05.mma, Q and K from shared memory (TMA, 128-byte swizzle), S in tensor memory (64 columns)
+//     S = Q K^T      tcgen05.mma, Q and K from shared memory (TMA, 128-byte swizzle), S in tensor memory (64 columns, two
+//                    buffers: the tensor core is up to two tiles ahead of the softmax)
 //     P = softmax    four warps, one thread per row: read S, mask, running maximum and sum in 32-bit, write P as
 //                    bfloat16 into shared memory in the layout the tensor core reads
 //     O += P V       tcgen05.mma, P and V from shared memory, O accumulates in tensor memory (HD columns).  V is read as
@@ -88,6 +89,13 @@ __device__ __forceinline__ void at_st32(uint32_t taddr, const uint32_t* r) {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// 2^x by the hardware approximation (relative error about 2^-22; -inf gives 0).
+__device__ __forceinline__ float at_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Operand descriptors, 128-byte swizzle, descriptor version 1.
 //   K-major (rows of 64 bfloat16 = 128 bytes, the contraction runs along the row): groups of 8 rows are 1024 bytes apart.
 __device__ __forceinline__ uint64_t at_desc_kmajor(const void* tile) {
@@ -123,7 +131,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        int table_width, float scale, int window, int G, int* error) {
     constexpr int ATOMS = AtSmem<HD>::ATOMS;
     constexpr uint32_t KV_BYTES = AtSmem<HD>::KV_BYTES;
-    constexpr uint32_t TMEM_COLS = HD == 128 ? 256 : 128;                   // S: 64 columns, O: HD columns
+    constexpr uint32_t TMEM_COLS = 256;                                     // S: 2 x 64 columns, O: HD columns
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* q_tile = base;
@@ -133,8 +141,9 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     uint64_t* q_full = reinterpret_cast<uint64_t*>(p_tile + AtSmem<HD>::P_BYTES);
     uint64_t* kv_full = q_full + 1;
     uint64_t* kv_empty = kv_full + AT_KV_STAGES;
-    uint64_t* s_full = kv_empty + AT_KV_STAGES;
-    uint64_t* p_full = s_full + 1;
+    uint64_t* s_full = kv_empty + AT_KV_STAGES;          // [2]: the two S buffers
+    uint64_t* s_empty = s_full + 2;                      // [2]
+    uint64_t* p_full = s_empty + 2;
     uint64_t* o_full = p_full + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
 
@@ -156,7 +165,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (threadIdx.x == 0) {
         at_bar_init(q_full, 1);
         for (int s = 0; s < AT_KV_STAGES; ++s) { at_bar_init(&kv_full[s], 1); at_bar_init(&kv_empty[s], 1); }
-        at_bar_init(s_full, 1);
+        for (int i = 0; i < 2; ++i) { at_bar_init(&s_full[i], 1); at_bar_init(&s_empty[i], 4); }
         at_bar_init(p_full, 4);
         at_bar_init(o_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -168,8 +177,8 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     at_fence_before();
     __syncthreads();
     at_fence_after();
-    const uint32_t tmem_s = *tmem_slot;                 // S: columns [0, 64)
-    const uint32_t tmem_o = tmem_s + 64;                // O: columns [64, 64 + HD)
+    const uint32_t tmem_s = *tmem_slot;                 // S: two buffers, columns [0, 64) and [64, 128)
+    const uint32_t tmem_o = tmem_s + 128;               // O: columns [128, 128 + HD)
 
     pdl_wait();
     pdl_launch_dependents();
@@ -203,19 +212,24 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             constexpr uint32_t idesc_s = at_idesc(AT_ROWS, AT_KEYS, false);           // S [128 x 64] = Q [128 x HD] K[64 x HD]^T
             constexpr uint32_t idesc_o = at_idesc(AT_ROWS, HD, true);                  // O [128 x HD] += P [128 x 64] V [64 x HD]
             bool ok = at_wait(q_full, 0);
-            auto issue_s = [&](int j) {
+            // S runs two tiles ahead of P V: while the softmax warps work on one S buffer the tensor core fills the other.
+            auto issue_s = [&](int j) -> bool {
                 const int s = j % AT_KV_STAGES;
+                if (!at_wait(&kv_full[s], (j / AT_KV_STAGES) & 1)) return false;
+                if (j >= 2 && !at_wait(&s_empty[j & 1], ((j >> 1) - 1) & 1)) return false;
+                at_fence_after();
                 const unsigned char* kt = k_tiles + (size_t)s * KV_BYTES;
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {                                    // 16 values of d per product
                     const uint64_t da = at_desc_kmajor(q_tile + (size_t)(k / 4) * AT_ROWS * 128) + 2 * (k % 4);
                     const uint64_t db = at_desc_kmajor(kt + (size_t)(k / 4) * AT_KEYS * 128) + 2 * (k % 4);
-                    at_mma(tmem_s, da, db, idesc_s, k > 0 ? 1u : 0u);
+                    at_mma(tmem_s + (uint32_t)(j & 1) * 64, da, db, idesc_s, k > 0 ? 1u : 0u);
                 }
-                at_commit(s_full);
+                at_commit(&s_full[j & 1]);
+                return true;
             };
-            if (ok) ok = at_wait(&kv_full[0], 0);
-            if (ok) { at_fence_after(); issue_s(0); }
+            if (ok) ok = issue_s(0);
+            if (ok && n_tiles > 1) ok = issue_s(1);
             for (int j = 0; j < n_tiles && ok; ++j) {
                 const int s = j % AT_KV_STAGES;
                 ok = at_wait(p_full, j & 1);                                           // P of this tile is in shared memory
@@ -230,16 +244,12 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 }
                 at_commit(&kv_empty[s]);                                               // K and V of this tile are read
                 at_commit(o_full);
-                if (j + 1 < n_tiles) {
-                    ok = at_wait(&kv_full[(j + 1) % AT_KV_STAGES], ((j + 1) / AT_KV_STAGES) & 1);
-                    if (!ok) break;
-                    at_fence_after();
-                    issue_s(j + 1);
-                }
+                if (j + 2 < n_tiles) ok = issue_s(j + 2);
             }
             if (!ok) {
                 atomicExch(error, 2);
-                at_commit(s_full);
+                at_commit(&s_full[0]);
+                at_commit(&s_full[1]);
                 at_commit(o_full);
             }
         }
@@ -255,29 +265,55 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         uint4* p_row = reinterpret_cast<uint4*>(p_tile + (size_t)r * 128);
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
-            ok = at_wait(s_full, j & 1);
+            ok = at_wait(&s_full[j & 1], (j >> 1) & 1);
             at_fence_after();
             if (!ok) { if (lane == 0) atomicExch(error, 3); break; }
             const int key0 = (tile_first + j) * AT_KEYS;
             uint32_t sv[2][32];
-            at_ld32(tmem_s + lane_off, sv[0]);
-            at_ld32(tmem_s + lane_off + 32, sv[1]);
+            at_ld32(tmem_s + (uint32_t)(j & 1) * 64 + lane_off, sv[0]);
+            at_ld32(tmem_s + (uint32_t)(j & 1) * 64 + lane_off + 32, sv[1]);
+            at_fence_before();                                                          // this S buffer may be filled again
+            __syncwarp();
+            if (lane == 0) at_arrive(&s_empty[j & 1]);
+            // a tile that lies wholly inside what this row may see needs no mask
+            const bool all_visible = key0 + AT_KEYS - 1 <= qp && key0 + AT_KEYS - 1 < len && (window <= 0 || key0 > qp - window);
             float mx = -INFINITY;
+            if (all_visible) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+                for (int h = 0; h < 2; ++h)
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int key = key0 + 32 * h + i;
-                    const bool vis = key <= qp && key < len && (window <= 0 || key > qp - window);
-                    const float s = vis ? __uint_as_float(sv[h][i]) : -INFINITY;
-                    sv[h][i] = __float_as_uint(s);
-                    mx = fmaxf(mx, s);
-                }
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[h][i]));
+            } else {
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int key = key0 + 32 * h + i;
+                        const bool vis = key <= qp && key < len && (window <= 0 || key > qp - window);
+                        const float sc = vis ? __uint_as_float(sv[h][i]) : -INFINITY;
+                        sv[h][i] = __float_as_uint(sc);
+                        mx = fmaxf(mx, sc);
+                    }
+            }
             // keep the old reference unless this tile's maximum is far above it
             const bool rescale = mx > m_ref + AT_RESCALE_LOG2 / sl2;
             const float m_new = rescale ? mx : m_ref;
-            const float alpha = rescale ? exp2f((m_ref - m_new) * sl2) : 1.f;        // m_ref = -inf gives 0
+            const float alpha = rescale ? at_exp2((m_ref - m_new) * sl2) : 1.f;       // m_ref = -inf gives 0
             const float base = m_new == -INFINITY ? 0.f : m_new * sl2;
+            l *= alpha;
+            m_ref = m_new;
+            // the probabilities, packed to bfloat16, while the product before this one may still run
+            uint32_t pk[2][16];
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float p0v = at_exp2(__uint_as_float(sv[h][i]) * sl2 - base);
+                    const float p1v = at_exp2(__uint_as_float(sv[h][i + 1]) * sl2 - base);
+                    l += p0v + p1v;
+                    __nv_bfloat162 v = __floats2bfloat162_rn(p0v, p1v);
+                    pk[h][i / 2] = *reinterpret_cast<uint32_t*>(&v);
+                }
             if (j > 0) {                                                               // the product before this one has read P and written O
                 ok = at_wait(o_full, (j - 1) & 1);
                 at_fence_after();
@@ -293,25 +329,12 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     }
                 }
             }
-            l *= alpha;
-            m_ref = m_new;
 #pragma unroll
             for (int h = 0; h < 2; ++h)
 #pragma unroll
-                for (int i = 0; i < 32; i += 8) {
-                    uint32_t pk[4];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const float p0v = exp2f(__uint_as_float(sv[h][i + 2 * u]) * sl2 - base);
-                        const float p1v = exp2f(__uint_as_float(sv[h][i + 2 * u + 1]) * sl2 - base);
-                        l += p0v + p1v;
-                        __nv_bfloat162 v = __floats2bfloat162_rn(p0v, p1v);
-                        pk[u] = *reinterpret_cast<uint32_t*>(&v);
-                    }
-                    const int piece = h * 4 + i / 8;
-                    p_row[piece ^ (r & 7)] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                }
-            at_fence_before();                                                          // S (and O) are read; P is written
+                for (int i = 0; i < 4; ++i)
+                    p_row[(h * 4 + i) ^ (r & 7)] = make_uint4(pk[h][4 * i], pk[h][4 * i + 1], pk[h][4 * i + 2], pk[h][4 * i + 3]);
+            at_fence_before();                                                          // O is rescaled (if at all); P is written
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) at_arrive(p_full);

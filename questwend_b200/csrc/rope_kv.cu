@@ -101,6 +101,71 @@ __global__ void qk_norm_rope_store_kernel(const float* __restrict__ qkv, const f
     }
 }
 
+template <typename TOut> struct Pack4Store;
+template <> struct Pack4Store<float> {
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Pack4Store<bf16> {
+    static __device__ __forceinline__ void store(bf16* p, float4 v) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        uint2 u;
+        u.x = *reinterpret_cast<uint32_t*>(&lo);
+        u.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p) = u;
+    }
+};
+
+// The same for head size 128 rotated over all 128 values, the common case: one 16-byte load per lane (lane L holds
+// values 4L..4L+3), the rotation partner (64 values away) comes from lane L ^ 16 by shuffle, one 8- or 16-byte store.
+template <typename TOut>
+__global__ void qk_norm_rope_store_hd128_kernel(const float* __restrict__ qkv, const float* __restrict__ q_weight,
+                                                const float* __restrict__ k_weight, const float* __restrict__ cos_t,
+                                                const float* __restrict__ sin_t, const int* __restrict__ tok_seq,
+                                                const int* __restrict__ tok_pos, const int* __restrict__ page_table,
+                                                TOut* __restrict__ q_out, TOut* __restrict__ k_pool, TOut* __restrict__ v_pool,
+                                                int Hq, int Hkv, float eps, int page_size, int table_width, int store_kv) {
+    pdl_wait();
+    pdl_launch_dependents();
+    constexpr int hd = 128;
+    const int t = blockIdx.x;
+    const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    const int n_heads = Hq + 2 * Hkv;
+    if (head >= n_heads) return;
+    const bool is_q = head < Hq, is_k = !is_q && head < Hq + Hkv;
+    if (!is_q && !store_kv) return;
+    const float4 x = reinterpret_cast<const float4*>(qkv + ((size_t)t * n_heads + head) * hd)[lane];
+    TOut* dst;
+    if (is_q) {
+        dst = q_out + ((size_t)t * Hq + head) * hd;
+    } else {
+        const int kvh = is_k ? head - Hq : head - Hq - Hkv;
+        const int p = tok_pos[t];
+        const int page = page_table[(size_t)tok_seq[t] * table_width + p / page_size];
+        dst = (is_k ? k_pool : v_pool) + (((size_t)page * Hkv + kvh) * page_size + (p % page_size)) * hd;
+    }
+    float4 y = x;
+    if (is_q || is_k) {
+        const float* nw = is_q ? q_weight : k_weight;
+        if (nw) {
+            const float ss = warp_sum(x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w);
+            const float scale = rsqrtf(ss / (float)hd + eps);
+            const float4 w = reinterpret_cast<const float4*>(nw)[lane];
+            y = make_float4(x.x * scale * w.x, x.y * scale * w.y, x.z * scale * w.z, x.w * scale * w.w);
+        }
+        float4 other;                                              // the values 64 places away
+        other.x = __shfl_xor_sync(0xffffffffu, y.x, 16);
+        other.y = __shfl_xor_sync(0xffffffffu, y.y, 16);
+        other.z = __shfl_xor_sync(0xffffffffu, y.z, 16);
+        other.w = __shfl_xor_sync(0xffffffffu, y.w, 16);
+        const float4 c = reinterpret_cast<const float4*>(cos_t + (size_t)t * (hd / 2))[lane & 15];
+        const float4 sn = reinterpret_cast<const float4*>(sin_t + (size_t)t * (hd / 2))[lane & 15];
+        if (lane < 16) y = make_float4(y.x * c.x - other.x * sn.x, y.y * c.y - other.y * sn.y, y.z * c.z - other.z * sn.z, y.w * c.w - other.w * sn.w);
+        else y = make_float4(other.x * sn.x + y.x * c.x, other.y * sn.y + y.y * c.y, other.z * sn.z + y.z * c.z, other.w * sn.w + y.w * c.w);
+    }
+    Pack4Store<TOut>::store(dst + 4 * lane, y);
+}
+
 extern "C" int qwb_qk_norm_rope_store(const float* qkv, const float* q_weight, const float* k_weight,
                                       const float* cos_t, const float* sin_t, const int* tok_seq,
                                       const int* tok_pos, const int* page_table, void* q_out, void* k_pool,
@@ -114,7 +179,19 @@ extern "C" int qwb_qk_norm_rope_store(const float* qkv, const float* q_weight, c
     const int warps = 4;
     dim3 grid(T, (Hq + 2 * Hkv + warps - 1) / warps);
     if (grid.y > 65535) return qwb_fail(QWB_ERR_ARG, "qk_norm_rope_store: too many heads (%d)", Hq + 2 * Hkv);
-    if (dtype == QWB_DT_F32)
+    const bool fast = hd == 128 && rot == 128 && (uintptr_t)qkv % 16 == 0 && (uintptr_t)q_out % 16 == 0 &&
+                      (uintptr_t)k_pool % 16 == 0 && (uintptr_t)v_pool % 16 == 0 && (uintptr_t)cos_t % 16 == 0 &&
+                      (uintptr_t)sin_t % 16 == 0 && (!q_weight || (uintptr_t)q_weight % 16 == 0) &&
+                      (!k_weight || (uintptr_t)k_weight % 16 == 0);
+    if (fast && dtype == QWB_DT_F32)
+        qwb_launch(qk_norm_rope_store_hd128_kernel<float>, grid, warps * 32, 0, stream, qkv, q_weight, k_weight, cos_t, sin_t,
+                   tok_seq, tok_pos, page_table, (float*)q_out, (float*)k_pool, (float*)v_pool, Hq, Hkv, eps, page_size,
+                   table_width, store_kv);
+    else if (fast && dtype == QWB_DT_BF16)
+        qwb_launch(qk_norm_rope_store_hd128_kernel<bf16>, grid, warps * 32, 0, stream, qkv, q_weight, k_weight, cos_t, sin_t,
+                   tok_seq, tok_pos, page_table, (bf16*)q_out, (bf16*)k_pool, (bf16*)v_pool, Hq, Hkv, eps, page_size,
+                   table_width, store_kv);
+    else if (dtype == QWB_DT_F32)
         qwb_launch(qk_norm_rope_store_kernel<float>, grid, warps * 32, 0, stream, 
             qkv, q_weight, k_weight, cos_t, sin_t, tok_seq, tok_pos, page_table, (float*)q_out, (float*)k_pool,
             (float*)v_pool, Hq, Hkv, hd, rot, eps, page_size, table_width, store_kv);

@@ -119,7 +119,8 @@ def paged(dense, n_kv_heads, head_dim, dtype, page_size=64, seed=0, extra_pages=
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("Hq,Hkv,hd,rot,norm", [(5, 1, 48, 32, True), (4, 2, 16, 16, True), (3, 3, 80, 80, False),
-                                                (2, 1, 32, 0, True)])
+                                                (2, 1, 32, 0, True), (6, 2, 128, 128, True), (3, 1, 128, 128, False),
+                                                (2, 2, 128, 64, True)])
 def test_qk_norm_rope_store(dtype, Hq, Hkv, hd, rot, norm):
     rng = np.random.default_rng(hd)
     page = 64

@@ -151,7 +151,8 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int b = blockIdx.z, kvh = blockIdx.y;
     const int tok_per_block = AT_ROWS / G;
     const int t0 = cu_seqlens[b], n_new = cu_seqlens[b + 1] - t0;
-    const int q0 = blockIdx.x * tok_per_block;
+    // the last tokens see the most keys: their blocks go first, so that the long blocks do not form the tail of the launch
+    const int q0 = (int)(gridDim.x - 1 - blockIdx.x) * tok_per_block;
     if (q0 >= n_new) return;
     const int p0 = pos0[b];
     const int len = p0 + n_new;

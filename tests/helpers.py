@@ -19,7 +19,17 @@ TINY_B = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hid
           "hidden_size": 96, "intermediate_size": 200, "num_attention_heads": 6, "num_key_value_heads": 1,
           "head_dim": 32, "vocab_size": 384, "rope_theta": 1e6, "rms_norm_eps": 1e-5,
           "tie_word_embeddings": False}
-TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1)}
+# Two more with the head sizes and head groups that the tensor-core kernels take (64 and 128; 2 and 4 query heads per
+# key/value head), still small everywhere else.
+TINY_C = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": 2,
+          "hidden_size": 128, "intermediate_size": 192, "num_attention_heads": 4, "num_key_value_heads": 2,
+          "head_dim": 64, "vocab_size": 320, "rope_theta": 50000.0, "rms_norm_eps": 1e-6,
+          "tie_word_embeddings": False}
+TINY_D = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": 2,
+          "hidden_size": 192, "intermediate_size": 264, "num_attention_heads": 8, "num_key_value_heads": 2,
+          "head_dim": 128, "vocab_size": 296, "rope_theta": 1e6, "rms_norm_eps": 1e-5,
+          "tie_word_embeddings": True}
+TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1), "C": (TINY_C, 2), "D": (TINY_D, 3)}
 
 FP32_TOL = 1e-4        # max |delta| <= FP32_TOL * max |logit|, 32-bit engine against the plain implementation
 BF16_TOL = 2.0 ** -7   # the same for the bfloat16 engine against the plain implementation that rounds where

@@ -27,9 +27,10 @@ def tol(dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_long_decoding(folders, dtype):
-    """300 tokens one by one after a short prompt: across pages (64) and across runs of the decode kernel (256)."""
-    folder = folders["B", dtype]
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_long_decoding(folders, name, dtype):
+    """300 tokens one by one after a short prompt: across pages (64) and across runs of the decode kernels (64 or 256)."""
+    folder = folders[name, dtype]
     cfg, w = pm.read_model_folder(folder)
     eng = qw.Engine.from_folder(folder, dtype=dtype, max_tokens=512)
     rng = np.random.default_rng(3)
@@ -45,7 +46,7 @@ def test_long_decoding(folders, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_first_tokens_of_a_sequence(folders, name, dtype):
     """Position 0 has one key and no rotation; prompts of one and two tokens, then one token each."""
     folder = folders[name, dtype]
@@ -87,8 +88,9 @@ def test_greedy_generation_matches_the_plain_implementation(folders, use_graph):
     assert eng.cache.slots.n_free == 2 and eng.cache.free_pages() == [eng.cache.n_pages]
 
 
-def test_bfloat16_greedy_generation(folders):
-    folder = folders["B", "bfloat16"]
+@pytest.mark.parametrize("name", ["B", "C", "D"])
+def test_bfloat16_greedy_generation(folders, name):
+    folder = folders[name, "bfloat16"]
     cfg, w = pm.read_model_folder(folder)
     prompts = [[3, 14, 15, 92, 65], [35, 89, 79], [32, 38, 46, 26, 43, 38, 32, 79, 50]]
     want = [pm.greedy_continue(cfg, w, p, 8, round16="bf16") for p in prompts]

@@ -66,7 +66,7 @@ def build_traces(tokens):
     return steps, where
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_replay_agrees_with_the_plain_implementation(name, dtype, tmp_path):
     cfgd, seed = TINY[name]

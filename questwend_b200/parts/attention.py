@@ -11,7 +11,7 @@ import torch
 from ..kernels import ops
 from ..weights.manifest import MATRIX, NORM_WEIGHT, VECTOR, TensorSpec
 from .base import KVSpec, Mixer
-from .linear import linear
+from .linear import kernel_modules as linear_modules, linear
 from .registry import register_mixer
 
 DECODE_SPLIT_TOKENS = 256     # keys per run of the plain decode kernel; fixed, so results do not depend on the batch
@@ -65,7 +65,7 @@ class GroupedQueryAttention(Mixer):
             self.k_norm_w = weights[px + n["k_norm"]].to(torch.float32).contiguous()
 
     def kernel_modules(self):
-        mods = ["rope_kv", "gemm_small", "gemm_stream", "gemm_tc"]
+        mods = ["rope_kv", *linear_modules(self.runtime.dtype)]
         if ops.mma_attention_fits(self.runtime.dtype, self.head_dim, ops.PAGE_SIZE):
             mods.append("attention_mma")
             if ops.tc_attention_fits(self.runtime.dtype, self.head_dim, ops.PAGE_SIZE, self.n_heads // self.n_kv_heads):

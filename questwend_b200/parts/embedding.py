@@ -7,7 +7,7 @@ import torch
 from ..kernels import ops
 from ..weights.manifest import MATRIX, TensorSpec
 from .base import Part
-from .linear import linear
+from .linear import kernel_modules as linear_modules, linear
 from .registry import register_embedding, register_head
 
 
@@ -59,7 +59,7 @@ class OutputHead(Part):
             self.weight = weights[self.name]
 
     def kernel_modules(self):
-        return ("gemm_small", "gemm_stream", "gemm_tc")
+        return linear_modules(self.runtime.dtype)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return linear(x, self.weight)

@@ -18,6 +18,11 @@ import torch
 from ..kernels import ops
 
 
+def kernel_modules(dtype: torch.dtype) -> tuple:
+    """The kernel modules that ``linear`` may launch for this engine dtype."""
+    return ("gemm_small", "gemm_stream", "gemm_tc") if dtype == torch.bfloat16 else ("gemm_small",)
+
+
 def require_true_fp32() -> None:
     torch.backends.cuda.matmul.allow_tf32 = False
     torch.backends.cudnn.allow_tf32 = False

@@ -6,7 +6,7 @@ import torch
 from ..kernels import ops
 from ..weights.manifest import MATRIX, TensorSpec
 from .base import FeedForward
-from .linear import linear, linear_swiglu
+from .linear import kernel_modules as linear_modules, linear, linear_swiglu
 from .registry import register_feed_forward
 
 
@@ -34,7 +34,7 @@ class GatedMLP(FeedForward):
         self.w_down = weights[px + n["down"]]
 
     def kernel_modules(self):
-        return ("elementwise", "gemm_small", "gemm_stream", "gemm_tc")
+        return ("elementwise", *linear_modules(self.runtime.dtype))
 
     adds_to_residual = True
 

@@ -6,6 +6,7 @@
 
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <cstring>
 #include <stdarg.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -51,14 +52,24 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // QWB200_PDL: unset or "some" = only the kernels that ask for it (qwb_launch_early: the weight-streaming
-// product, whose first loads do not depend on the kernel before it); "all" = every kernel; "0" = none.
-static int qwb_pdl_mode() {
+// product, whose first loads do not depend on the kernel before it); "all" = every kernel; "0" = none;
+// a comma-separated list of kernel modules ("elementwise,rope_kv") = those too, for experiments.
+#ifndef QWB_MODULE_NAME
+#define QWB_MODULE_NAME ""
+#endif
+static int qwb_pdl_mode() {        // 0 none, 1 those that ask, 2 every kernel of this module
     static int mode = -1;
     if (mode < 0) {
         const char* e = getenv("QWB200_PDL");
-        if (!e || !e[0] || e[0] == 's') mode = 1;
-        else if (e[0] == 'a') mode = 2;
-        else mode = 0;
+        if (!e || !e[0] || !strcmp(e, "some")) mode = 1;
+        else if (!strcmp(e, "all")) mode = 2;
+        else if (!strcmp(e, "0") || !strcmp(e, "none")) mode = 0;
+        else {
+            mode = 1;
+            const size_t n = strlen(QWB_MODULE_NAME);
+            for (const char* p = e; n && (p = strstr(p, QWB_MODULE_NAME)); p += n)
+                if ((p == e || p[-1] == ',') && (p[n] == 0 || p[n] == ',')) { mode = 2; break; }
+        }
     }
     return mode;
 }

@@ -146,32 +146,36 @@ extern "C" int qwb_rmsnorm(const float* x, const float* delta, float* sum_out, c
 
 // ---------------------------------------------------------------------------------
 // a[t,f] = silu(g[t,f]) * u[t,f], silu(x) = x / (1 + exp(-x)), from one [T, 2F] float
-// matrix whose first F columns are the gate and last F the up projection (the reference:
-// core/runtime.cpp:1074-1076, ggml-cuda/unary.cuh:96-98).
+// matrix (the reference: core/runtime.cpp:1074-1076, ggml-cuda/unary.cuh:96-98).
+// interleave 0: the first F columns are the gate and the last F the up projection;
+// interleave G > 0 (F a multiple of G): for every G features, their G gates and then their G ups.
 // ---------------------------------------------------------------------------------
 template <typename TOut>
-__global__ void silu_mul_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int T, int F) {
+__global__ void silu_mul_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int T, int F, int interleave) {
     pdl_wait();
     pdl_launch_dependents();
     const size_t n = (size_t)T * F;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const size_t t = i / F, f = i - t * F;
-        const float g = gu[t * 2 * F + f];
-        const float u = gu[t * 2 * F + F + f];
+        const size_t gate_at = interleave > 0 ? (f / interleave) * 2 * interleave + f % interleave : f;
+        const float g = gu[t * 2 * F + gate_at];
+        const float u = gu[t * 2 * F + gate_at + (interleave > 0 ? interleave : F)];
         out[i] = from_f32<TOut>(g / (1.f + expf(-g)) * u);
     }
 }
 
-extern "C" int qwb_silu_mul(const float* gate_up, void* out, int out_dtype, int T, int F, cudaStream_t stream) {
+extern "C" int qwb_silu_mul(const float* gate_up, void* out, int out_dtype, int T, int F, int interleave, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (F <= 0) return qwb_fail(QWB_ERR_ARG, "silu_mul: bad width %d", F);
+    if (interleave < 0 || (interleave > 0 && F % interleave))
+        return qwb_fail(QWB_ERR_ARG, "silu_mul: %d features cannot be interleaved in groups of %d", F, interleave);
     const size_t n = (size_t)T * F;
     const int block = 256;
     const int grid = (int)((n + block - 1) / block < 148 * 16 ? (n + block - 1) / block : 148 * 16);
     if (out_dtype == QWB_DT_F32)
-        qwb_launch(silu_mul_kernel<float>, grid, block, 0, stream, gate_up, (float*)out, T, F);
+        qwb_launch(silu_mul_kernel<float>, grid, block, 0, stream, gate_up, (float*)out, T, F, interleave);
     else if (out_dtype == QWB_DT_BF16)
-        qwb_launch(silu_mul_kernel<bf16>, grid, block, 0, stream, gate_up, (bf16*)out, T, F);
+        qwb_launch(silu_mul_kernel<bf16>, grid, block, 0, stream, gate_up, (bf16*)out, T, F, interleave);
     else
         return qwb_fail(QWB_ERR_ARG, "silu_mul: unknown dtype %d", out_dtype);
     return qwb_check_launch("silu_mul");

@@ -11,6 +11,9 @@
 // no shuffle is needed.  The warps' partial sums meet in shared memory and are added in
 // warp order; how K is split depends on N and K only, so a row's result depends neither on the
 // batch nor on timing.
+// With the SwiGLU epilogue W holds, for every 8 features, their 8 gate rows and then their 8 up
+// rows: a block's 16 rows are the gates and ups of 8 features, one thread's accumulators hold a
+// feature's gate (row g) and up (row g + 8), and the block writes a = silu(gate) * up as bfloat16.
 // (The reference's counterpart for few rows: ggml-cuda/mmvf.cu and mmf.cuh.)
 #include "common.cuh"
 
@@ -31,10 +34,10 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, uint32_t a0, uint32_t a
 }
 
 // NT = number of 8-row tiles of x handled at once (M <= 8 * NT).
-template <int NT, int U, int GS_WARPS>
+template <int NT, int U, int GS_WARPS, bool SWIGLU>
 __global__ void __launch_bounds__(GS_WARPS * 32)
 gemm_stream_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const float* residual, float* y,
-                   int M, int N, int K) {
+                   bf16* __restrict__ act, int M, int N, int K) {
     __shared__ float part[GS_WARPS][NT][4][32];          // [warp][tile][c register][lane]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -104,33 +107,44 @@ gemm_stream_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const
 
     // c0: (row g, col 2t), c1: (row g, col 2t+1), c2: (row g+8, col 2t), c3: (row g+8, col 2t+1);
     // rows are rows of W (outputs n), columns are rows of x (m).
+    __shared__ float sums[SWIGLU ? NT : 1][4][32];       // SwiGLU: the block's sums, before gate meets up
     for (int idx = threadIdx.x; idx < NT * 4 * 32; idx += blockDim.x) {
         const int j = idx >> 7, r = (idx >> 5) & 3, ln = idx & 31;
         float s = 0.f;
 #pragma unroll
         for (int w = 0; w < GS_WARPS; ++w) s += part[w][j][r][ln];
-        const int gg = ln >> 2, tt = ln & 3;
-        const int n = n0 + gg + ((r & 2) ? 8 : 0);
-        const int m = 8 * j + 2 * tt + (r & 1);
-        if (n < N && m < M) {
-            const size_t at = (size_t)m * N + n;
-            y[at] = residual ? residual[at] + s : s;
+        if (SWIGLU) {
+            sums[j][r][ln] = s;
+        } else {
+            const int gg = ln >> 2, tt = ln & 3;
+            const int n = n0 + gg + ((r & 2) ? 8 : 0);
+            const int m = 8 * j + 2 * tt + (r & 1);
+            if (n < N && m < M) {
+                const size_t at = (size_t)m * N + n;
+                y[at] = residual ? residual[at] + s : s;
+            }
+        }
+    }
+    if (SWIGLU) {                                         // rows g are gates, rows g + 8 the ups of the same features
+        __syncthreads();
+        const int F = N >> 1, f0 = n0 >> 1;               // features in all; the block's first feature
+        for (int idx = threadIdx.x; idx < NT * 2 * 32; idx += blockDim.x) {
+            const int j = idx >> 6, r = (idx >> 5) & 1, ln = idx & 31;
+            const float gate = sums[j][r][ln], up = sums[j][r + 2][ln];
+            const int f = f0 + (ln >> 2), m = 8 * j + 2 * (ln & 3) + r;
+            if (f < F && m < M) act[(size_t)m * F + f] = __float2bfloat16_rn(gate / (1.f + expf(-gate)) * up);
         }
     }
 }
 
-extern "C" int qwb_gemm_stream(const void* x, const void* W, const float* residual, float* y, int M, int N, int K,
-                               cudaStream_t stream) {
-    if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || K % 8) return qwb_fail(QWB_ERR_ARG, "gemm_stream: inner size %d is not a multiple of 8", K);
-    if (M > 16) return qwb_fail(QWB_ERR_ARG, "gemm_stream: %d rows; this kernel is for at most 16", M);
-    if ((uintptr_t)x % 16 || (uintptr_t)W % 16) return qwb_fail(QWB_ERR_ARG, "gemm_stream: operands must be 16-byte aligned");
+template <bool SWIGLU>
+static int launch_stream(const bf16* xp, const bf16* wp, const float* residual, float* y, bf16* act, int M, int N, int K,
+                         cudaStream_t stream) {
     const int grid = (N + GS_ROWS - 1) / GS_ROWS;
-    const bf16* xp = (const bf16*)x;
-    const bf16* wp = (const bf16*)W;
     // How deep each warp prefetches (U blocks of 32 k) and how many warps split K, by what measured best at the sizes of
     // a Qwen3-8B decode step: long rows want deep prefetch; short rows with few blocks want more warps; else shallow.
-#define GS_GO(NT, U, WARPS) qwb_launch_early(gemm_stream_kernel<NT, U, WARPS>, grid, WARPS * 32, 0, stream, xp, wp, residual, y, M, N, K)
+#define GS_GO(NT, U, WARPS) \
+    qwb_launch_early(gemm_stream_kernel<NT, U, WARPS, SWIGLU>, grid, WARPS * 32, 0, stream, xp, wp, residual, y, act, M, N, K)
 #define GS_PICK(NT)                                      \
     do {                                                 \
         if (K >= 8192) GS_GO(NT, 8, 8);                  \
@@ -142,4 +156,27 @@ extern "C" int qwb_gemm_stream(const void* x, const void* W, const float* residu
 #undef GS_PICK
 #undef GS_GO
     return qwb_check_launch("gemm_stream");
+}
+
+static int check_stream(const void* x, const void* W, int M, int K) {
+    if (K <= 0 || K % 8) return qwb_fail(QWB_ERR_ARG, "gemm_stream: inner size %d is not a multiple of 8", K);
+    if (M > 16) return qwb_fail(QWB_ERR_ARG, "gemm_stream: %d rows; this kernel is for at most 16", M);
+    if ((uintptr_t)x % 16 || (uintptr_t)W % 16) return qwb_fail(QWB_ERR_ARG, "gemm_stream: operands must be 16-byte aligned");
+    return 0;
+}
+
+extern "C" int qwb_gemm_stream(const void* x, const void* W, const float* residual, float* y, int M, int N, int K,
+                               cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (int rc = check_stream(x, W, M, K)) return rc;
+    return launch_stream<false>((const bf16*)x, (const bf16*)W, residual, y, nullptr, M, N, K, stream);
+}
+
+// W [2 F, K]: for every 8 features their 8 gate rows, then their 8 up rows (F a multiple of 8).
+// act bfloat16 [M, F] = silu(x gate^T) * (x up^T).
+extern "C" int qwb_gemm_stream_swiglu(const void* x, const void* W, void* act, int M, int F, int K, cudaStream_t stream) {
+    if (M <= 0 || F <= 0) return 0;
+    if (F % 8) return qwb_fail(QWB_ERR_ARG, "gemm_stream: %d features are not a multiple of 8", F);
+    if (int rc = check_stream(x, W, M, K)) return rc;
+    return launch_stream<true>((const bf16*)x, (const bf16*)W, nullptr, nullptr, (bf16*)act, M, 2 * F, K, stream);
 }

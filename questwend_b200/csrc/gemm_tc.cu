@@ -2,7 +2,8 @@
 //     y[M,N] = x[M,K] W[N,K]^T, 32-bit sums in tensor memory, with the epilogue fused:
 //       EPI_STORE   y float                               (the q/k/v projection)
 //       EPI_ADD     y += product, y float                 (o and down projections onto the residual stream)
-//       EPI_SWIGLU  a = silu(gate) * up as bfloat16       (gate/up projection; W holds the F gate rows, then the F up rows)
+//       EPI_SWIGLU  a = silu(gate) * up as bfloat16       (gate/up projection; W holds, for every 8 features, their 8 gate
+//                                                          rows and then their 8 up rows)
 //
 // One block per SM walks over 128 x BN tiles of y (tile t, t + blocks, ...).  Six warps with fixed roles:
 //   warp 0  one lane issues the TMA loads: per 64 columns of k a 128 x 64 tile of x and a BN x 64 tile of W, into a ring
@@ -117,7 +118,7 @@ struct TcSmem {
 template <int BN, int EPI>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-               const __grid_constant__ CUtensorMap map_out, int M, int N, int K, int up_row0, int* error) {
+               const __grid_constant__ CUtensorMap map_out, int M, int N, int K, int* error) {
     constexpr int STAGES = TcSmem<BN>::STAGES;
     constexpr uint32_t A_BYTES = TcSmem<BN>::A_BYTES, B_BYTES = TcSmem<BN>::B_BYTES;
     constexpr int COLS_PER_TILE = EPI == EPI_SWIGLU ? BN / 2 : BN;     // output columns of one tile
@@ -165,12 +166,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     if (!ok) break;
                     mbar_expect_tx(&full_bar[s], A_BYTES + B_BYTES);
                     tma_load_2d(a_tiles + (size_t)s * A_BYTES, &map_x, &full_bar[s], kb * TC_BK, m0);
-                    if (EPI == EPI_SWIGLU) {
-                        tma_load_2d(b_tiles + (size_t)s * B_BYTES, &map_w, &full_bar[s], kb * TC_BK, n0);
-                        tma_load_2d(b_tiles + (size_t)s * B_BYTES + B_BYTES / 2, &map_w, &full_bar[s], kb * TC_BK, up_row0 + n0);
-                    } else {
-                        tma_load_2d(b_tiles + (size_t)s * B_BYTES, &map_w, &full_bar[s], kb * TC_BK, n0);
-                    }
+                    // SwiGLU: COLS_PER_TILE features are BN rows of W, gate and up interleaved in eights
+                    tma_load_2d(b_tiles + (size_t)s * B_BYTES, &map_w, &full_bar[s], kb * TC_BK, EPI == EPI_SWIGLU ? 2 * n0 : n0);
                 }
             }
             if (!ok) {
@@ -240,25 +237,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 }
                 uint4* my_row = reinterpret_cast<uint4*>(st + lane * 128);
                 if (EPI == EPI_SWIGLU) {
-                    constexpr int HALF = BN / 2;
+                    // 64 features = 128 accumulator columns: per 16 columns 8 gates, then the 8 ups of the same features
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {    // 2 x 32 features -> 64 bfloat16 = one 128-byte row
-                        uint32_t g[32], u[32];
-                        tmem_ld32(taddr + ch * 64 + half * 32, g);
-                        tmem_ld32(taddr + HALF + ch * 64 + half * 32, u);
+                    for (int q = 0; q < 4; ++q) {             // 4 x 16 features -> 64 bfloat16 = one 128-byte row
+                        uint32_t v[32];
+                        tmem_ld32(taddr + ch * 128 + q * 32, v);
 #pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
+                        for (int grp = 0; grp < 2; ++grp) {
                             uint32_t pk[4];
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
-                                const float g0 = __uint_as_float(g[i + 2 * j]), g1 = __uint_as_float(g[i + 2 * j + 1]);
-                                const float a0 = g0 / (1.f + __expf(-g0)) * __uint_as_float(u[i + 2 * j]);
-                                const float a1 = g1 / (1.f + __expf(-g1)) * __uint_as_float(u[i + 2 * j + 1]);
-                                __nv_bfloat162 v = __floats2bfloat162_rn(a0, a1);
-                                pk[j] = *reinterpret_cast<uint32_t*>(&v);
+                                const float g0 = __uint_as_float(v[16 * grp + 2 * j]), g1 = __uint_as_float(v[16 * grp + 2 * j + 1]);
+                                const float a0 = g0 / (1.f + __expf(-g0)) * __uint_as_float(v[16 * grp + 8 + 2 * j]);
+                                const float a1 = g1 / (1.f + __expf(-g1)) * __uint_as_float(v[16 * grp + 8 + 2 * j + 1]);
+                                __nv_bfloat162 r = __floats2bfloat162_rn(a0, a1);
+                                pk[j] = *reinterpret_cast<uint32_t*>(&r);
                             }
-                            const int piece = half * 4 + i / 8;
-                            my_row[piece ^ (lane & 7)] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                            my_row[(q * 2 + grp) ^ (lane & 7)] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                         }
                     }
                 } else {
@@ -335,7 +330,7 @@ template <int BN, int EPI>
 static int launch_tc(const void* x, const void* W, void* out, int M, int N, int K, int w_rows, int* error, cudaStream_t stream) {
     CUtensorMap map_x, map_w, map_out;
     if (int rc = make_map(&map_x, x, M, K, TC_BM, "x")) return rc;
-    if (int rc = make_map(&map_w, W, w_rows, K, EPI == EPI_SWIGLU ? BN / 2 : BN, "W")) return rc;
+    if (int rc = make_map(&map_w, W, w_rows, K, BN, "W")) return rc;
     if (int rc = make_map(&map_out, out, M, N, 32, "out", EPI != EPI_SWIGLU)) return rc;
     const size_t smem = TcSmem<BN>::BYTES;
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -349,7 +344,7 @@ static int launch_tc(const void* x, const void* W, void* out, int M, int N, int 
         if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
     }
     dim3 grid((unsigned)(n_tiles < n_sm ? n_tiles : n_sm));          // one block per SM, each walks over its tiles
-    e = qwb_launch(gemm_tc_kernel<BN, EPI>, grid, TC_THREADS, smem, stream, map_x, map_w, map_out, M, N, K, N, error);
+    e = qwb_launch(gemm_tc_kernel<BN, EPI>, grid, TC_THREADS, smem, stream, map_x, map_w, map_out, M, N, K, error);
     if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "gemm_tc: launch failed: %s", cudaGetErrorString(e));
     return qwb_check_launch("gemm_tc");
 }
@@ -357,7 +352,7 @@ static int launch_tc(const void* x, const void* W, void* out, int M, int N, int 
 // x [M, K] and W bfloat16, 16-byte aligned, K a multiple of 8.  `error` is one int on the device, 0 before the call; a
 // value other than 0 afterwards means a wait inside the kernel gave up (the result is then not valid).
 //   epilogue 0: W [N, K], out float [M, N]          1: the same, out += product
-//   epilogue 2: W [2 N, K] (N gate rows, then N up rows), out bfloat16 [M, N] = silu(gate) * up
+//   epilogue 2: W [2 N, K] (for every 8 features their 8 gate rows, then their 8 up rows), out bfloat16 [M, N] = silu(gate) * up
 extern "C" int qwb_gemm_tc(const void* x, const void* W, void* out, int epilogue, int M, int N, int K, int tile_n, int* error,
                            cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;

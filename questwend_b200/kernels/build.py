@@ -100,7 +100,8 @@ def compile_module(module: str, verbose: bool = True) -> str:
         raise KernelBuildError(f"kernel module '{module}' is not built and nvcc was not found "
                                f"(looked on PATH and in /usr/local/cuda/bin)")
     tmp = f"{lib}.{os.getpid()}.tmp"
-    cmd = [nvcc] + NVCC_FLAGS + ["-I", CSRC, "-o", tmp, os.path.join(CSRC, f"{module}.cu")] + EXTRA_FLAGS.get(module, [])
+    cmd = ([nvcc] + NVCC_FLAGS + [f'-DQWB_MODULE_NAME="{module}"', "-I", CSRC, "-o", tmp, os.path.join(CSRC, f"{module}.cu")]
+           + EXTRA_FLAGS.get(module, []))
     if verbose:
         _log(f"compiling kernel module '{module}' for sm_100a (first use) ...")
     t0 = time.time()

@@ -103,14 +103,28 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     return out
 
 
-def silu_mul(gate_up: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
-    """silu(gate) * up from a float32 [T, 2F] matrix (gate columns first)."""
+GATE_UP_GROUP = 8       # the fused products want gate and up rows interleaved in groups of this many features
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, group: int = GATE_UP_GROUP) -> torch.Tensor:
+    """[F, K] gate and up rows as one [2F, K] matrix: for every ``group`` features their gate rows, then their up rows.
+    A reordering of rows; the products are the same numbers."""
+    F, K = gate.shape
+    if up.shape != gate.shape or F % group:
+        raise KernelError(f"interleave_gate_up: shapes {tuple(gate.shape)}, {tuple(up.shape)} with groups of {group}")
+    return torch.cat([gate.reshape(F // group, group, K), up.reshape(F // group, group, K)], dim=1).reshape(2 * F, K).contiguous()
+
+
+def silu_mul(gate_up: torch.Tensor, out_dtype: torch.dtype, interleave: int = 0) -> torch.Tensor:
+    """silu(gate) * up from a float32 [T, 2F] matrix: gate columns first (``interleave`` 0), or for every
+    ``interleave`` features their gates and then their ups."""
     _need(gate_up, "gate_up", torch.float32, 2)
     T, F2 = gate_up.shape
     if F2 % 2:
         raise KernelError(f"silu_mul: {F2} columns cannot be split into gate and up")
     out = torch.empty((T, F2 // 2), dtype=out_dtype, device=gate_up.device)
-    _call("elementwise", "qwb_silu_mul", _ptr(gate_up), _ptr(out), _i(_dt(out_dtype)), _i(T), _i(F2 // 2), _stream())
+    _call("elementwise", "qwb_silu_mul", _ptr(gate_up), _ptr(out), _i(_dt(out_dtype)), _i(T), _i(F2 // 2), _i(interleave),
+          _stream())
     return out
 
 
@@ -306,6 +320,20 @@ def gemm_stream(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor | 
     return out
 
 
+def gemm_stream_swiglu(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """silu(x gate^T) * (x up^T) as bfloat16 [M, F] for bfloat16 x [M, K], M <= 16, and the weight [2F, K] with gate and up
+    rows interleaved in groups of 8 features (``interleave_gate_up``)."""
+    _need(x, "x", torch.bfloat16, 2)
+    _need(weight, "weight", torch.bfloat16, 2)
+    M, K = x.shape
+    if weight.shape[1] != K or weight.shape[0] % 2:
+        raise KernelError(f"gemm_stream_swiglu: x is {tuple(x.shape)}, the weight {tuple(weight.shape)}")
+    F = weight.shape[0] // 2
+    out = torch.empty((M, F), dtype=torch.bfloat16, device=x.device)
+    _call("gemm_stream", "qwb_gemm_stream_swiglu", _ptr(x), _ptr(weight), _ptr(out), _i(M), _i(F), _i(K), _stream())
+    return out
+
+
 _TC_ERROR: dict = {}    # device -> one int32 that a gemm_tc kernel sets when one of its waits gives up
 TC_EPILOGUES = {"store": 0, "add": 1, "swiglu": 2}
 
@@ -334,7 +362,8 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, epilogue: str = "store", out:
     """bfloat16 x [M, K] times bfloat16 weight transposed on the tcgen05 tensor cores.
 
     "store": weight [N, K] -> float32 [M, N].  "add": the same, added onto ``out``.
-    "swiglu": weight [2F, K] (F gate rows, then F up rows) -> bfloat16 [M, F] = silu(gate) * up.
+    "swiglu": weight [2F, K] (gate and up rows interleaved in groups of 8 features, ``interleave_gate_up``)
+    -> bfloat16 [M, F] = silu(gate) * up.
     """
     _need(x, "x", torch.bfloat16, 2)
     _need(weight, "weight", torch.bfloat16, 2)

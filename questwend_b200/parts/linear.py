@@ -59,8 +59,13 @@ def linear(x: torch.Tensor, weight: torch.Tensor, add_to: torch.Tensor | None = 
     return torch.mm(x, weight.t())
 
 
-def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
-    """silu(x Wg^T) * (x Wu^T) for the stacked weight [2F, K] (gate rows first) -> [M, F] in ``out_dtype``."""
-    if _tc_fits(x, weight_gate_up, weight_gate_up.shape[0] // 2) and out_dtype == torch.bfloat16:
-        return ops.gemm_tc(x, weight_gate_up, epilogue="swiglu", tile_n=256)
-    return ops.silu_mul(linear(x, weight_gate_up), out_dtype)
+def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor, out_dtype: torch.dtype, interleave: int = 0) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) for the stacked weight [2F, K] -> [M, F] in ``out_dtype``.  ``interleave`` 0: gate rows
+    first; ``ops.GATE_UP_GROUP``: gate and up rows interleaved in groups of that many features, which lets the products
+    with a fused epilogue find a feature's gate and up in one thread."""
+    if interleave == ops.GATE_UP_GROUP and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16:
+        if x.shape[0] <= ops.STREAM_M and x.shape[1] % 8 == 0:
+            return ops.gemm_stream_swiglu(x, weight_gate_up)
+        if _tc_fits(x, weight_gate_up, weight_gate_up.shape[0] // 2):
+            return ops.gemm_tc(x, weight_gate_up, epilogue="swiglu", tile_n=256)
+    return ops.silu_mul(linear(x, weight_gate_up), out_dtype, interleave)

@@ -75,6 +75,11 @@ def test_rmsnorm_refuses_a_row_that_does_not_fit():
 def test_silu_mul(out_dtype):
     gu = (torch.randn(5, 2 * 77, generator=torch.Generator().manual_seed(1)) * 4).to(DEV)
     close(ops.silu_mul(gu, out_dtype), pm.swiglu(f64(gu)[:, :77], f64(gu)[:, 77:]), out_dtype)
+    # the same with gates and ups interleaved in groups of 7 features
+    inter = gu.reshape(5, 2, 11, 7).permute(0, 2, 1, 3).reshape(5, 2 * 77).contiguous()
+    assert torch.equal(ops.silu_mul(inter, out_dtype, interleave=7), ops.silu_mul(gu, out_dtype))
+    with pytest.raises(KernelError, match="interleaved"):
+        ops.silu_mul(gu, out_dtype, interleave=8)
 
 
 def test_add_inplace_and_decode_advance():
@@ -382,6 +387,25 @@ def test_gemm_tc(M, N, K, tile_n):
     close(added, f64(base) + ref, torch.float32, scale=np.abs(ref).max() * 4)
 
 
+@pytest.mark.parametrize("M", [1, 5, 8, 11, 16])
+@pytest.mark.parametrize("F,K", [(8, 64), (104, 200), (1000, 1024), (24, 4104), (2504, 8200)])
+def test_gemm_stream_swiglu(M, F, K):
+    g = torch.Generator().manual_seed(M * 1000 + F)
+    x = (torch.randn(M, K, generator=g) * 0.3).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(2 * F, K, generator=g) * 0.3).to(torch.bfloat16).to(DEV)
+    gu = f64(x) @ f64(w).T
+    out = ops.gemm_stream_swiglu(x, ops.interleave_gate_up(w[:F], w[F:]))
+    assert out.dtype == torch.bfloat16 and tuple(out.shape) == (M, F)
+    close(out, pm.swiglu(gu[:, :F], gu[:, F:]), torch.bfloat16)
+    # the same numbers as the product followed by the separate kernel, and a row does not depend on the others
+    assert torch.equal(out, ops.silu_mul(ops.gemm_stream(x, w), torch.bfloat16))
+    assert torch.equal(ops.gemm_stream_swiglu(x[:1], ops.interleave_gate_up(w[:F], w[F:]))[0], out[0])
+    with pytest.raises(KernelError, match="multiple of 8"):
+        ops.gemm_stream_swiglu(x, w[:2 * F - 4])
+    with pytest.raises(KernelError, match="interleave_gate_up"):
+        ops.interleave_gate_up(w[:F - 1], w[F:2 * F - 1])
+
+
 @pytest.mark.parametrize("M,F,K", [(128, 128, 64), (200, 200, 96), (64, 1000, 512), (300, 64, 4096)])
 @pytest.mark.parametrize("tile_n", [128, 256])
 def test_gemm_tc_swiglu(M, F, K, tile_n):
@@ -390,7 +414,7 @@ def test_gemm_tc_swiglu(M, F, K, tile_n):
     w = (torch.randn(2 * F, K, generator=g) * 0.3).to(torch.bfloat16).to(DEV)
     gu = f64(x) @ f64(w).T
     ref = pm.swiglu(gu[:, :F], gu[:, F:])
-    out = ops.gemm_tc(x, w, epilogue="swiglu", tile_n=tile_n)
+    out = ops.gemm_tc(x, ops.interleave_gate_up(w[:F], w[F:]), epilogue="swiglu", tile_n=tile_n)
     ops.gemm_tc_check(DEV)
     assert out.dtype == torch.bfloat16
     close(out, ref, torch.bfloat16)

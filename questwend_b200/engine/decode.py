@@ -15,6 +15,7 @@ bucket of 32 (core/runtime.cpp:1768-1829), replayed as a CUDA graph inside ggml.
 """
 from __future__ import annotations
 
+import gc
 import math
 
 import numpy as np
@@ -113,9 +114,18 @@ class DecodeRunner:
         torch.cuda.current_stream().synchronize()
         g = torch.cuda.CUDAGraph()
         before = ops.LAUNCHES[0]
-        with torch.cuda.graph(g):
-            self._forward_and_sample(bucket)
-            self._advance()
+        # No garbage collection while the stream is capturing: an unreachable engine's graphs would be destroyed
+        # in the middle of it, which CUDA refuses during a capture and which invalidates the capture.
+        collect_again = gc.isenabled()
+        gc.collect()
+        gc.disable()
+        try:
+            with torch.cuda.graph(g):
+                self._forward_and_sample(bucket)
+                self._advance()
+        finally:
+            if collect_again:
+                gc.enable()
         self.launches_per_step = ops.LAUNCHES[0] - before
         return g
 

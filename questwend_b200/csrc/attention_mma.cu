@@ -16,10 +16,10 @@
 //
 //   prefill: 4 warps x 16 rows = 64 rows per block (64 / group tokens), all warps walk the
 //            same tiles, double buffered.
-//   decode : one token per sequence; the rows are the group's heads (padded to 16); the
-//            4 warps take different pages of the block's run of keys and their partial
-//            results meet in shared memory.  Runs, scratch layout and the combine kernel
-//            are those of attention.cu.
+//   decode : one token per sequence; the rows are the group's heads (padded to 16); a
+//            block is one warp that takes a run of the sequence's pages; the runs' partial
+//            results are merged by a combine kernel.  A run's length follows from the
+//            sequence's own length alone, so a result does not depend on the batch.
 #include "common.cuh"
 
 #define AM_TILE 64          // keys per tile = tokens per cache page
@@ -261,29 +261,47 @@ attn_mma_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
 }
 
 // ---------------------------------------------------------------------------------
-// decode: block = (run of keys, key/value head and head chunk, sequence) with WARPS warps; warp w takes the run's
-// pages w, w + WARPS, ...  With runs of one page (the engine's choice) a block is a single warp that holds
-// 32 KB of shared memory, so seven of them share an SM and one's loads overlap another's arithmetic; its partial
-// result goes straight from registers to the scratch that the combine kernel reads.
+// decode: block = (run of keys, key/value head and head chunk, sequence), a single warp that takes the run's pages
+// one after the other.  It holds 32 KB of shared memory, so seven blocks share an SM and one's loads overlap
+// another's arithmetic; its partial result goes straight from registers to the scratch that the combine kernel reads.
+// How long a run is depends on the sequence's own length only (never on the batch): short sequences are cut into
+// single pages, longer ones into about `runs_target` runs of up to `run_pages_max` pages, which keeps the number
+// of partial results, and the work of combining them, small against the keys read.
 // ---------------------------------------------------------------------------------
-template <int HD, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32)
+__host__ __device__ __forceinline__ int run_pages_for(int len, int runs_target, int run_pages_max) {
+    const int pages = (len + AM_TILE - 1) / AM_TILE;
+    const int want = (pages + runs_target - 1) / runs_target;
+    return want < 1 ? 1 : (want > run_pages_max ? run_pages_max : want);
+}
+
+// The most runs that any sequence of up to max_len keys is cut into (the grid's width and the scratch's size).
+static int max_runs_for(int max_len, int runs_target, int run_pages_max) {
+    const int pages = (max_len + AM_TILE - 1) / AM_TILE;
+    if (pages <= runs_target) return pages < 1 ? 1 : pages;
+    if (pages <= runs_target * run_pages_max) return runs_target;
+    return (pages + run_pages_max - 1) / run_pages_max;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(32)
 attn_mma_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                        const int* __restrict__ page_table, const int* __restrict__ seq_len, float* __restrict__ part_acc,
                        float* __restrict__ part_m, float* __restrict__ part_l, bf16* __restrict__ out, int Hq, int Hkv,
-                       int table_width, float scale, int window, int split_tokens, int max_runs, int Gc, int chunks) {
+                       int table_width, float scale, int window, int runs_target, int run_pages_max, int max_runs, int Gc,
+                       int chunks) {
     pdl_wait();
     pdl_launch_dependents();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int b = blockIdx.z, run = blockIdx.x;
     const int len = seq_len[b];
+    const int split_tokens = run_pages_for(len, runs_target, run_pages_max) * AM_TILE;
     const int k_lo = window > 0 ? max(0, len - window) : 0;
-    const int run_first = k_lo / split_tokens, run_end = (len + split_tokens - 1) / split_tokens;
+    const int run_first = k_lo / split_tokens, run_end = min(max_runs, (len + split_tokens - 1) / split_tokens);
     if (run < run_first || run >= run_end) return;
     const int kvh = blockIdx.y / chunks, chunk = blockIdx.y % chunks;
     const int G = Hq / Hkv;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    bf16* my_tiles = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * 2 * AM_TILE * HD;   // K then V, this warp's own
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    bf16* my_tiles = reinterpret_cast<bf16*>(smem_raw);                         // K then V
 
     int row_pos[2];
     const bf16* qrow[2];
@@ -303,7 +321,7 @@ attn_mma_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
     const int tok_begin = run * split_tokens, tok_end = min(len, tok_begin + split_tokens);
     const int* pages = page_table + (size_t)b * table_width;
     const float sl2 = scale * 1.4426950408889634f;
-    for (int base = tok_begin + warp * AM_TILE; base < tok_end; base += WARPS * AM_TILE) {
+    for (int base = tok_begin; base < tok_end; base += AM_TILE) {
         if (base + AM_TILE <= k_lo) continue;                                  // a page wholly before the window
         const size_t src = ((size_t)pages[base / AM_TILE] * Hkv + kvh) * AM_TILE * HD;
         const int n_valid = min(AM_TILE, len - base);
@@ -320,86 +338,64 @@ attn_mma_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
         l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
     }
     const bool single = (run_end - run_first) == 1;
-    if (WARPS == 1) {
-        // one warp: its registers are the run's result
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const int r = g + 8 * h, head_in = chunk * Gc + r;
-            if (r >= Gc || head_in >= G) continue;
-            const int head = kvh * G + head_in;
-            if (single) {
-                const float inv = 1.f / l[h];
-                bf16* dst = out + ((size_t)b * Hq + head) * HD;
-#pragma unroll
-                for (int d = 0; d < HD / 8; ++d)
-                    *reinterpret_cast<uint32_t*>(dst + 8 * d + 2 * t) = pack_bf16(o[d][2 * h] * inv, o[d][2 * h + 1] * inv);
-            } else {
-                const size_t at = ((size_t)b * Hq + head) * max_runs + run;
-                float* dst = part_acc + at * HD;
-#pragma unroll
-                for (int d = 0; d < HD / 8; ++d)
-                    *reinterpret_cast<float2*>(dst + 8 * d + 2 * t) = make_float2(o[d][2 * h], o[d][2 * h + 1]);
-                if (t == 0) { part_m[at] = m[h] * scale; part_l[at] = l[h]; }   // the combine kernel works with scaled scores
-            }
-        }
-        return;
-    }
-    // several warps: their partial results meet in shared memory, [warp][16 rows][HD + 2]
-    __syncthreads();
-    float* merge = reinterpret_cast<float*>(smem_raw);
-    constexpr int RS = HD + 2;
+    // the warp's registers are the run's result
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-        float* row = merge + ((size_t)warp * 16 + g + 8 * h) * RS;
-#pragma unroll
-        for (int d = 0; d < HD / 8; ++d) { row[8 * d + 2 * t] = o[d][2 * h]; row[8 * d + 2 * t + 1] = o[d][2 * h + 1]; }
-        if (t == 0) { row[HD] = m[h]; row[HD + 1] = l[h]; }
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < Gc * HD; idx += blockDim.x) {
-        const int r = idx / HD, d = idx - r * HD, head_in = chunk * Gc + r;
-        if (head_in >= G) continue;
-        float M = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < WARPS; ++w) M = fmaxf(M, merge[((size_t)w * 16 + r) * RS + HD]);
-        float L = 0.f, acc = 0.f;
-#pragma unroll
-        for (int w = 0; w < WARPS; ++w) {
-            const float* row = merge + ((size_t)w * 16 + r) * RS;
-            const float f = row[HD] == -INFINITY ? 0.f : exp2f((row[HD] - M) * sl2);
-            L += row[HD + 1] * f;
-            acc += row[d] * f;
-        }
+        const int r = g + 8 * h, head_in = chunk * Gc + r;
+        if (r >= Gc || head_in >= G) continue;
         const int head = kvh * G + head_in;
         if (single) {
-            out[((size_t)b * Hq + head) * HD + d] = __float2bfloat16_rn(acc / L);
+            const float inv = 1.f / l[h];
+            bf16* dst = out + ((size_t)b * Hq + head) * HD;
+#pragma unroll
+            for (int d = 0; d < HD / 8; ++d)
+                *reinterpret_cast<uint32_t*>(dst + 8 * d + 2 * t) = pack_bf16(o[d][2 * h] * inv, o[d][2 * h + 1] * inv);
         } else {
             const size_t at = ((size_t)b * Hq + head) * max_runs + run;
-            part_acc[at * HD + d] = acc;
-            if (d == 0) { part_m[at] = M * scale; part_l[at] = L; }   // the combine kernel works with scaled scores
+            float* dst = part_acc + at * HD;
+#pragma unroll
+            for (int d = 0; d < HD / 8; ++d)
+                *reinterpret_cast<float2*>(dst + 8 * d + 2 * t) = make_float2(o[d][2 * h], o[d][2 * h + 1]);
+            if (t == 0) { part_m[at] = m[h] * scale; part_l[at] = l[h]; }   // the combine kernel works with scaled scores
         }
     }
 }
 
 // out = sum_r acc_r e^(m_r - M) / sum_r l_r e^(m_r - M) over the runs, in index order (as in attention.cu).
-__global__ void attn_mma_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_m,
-                                        const float* __restrict__ part_l, const int* __restrict__ seq_len,
-                                        bf16* __restrict__ out, int Hq, int hd, int window, int split_tokens, int max_runs) {
+// One block per (head, sequence); the runs' weights e^(m_r - M) are formed once, in shared memory.
+#define AM_COMBINE_THREADS 128
+__global__ void __launch_bounds__(AM_COMBINE_THREADS)
+attn_mma_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_m,
+                        const float* __restrict__ part_l, const int* __restrict__ seq_len, bf16* __restrict__ out, int Hq,
+                        int hd, int window, int runs_target, int run_pages_max, int max_runs) {
     pdl_wait();
     pdl_launch_dependents();
+    extern __shared__ float weight[];                     // [max_runs]
+    __shared__ float red[AM_COMBINE_THREADS / 32];
     const int h = blockIdx.x, b = blockIdx.y;
     const int len = seq_len[b];
+    const int split_tokens = run_pages_for(len, runs_target, run_pages_max) * AM_TILE;
     const int k_lo = window > 0 ? max(0, len - window) : 0;
-    const int run_first = k_lo / split_tokens, run_end = (len + split_tokens - 1) / split_tokens;
-    if (run_end - run_first <= 1) return;
+    const int run_first = k_lo / split_tokens, run_end = min(max_runs, (len + split_tokens - 1) / split_tokens);
+    if (run_end - run_first <= 1) return;                 // a single run wrote the output itself
     const size_t row = ((size_t)b * Hq + h) * max_runs;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float M = -INFINITY;
-    for (int r = run_first; r < run_end; ++r) M = fmaxf(M, part_m[row + r]);
-    float L = 0.f;
-    for (int r = run_first; r < run_end; ++r) L += part_l[row + r] * expf(part_m[row + r] - M);
+    for (int r = run_first + threadIdx.x; r < run_end; r += blockDim.x) M = fmaxf(M, part_m[row + r]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+    if (lane == 0) red[warp] = M;
+    __syncthreads();
+    M = red[0];
+#pragma unroll
+    for (int w = 1; w < AM_COMBINE_THREADS / 32; ++w) M = fmaxf(M, red[w]);
+    for (int r = run_first + threadIdx.x; r < run_end; r += blockDim.x) weight[r - run_first] = expf(part_m[row + r] - M);
+    __syncthreads();
+    float L = 0.f;                                        // every thread the same sum, in run order
+    for (int r = run_first; r < run_end; ++r) L += part_l[row + r] * weight[r - run_first];
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
         float a = 0.f;
-        for (int r = run_first; r < run_end; ++r) a += part_acc[(row + r) * hd + d] * expf(part_m[row + r] - M);
+        for (int r = run_first; r < run_end; ++r) a += part_acc[(row + r) * hd + d] * weight[r - run_first];
         out[((size_t)b * Hq + h) * hd + d] = __float2bfloat16_rn(a / L);
     }
 }
@@ -439,53 +435,52 @@ extern "C" int qwb_attn_mma_prefill(const void* q, const void* k_pool, const voi
     return launch_prefill<128>(q, k_pool, v_pool, page_table, cu_seqlens, pos0, out, B, max_new, Hq, Hkv, table_width, scale, window, stream);
 }
 
-template <int HD, int WARPS>
+template <int HD>
 static int launch_decode(const void* q, const void* k_pool, const void* v_pool, const int* page_table, const int* seq_len,
                          float* scratch, void* out, int B, int Hq, int Hkv, int table_width, float scale, int window,
-                         int split_tokens, int max_runs, cudaStream_t stream) {
+                         int runs_target, int run_pages_max, int max_runs, cudaStream_t stream) {
     const int G = Hq / Hkv, Gc = group_chunk(G), chunks = (G + Gc - 1) / Gc;
-    size_t smem = (size_t)WARPS * 2 * AM_TILE * HD * sizeof(bf16);
-    const size_t merge = (size_t)WARPS * 16 * (HD + 2) * sizeof(float);
-    if (merge > smem) smem = merge;
-    cudaError_t e = cudaFuncSetAttribute(attn_mma_decode_kernel<HD, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const size_t smem = (size_t)2 * AM_TILE * HD * sizeof(bf16);
+    cudaError_t e = cudaFuncSetAttribute(attn_mma_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "attn_mma_decode: %s", cudaGetErrorString(e));
     float* part_acc = scratch;
     float* part_m = scratch + (size_t)B * Hq * max_runs * HD;
     float* part_l = part_m + (size_t)B * Hq * max_runs;
     dim3 grid(max_runs, Hkv * chunks, B);
-    qwb_launch(attn_mma_decode_kernel<HD, WARPS>, grid, WARPS * 32, smem, stream, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
-        page_table, seq_len, part_acc, part_m, part_l, (bf16*)out, Hq, Hkv, table_width, scale, window, split_tokens, max_runs,
-        Gc, chunks);
+    qwb_launch(attn_mma_decode_kernel<HD>, grid, 32, smem, stream, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
+        page_table, seq_len, part_acc, part_m, part_l, (bf16*)out, Hq, Hkv, table_width, scale, window, runs_target, run_pages_max,
+        max_runs, Gc, chunks);
     if (int rc = qwb_check_launch("attn_mma_decode")) return rc;
     if (max_runs > 1) {
-        qwb_launch(attn_mma_combine_kernel, dim3(Hq, B), 128, 0, stream, part_acc, part_m, part_l, seq_len, (bf16*)out, Hq, HD, window,
-                                                                 split_tokens, max_runs);
+        qwb_launch(attn_mma_combine_kernel, dim3(Hq, B), AM_COMBINE_THREADS, (size_t)max_runs * sizeof(float), stream, part_acc, part_m,
+                   part_l, seq_len, (bf16*)out, Hq, HD, window, runs_target, run_pages_max, max_runs);
         return qwb_check_launch("attn_mma_combine");
     }
     return 0;
 }
 
-template <int HD>
-static int launch_decode_warps(const void* q, const void* k_pool, const void* v_pool, const int* page_table, const int* seq_len,
-                               float* scratch, void* out, int B, int Hq, int Hkv, int table_width, float scale, int window,
-                               int split_tokens, int max_runs, cudaStream_t stream) {
-    const int pages = split_tokens / AM_TILE;
-#define AM_ARGS q, k_pool, v_pool, page_table, seq_len, scratch, out, B, Hq, Hkv, table_width, scale, window, split_tokens, max_runs, stream
-    if (pages <= 1) return launch_decode<HD, 1>(AM_ARGS);
-    if (pages == 2) return launch_decode<HD, 2>(AM_ARGS);
-    return launch_decode<HD, 4>(AM_ARGS);
-#undef AM_ARGS
+// The most runs that a sequence of up to max_len keys is cut into under (runs_target, run_pages_max): the host sizes the
+// scratch with it, B * Hq * runs * (hd + 2) floats.
+extern "C" int qwb_attn_mma_decode_runs(int max_len, int runs_target, int run_pages_max) {
+    if (max_len <= 0 || runs_target <= 0 || run_pages_max <= 0) return 0;
+    return max_runs_for(max_len, runs_target, run_pages_max);
 }
 
-// bfloat16 only.  Arguments as qwb_attn_decode (scratch of the same size).
+// bfloat16 only.  Arguments as qwb_attn_decode, but for how the keys are cut into runs: a sequence of p pages is cut into
+// runs of clamp(ceil(p / runs_target), 1, run_pages_max) pages (runs_target 1 gives runs of exactly run_pages_max pages);
+// max_len bounds every entry of seq_len.  scratch: B * Hq * runs(max_len) * (hd + 2) floats, unused with a single run.
 extern "C" int qwb_attn_mma_decode(const void* q, const void* k_pool, const void* v_pool, const int* page_table,
                                    const int* seq_len, float* scratch, void* out, int B, int Hq, int Hkv, int hd, int page_size,
-                                   int table_width, float scale, int window, int split_tokens, int max_runs, cudaStream_t stream) {
+                                   int table_width, float scale, int window, int runs_target, int run_pages_max, int max_len,
+                                   cudaStream_t stream) {
     if (B <= 0) return 0;
     if (int rc = check_sizes("attn_mma_decode", Hq, Hkv, hd, page_size, B)) return rc;
-    if (split_tokens <= 0 || split_tokens % AM_TILE || max_runs <= 0)
-        return qwb_fail(QWB_ERR_ARG, "attn_mma_decode: run of %d keys is not a multiple of %d, or %d runs", split_tokens, AM_TILE, max_runs);
+    if (runs_target <= 0 || run_pages_max <= 0 || max_len <= 0)
+        return qwb_fail(QWB_ERR_ARG, "attn_mma_decode: %d runs of up to %d pages for up to %d keys", runs_target, run_pages_max, max_len);
+    const int max_runs = max_runs_for(max_len, runs_target, run_pages_max);
+    if (max_runs > 65535) return qwb_fail(QWB_ERR_ARG, "attn_mma_decode: %d runs of keys; at most 65535", max_runs);
+    if ((size_t)max_runs * sizeof(float) > 40 * 1024) return qwb_fail(QWB_ERR_ARG, "attn_mma_decode: %d runs of keys are too many to combine", max_runs);
     if (max_runs > 1 && !scratch) return qwb_fail(QWB_ERR_ARG, "attn_mma_decode: %d runs need scratch memory", max_runs);
-    if (hd == 64) return launch_decode_warps<64>(q, k_pool, v_pool, page_table, seq_len, scratch, out, B, Hq, Hkv, table_width, scale, window, split_tokens, max_runs, stream);
-    return launch_decode_warps<128>(q, k_pool, v_pool, page_table, seq_len, scratch, out, B, Hq, Hkv, table_width, scale, window, split_tokens, max_runs, stream);
+    if (hd == 64) return launch_decode<64>(q, k_pool, v_pool, page_table, seq_len, scratch, out, B, Hq, Hkv, table_width, scale, window, runs_target, run_pages_max, max_runs, stream);
+    return launch_decode<128>(q, k_pool, v_pool, page_table, seq_len, scratch, out, B, Hq, Hkv, table_width, scale, window, runs_target, run_pages_max, max_runs, stream);
 }

@@ -75,7 +75,7 @@ def bench_gemm(M: int, N: int, K: int, impl: str, iters: int, dtype=torch.bfloat
             "GBps": nbytes / us / 1e3, "TFLOPs": 2.0 * M * N * K / us / 1e6}
 
 
-def bench_attn_decode(B, ctx, Hq, Hkv, hd, iters, dtype=torch.bfloat16, split=64) -> dict:
+def bench_attn_decode(B, ctx, Hq, Hkv, hd, iters, dtype=torch.bfloat16, split=0) -> dict:
     page = ops.PAGE_SIZE
     pages_per = math.ceil(ctx / page)
     per_copy = B * pages_per
@@ -89,7 +89,11 @@ def bench_attn_decode(B, ctx, Hq, Hkv, hd, iters, dtype=torch.bfloat16, split=64
               for c in range(copies)]
     q = torch.randn(B, Hq, hd, device="cuda").to(dtype)
     seq_len = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
-    fn = lambda i: ops.attn_decode(q, k_pool, v_pool, tables[i], seq_len, 1 / math.sqrt(hd), ctx, split_tokens=split)
+    if split:       # runs of exactly this many keys instead of the kernels' own choice
+        how = dict(split_tokens=split, runs_target=1, run_pages_max=max(1, split // page))
+    else:
+        how = {}
+    fn = lambda i: ops.attn_decode(q, k_pool, v_pool, tables[i], seq_len, 1 / math.sqrt(hd), ctx, **how)
     us = _time(fn, copies, iters)
     nbytes = 2 * B * ctx * Hkv * hd * elem
     return {"kernel": "attn_decode", "B": B, "ctx": ctx, "Hq": Hq, "Hkv": Hkv, "hd": hd, "us": us, "bytes": nbytes,
@@ -138,7 +142,7 @@ def main() -> int:
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--tile-n", type=int, default=None)
-    ap.add_argument("--split", type=int, default=64, help="keys per run of the decode attention kernel")
+    ap.add_argument("--split", type=int, default=0, help="keys per run of the decode attention kernel (0: its own choice)")
     args = ap.parse_args()
     dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
     if args.what == "gemm":

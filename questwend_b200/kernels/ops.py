@@ -242,30 +242,48 @@ def attn_decode_scratch_floats(B: int, Hq: int, hd: int, max_runs: int) -> int:
     return B * Hq * max_runs * (hd + 2)
 
 
+MMA_RUNS_TARGET = 16        # the tensor-core decode kernel cuts a sequence into about this many runs of keys ...
+MMA_RUN_PAGES_MAX = 8       # ... of at most this many pages each (more runs beyond that)
+
+
+def mma_decode_runs(max_len: int, runs_target: int = MMA_RUNS_TARGET, run_pages_max: int = MMA_RUN_PAGES_MAX) -> int:
+    """The most runs that the tensor-core decode kernel cuts a sequence of up to ``max_len`` keys into."""
+    return int(load_module("attention_mma").qwb_attn_mma_decode_runs(_i(max_len), _i(runs_target), _i(run_pages_max)))
+
+
 def attn_decode(q, k_pool, v_pool, page_table, seq_len, scale: float, max_len: int, window: int = 0,
-                split_tokens: int = 256, scratch: torch.Tensor | None = None, impl: str = "auto") -> torch.Tensor:
+                split_tokens: int = 256, scratch: torch.Tensor | None = None, impl: str = "auto",
+                runs_target: int = MMA_RUNS_TARGET, run_pages_max: int = MMA_RUN_PAGES_MAX) -> torch.Tensor:
     """Attention of one new token per sequence over the cache.  q [B, Hq, hd]; ``seq_len`` counts
-    the new token; ``max_len`` bounds every entry of ``seq_len``.  Returns [B, Hq * hd]."""
+    the new token; ``max_len`` bounds every entry of ``seq_len``.  Returns [B, Hq * hd].
+
+    The keys are cut into runs whose partial results are merged.  The plain kernel cuts into runs of
+    ``split_tokens`` keys.  The tensor-core kernel cuts a sequence of p pages into runs of
+    clamp(ceil(p / runs_target), 1, run_pages_max) pages (``runs_target`` 1: runs of exactly ``run_pages_max``
+    pages): by the sequence's own length, never by what else is in the batch."""
     _need(q, "q", k_pool.dtype, 3)
     _need(k_pool, "k_pool", ndim=4)
     _need(v_pool, "v_pool", k_pool.dtype, 4)
     _need(page_table, "page_table", torch.int32, 2)
     _need(seq_len, "seq_len", torch.int32, 1)
     B, Hq, hd = q.shape
-    max_runs = max(1, math.ceil(max_len / split_tokens))
+    use_mma = impl == "mma" or (impl == "auto" and mma_attention_fits(q.dtype, hd, k_pool.shape[2]))
+    if use_mma and q.dtype != torch.bfloat16:
+        raise KernelError("attn_decode: the tensor-core kernel takes bfloat16 only")
+    if use_mma:
+        max_runs = max(1, mma_decode_runs(max_len, runs_target, run_pages_max))
+    else:
+        max_runs = max(1, math.ceil(max_len / split_tokens))
     need = attn_decode_scratch_floats(B, Hq, hd, max_runs) if max_runs > 1 else 0
     if need and (scratch is None or scratch.numel() < need):
         scratch = torch.empty(need, dtype=torch.float32, device=q.device)
     if scratch is not None:
         _need(scratch, "scratch", torch.float32)
     out = torch.empty((B, Hq * hd), dtype=q.dtype, device=q.device)
-    use_mma = impl == "mma" or (impl == "auto" and mma_attention_fits(q.dtype, hd, k_pool.shape[2]))
     if use_mma:
-        if q.dtype != torch.bfloat16:
-            raise KernelError("attn_decode: the tensor-core kernel takes bfloat16 only")
         _call("attention_mma", "qwb_attn_mma_decode", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table),
               _ptr(seq_len), _ptr(scratch), _ptr(out), _i(B), _i(Hq), _i(k_pool.shape[1]), _i(hd), _i(k_pool.shape[2]),
-              _i(page_table.shape[1]), _f(scale), _i(window), _i(split_tokens), _i(max_runs), _stream(),
+              _i(page_table.shape[1]), _f(scale), _i(window), _i(runs_target), _i(run_pages_max), _i(max_len), _stream(),
               kernels=2 if max_runs > 1 else 1)
         return out
     _call("attention", "qwb_attn_decode", _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _ptr(seq_len),

@@ -15,7 +15,7 @@ from .linear import kernel_modules as linear_modules, linear
 from .registry import register_mixer
 
 DECODE_SPLIT_TOKENS = 256     # keys per run of the plain decode kernel; fixed, so results do not depend on the batch
-DECODE_SPLIT_TOKENS_MMA = 64  # the same for the tensor-core kernel: one page, one warp, one block
+                              # (the tensor-core kernel cuts by each sequence's own length: ops.attn_decode)
 
 
 class GroupedQueryAttention(Mixer):
@@ -89,10 +89,8 @@ class GroupedQueryAttention(Mixer):
                                    cache.k_pool, cache.v_pool, self.n_heads, self.n_kv_heads, self.head_dim,
                                    self.rotary_dim, self.eps, store_kv=cache.writable)
         if ctx.single_token:
-            mma = ops.mma_attention_fits(q.dtype, self.head_dim, cache.k_pool.shape[2])
             att = ops.attn_decode(q, cache.k_pool, cache.v_pool, table, ctx.seq_len, self.scale, ctx.max_len,
-                                  window=self.window,
-                                  split_tokens=DECODE_SPLIT_TOKENS_MMA if mma else DECODE_SPLIT_TOKENS)
+                                  window=self.window, split_tokens=DECODE_SPLIT_TOKENS)
         else:
             att = ops.attn_prefill(q, cache.k_pool, cache.v_pool, table, ctx.cu_seqlens, ctx.pos0, ctx.max_new,
                                    self.scale, window=self.window)

@@ -232,12 +232,28 @@ def test_attn_decode(dtype, Hq, Hkv, hd, window, split, page):
 
 
 @pytest.mark.parametrize("Hq,Hkv,hd", [(8, 2, 64), (8, 1, 128), (4, 4, 128), (12, 1, 64), (32, 1, 128), (6, 2, 128)])
-@pytest.mark.parametrize("window,split", [(0, 128), (100, 64), (0, 64), (0, 256), (0, 512), (300, 256)])
-def test_attn_decode_tensor_cores(Hq, Hkv, hd, window, split):
-    _attn_decode_case(torch.bfloat16, Hq, Hkv, hd, window, split, 64, "mma")
+@pytest.mark.parametrize("window,runs_target,run_pages_max", [
+    (0, 1, 2), (100, 1, 1), (0, 1, 1), (0, 1, 4), (0, 1, 8), (300, 1, 4),      # runs of a fixed number of pages
+    (0, 16, 8), (0, 4, 2), (100, 3, 8), (0, 2, 1), (0, 5, 3)])                  # by the sequence's length
+def test_attn_decode_tensor_cores(Hq, Hkv, hd, window, runs_target, run_pages_max):
+    _attn_decode_case(torch.bfloat16, Hq, Hkv, hd, window, 64 * run_pages_max, 64, "mma",
+                      dict(runs_target=runs_target, run_pages_max=run_pages_max))
 
 
-def _attn_decode_case(dtype, Hq, Hkv, hd, window, split, page, impl):
+def test_attn_decode_runs_by_length():
+    """How the tensor-core kernel cuts a sequence of p pages: clamp(ceil(p / target), 1, most) pages a run."""
+    def runs(pages, target, most):
+        per = min(most, max(1, -(-pages // target)))
+        return -(-pages // per)
+    for target, most in ((16, 8), (1, 4), (3, 2), (5, 1)):
+        for max_pages in (1, 2, 15, 16, 17, 31, 33, 128, 129, 1000):
+            want = max(runs(p, target, most) for p in range(1, max_pages + 1))
+            assert ops.mma_decode_runs(64 * max_pages, target, most) == want
+            assert ops.mma_decode_runs(64 * max_pages - 63, target, most) == want
+
+
+def _attn_decode_case(dtype, Hq, Hkv, hd, window, split, page, impl, how=None):
+    how = dict(split_tokens=split) if how is None else how
     if page == 128 and hd == 256 and dtype == torch.float32:
         pytest.skip("refused: see test_attention_refusals")
     lens = [1, 64, 65, 300, 129, 700]
@@ -247,17 +263,17 @@ def _attn_decode_case(dtype, Hq, Hkv, hd, window, split, page, impl):
     q_last = torch.stack([torch.as_tensor(qq[-1]) for qq in q]).to(dtype).to(DEV)
     seq_len = torch.tensor(lens, dtype=torch.int32, device=DEV)
     out = ops.attn_decode(q_last, k_pool, v_pool, table, seq_len, 1 / math.sqrt(hd), max(lens), window=window,
-                          split_tokens=split, impl=impl)
+                          impl=impl, **how)
     ref = np.stack([pm.attention_causal(qq, kk, vv, window=window or None)[-1].reshape(Hq * hd)
                     for qq, kk, vv in zip(q, k, v)])
     close(out, ref, dtype)
     # more runs than the longest sequence needs (a graph's bucket) change nothing
     again = ops.attn_decode(q_last, k_pool, v_pool, table, seq_len, 1 / math.sqrt(hd), max(lens) + 3 * split,
-                            window=window, split_tokens=split, impl=impl)
+                            window=window, impl=impl, **how)
     assert torch.equal(out, again)
     # a sequence's result does not depend on the rest of the batch
     alone = ops.attn_decode(q_last[3:4], k_pool, v_pool, table[3:4], seq_len[3:4], 1 / math.sqrt(hd), lens[3],
-                            window=window, split_tokens=split, impl=impl)
+                            window=window, impl=impl, **how)
     assert torch.equal(alone[0], out[3])
 
 

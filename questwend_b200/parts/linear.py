@@ -1,15 +1,19 @@
 """Matrix products y = x W^T with 32-bit sums and a 32-bit result.
 
 Few rows (a decode step) go to the hand-written weight-streaming kernels: bfloat16
-with up to 16 rows to the tensor-core one (mma.sync), float32 (and odd inner sizes)
-with up to 16 rows to the plain one.  More bfloat16 rows go to the tcgen05 kernel
-(TMA-fed, accumulators in tensor memory), which also folds the residual sum or the
-gated SiLU into its epilogue.  What is left (float32 with many rows, inner sizes
-that are no multiple of 8) goes to the library product, as in the reference, whose
-dispatcher sends up to 16 rows to its own kernels and the rest to cuBLAS
-(ggml-cuda/ggml-cuda.cu:1812-1866).  In the 32-bit engine the library product
-runs in plain float32: the reduced-precision (TF32) mode is switched off and
-checked at every call.
+with up to 16 rows to the tensor-core one (mma.sync), which also folds the residual
+sum or the gated SiLU into its epilogue; float32 (and odd inner sizes) with up to 16
+rows to the plain one.  More rows go to the library product, as in the reference,
+whose dispatcher sends up to 16 rows to its own kernels and the rest to cuBLAS
+(ggml-cuda/ggml-cuda.cu:1812-1866); the residual sum rides in the library call
+(beta = 1).  The exception is the gate/up projection of many bfloat16 rows: the
+tcgen05 kernel (TMA-fed, accumulators in tensor memory) with the gated SiLU in its
+epilogue beats the library product followed by a separate kernel.  That kernel's
+plain and residual-add epilogues are measured against the library in the
+microbenchmark and lose to it (by 4-11 % at 2,048 rows, by 2x at 256 rows, where
+it has too few tiles for 148 SMs), so the engine does not use them.
+In the 32-bit engine the library product runs in plain float32: the
+reduced-precision (TF32) mode is switched off and checked at every call.
 """
 from __future__ import annotations
 
@@ -29,12 +33,13 @@ def require_true_fp32() -> None:
     torch.set_float32_matmul_precision("highest")
 
 
-TC_MIN_ROWS = 129       # the tcgen05 kernel's tiles have 128 rows; below that the library's split-K products are faster
+TC_SWIGLU_MIN_ROWS = 512    # from here on the tcgen05 gate/up product with the SiLU in its epilogue beats library + kernel
 
 
-def _tc_fits(x: torch.Tensor, weight: torch.Tensor, n_out: int | None = None) -> bool:
-    n_out = weight.shape[0] if n_out is None else n_out
-    return (weight.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and n_out % 8 == 0 and x.shape[0] >= TC_MIN_ROWS)
+def _check_true_fp32() -> None:
+    if torch.backends.cuda.matmul.allow_tf32 or torch.get_float32_matmul_precision() != "highest":
+        raise RuntimeError("the 32-bit engine needs plain float32 matrix products; a reduced-precision "
+                           "mode was switched on after the engine was made")
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, add_to: torch.Tensor | None = None) -> torch.Tensor:
@@ -45,17 +50,13 @@ def linear(x: torch.Tensor, weight: torch.Tensor, add_to: torch.Tensor | None = 
         return ops.gemm_stream(x, weight, residual=add_to)
     if M <= ops.SMALL_M:
         return ops.gemm_small(x, weight, residual=add_to)
-    if _tc_fits(x, weight):
-        if add_to is not None:
-            return ops.gemm_tc(x, weight, epilogue="add", out=add_to, tile_n=256)
-        return ops.gemm_tc(x, weight, tile_n=256)
-    if add_to is not None:
-        return ops.add_inplace(add_to, linear(x, weight))
     if weight.dtype == torch.bfloat16:
+        if add_to is not None:
+            return torch.addmm(add_to, x, weight.t(), out_dtype=torch.float32, out=add_to)
         return torch.mm(x, weight.t(), out_dtype=torch.float32)
-    if torch.backends.cuda.matmul.allow_tf32 or torch.get_float32_matmul_precision() != "highest":
-        raise RuntimeError("the 32-bit engine needs plain float32 matrix products; a reduced-precision "
-                           "mode was switched on after the engine was made")
+    _check_true_fp32()
+    if add_to is not None:
+        return torch.addmm(add_to, x, weight.t(), out=add_to)
     return torch.mm(x, weight.t())
 
 
@@ -66,6 +67,6 @@ def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor, out_dtype: torc
     if interleave == ops.GATE_UP_GROUP and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16:
         if x.shape[0] <= ops.STREAM_M and x.shape[1] % 8 == 0:
             return ops.gemm_stream_swiglu(x, weight_gate_up)
-        if _tc_fits(x, weight_gate_up, weight_gate_up.shape[0] // 2):
+        if x.shape[0] >= TC_SWIGLU_MIN_ROWS and x.shape[1] % 8 == 0:
             return ops.gemm_tc(x, weight_gate_up, epilogue="swiglu", tile_n=256)
     return ops.silu_mul(linear(x, weight_gate_up), out_dtype, interleave)

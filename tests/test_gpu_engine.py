@@ -68,6 +68,28 @@ def test_first_tokens_of_a_sequence(folders, name, dtype):
             assert rel_err(row, refs[i][j]) < tol(dtype)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_long_prompts_in_one_step(folders, name, dtype):
+    """A step of 690 rows (prompts of 640 and 50 tokens): enough rows for the kernels that only prefill of many
+    tokens reaches (the tcgen05 gate/up product and attention), then a second step that continues from the cache."""
+    folder = folders[name, dtype]
+    cfg, w = pm.read_model_folder(folder)
+    eng = qw.Engine.from_folder(folder, dtype=dtype, max_tokens=1024)
+    rng = np.random.default_rng(11)
+    seqs = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (660, 50)]
+    refs = [pm.forward_logits(cfg, w, t, round16=None if dtype == "float32" else "bf16") for t in seqs]
+    slots = eng.open_sequences(2)
+    heads = [640, 50]
+    want = [[0, 1, 63, 64, 65, 300, 511, 512, 638, 639], list(range(50))]
+    first = eng.step([StepEntry(s, t[:h], wt) for s, t, h, wt in zip(slots, seqs, heads, want)]).cpu().numpy()
+    assert rel_err(first[:10], refs[0][want[0]]) < tol(dtype)
+    assert rel_err(first[10:], refs[1]) < tol(dtype)
+    more = eng.step([StepEntry(slots[0], seqs[0][640:], list(range(20)))]).cpu().numpy()    # 20 more tokens of the first
+    assert rel_err(more, refs[0][640:]) < tol(dtype)
+    eng.close_sequences(slots)
+
+
 @pytest.mark.parametrize("use_graph", [True, False])
 def test_greedy_generation_matches_the_plain_implementation(folders, use_graph):
     folder = folders["B", "float32"]

@@ -120,7 +120,7 @@ struct AtSmem {
     static constexpr size_t Q_BYTES = (size_t)AT_ROWS * HD * 2;            // ATOMS blocks of [128 rows][128 bytes]
     static constexpr size_t KV_BYTES = (size_t)AT_KEYS * HD * 2;           // ATOMS blocks of [64 keys][128 bytes]
     static constexpr size_t P_BYTES = (size_t)AT_ROWS * AT_KEYS * 2;       // [128 rows][128 bytes]
-    static constexpr size_t BYTES = 1024 + Q_BYTES + 2 * AT_KV_STAGES * KV_BYTES + P_BYTES + 256;
+    static constexpr size_t BYTES = Q_BYTES + 2 * AT_KV_STAGES * KV_BYTES + P_BYTES + 128;   // 128: barriers, tensor-memory slot
 };
 
 template <int HD>
@@ -132,9 +132,14 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     constexpr int ATOMS = AtSmem<HD>::ATOMS;
     constexpr uint32_t KV_BYTES = AtSmem<HD>::KV_BYTES;
     constexpr uint32_t TMEM_COLS = 256;                                     // S: 2 x 64 columns, O: HD columns
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned char* q_tile = base;
+    // The tiles need 1024-byte alignment (128-byte swizzle).  No padding to reach it: at head size 128 the block's
+    // 113 KB then leave room for a second block on the SM, whose products run while this block's softmax does.
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    if (at_smem(smem_raw) & 1023u) {                      // never seen; refuse rather than compute with a wrong layout
+        if (threadIdx.x == 0) atomicExch(error, 7);
+        return;
+    }
+    unsigned char* q_tile = smem_raw;
     unsigned char* k_tiles = q_tile + AtSmem<HD>::Q_BYTES;
     unsigned char* v_tiles = k_tiles + AT_KV_STAGES * KV_BYTES;
     unsigned char* p_tile = v_tiles + AT_KV_STAGES * KV_BYTES;

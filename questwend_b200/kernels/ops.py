@@ -371,7 +371,8 @@ def gemm_tc_check(device) -> None:
     if code:
         word.zero_()
         where = {1: "the loader waiting for a free stage", 2: "the tensor-core issuer waiting for its operands",
-                 3: "the epilogue or softmax warps waiting for the tensor core"}.get(code, f"code {code}")
+                 3: "the epilogue or softmax warps waiting for the tensor core",
+                 7: "shared memory was not aligned to 1024 bytes"}.get(code, f"code {code}")
         raise KernelError(f"a bounded wait in a tcgen05 kernel ran out ({where}); that kernel's result is not valid")
 
 

@@ -65,26 +65,28 @@ __device__ __forceinline__ void load_tile(bf16* tile, const bf16* src, int n_val
     }
 }
 
-// One warp, 16 rows, one tile of 64 keys: S = Q K^T, mask, online softmax, O += P V.
+// One warp, 16 rows, one tile of 64 keys: S = Q K^T, mask, online softmax, O += P V, in two halves so that a caller
+// can wait for K and for V separately and start the next tile's copies in between.
 //   qf     Q fragments of the warp's 16 rows: [HD/16][4]
 //   key0   position of the tile's first key; row_pos[2]: positions of rows g and g + 8 (-1: row unused)
 //   len    keys of the sequence; window (0: none)
 //   m, l   running maximum and (this thread's share of the) sum for rows g and g + 8;  o: [HD/8][4]
-template <int HD, bool SPLIT_WAIT>
-__device__ __forceinline__ void tile_step_impl(const uint32_t (*qf)[4], const bf16* Kt, const bf16* Vt, int key0, const int* row_pos,
-                                          int len, int window, float sl2, float* m, float* l, float (*o)[4], int lane) {
-    constexpr int KS = HD / 16, NT = AM_TILE / 8, DT = HD / 8;
+//   KEYS, key_off: the warp takes the KEYS keys (a multiple of 16) of the tile that start at key_off
+//   s, base: the masked scores and the rows' new maxima (scaled), handed from the first half to the second
+template <int HD, int KEYS>
+__device__ __forceinline__ void tile_scores(const uint32_t (*qf)[4], const bf16* Kt, int key0, const int* row_pos, int len,
+                                            int window, float sl2, float* m, float* l, float (*o)[4], int lane, int key_off,
+                                            float (*s)[4], float* base) {
+    constexpr int KS = HD / 16, NT = KEYS / 8, DT = HD / 8;
     const int t = lane & 3;
-    float s[NT][4];
 #pragma unroll
     for (int j = 0; j < NT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
     const int mi = lane >> 3, mr = lane & 7;          // ldmatrix: which matrix this lane addresses, and its row
-    if (SPLIT_WAIT) { cp_async_wait<1>(); __syncwarp(); }     // K has landed; V may still be on its way
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks) {
 #pragma unroll
         for (int j = 0; j < NT; j += 2) {
-            const int key = 8 * (j + (mi >> 1)) + mr, chunk = 2 * ks + (mi & 1);
+            const int key = key_off + 8 * (j + (mi >> 1)) + mr, chunk = 2 * ks + (mi & 1);
             uint32_t b[4];
             ldmatrix_x4(b, Kt + key * HD + ((chunk ^ (key & 7)) << 3));
             mma_16816(s[j], qf[ks], b[0], b[1]);
@@ -97,14 +99,14 @@ __device__ __forceinline__ void tile_step_impl(const uint32_t (*qf)[4], const bf
     for (int j = 0; j < NT; ++j) {
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
-            const int key = key0 + 8 * j + 2 * t + (r & 1);
+            const int key = key0 + key_off + 8 * j + 2 * t + (r & 1);
             const int qp = row_pos[r >> 1];
             const bool ok = qp >= 0 && key <= qp && key < len && (window <= 0 || key > qp - window);
             s[j][r] = ok ? s[j][r] : -INFINITY;
             mx[r >> 1] = fmaxf(mx[r >> 1], s[j][r]);
         }
     }
-    float alpha[2], base[2];
+    float alpha[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
@@ -120,10 +122,16 @@ __device__ __forceinline__ void tile_step_impl(const uint32_t (*qf)[4], const bf
         o[d][0] *= alpha[0]; o[d][1] *= alpha[0];
         o[d][2] *= alpha[1]; o[d][3] *= alpha[1];
     }
-    if (SPLIT_WAIT) { cp_async_wait<0>(); __syncwarp(); }     // V has landed
-    // probabilities, then O += P V
+}
+
+// probabilities, then O += P V
+template <int HD, int KEYS>
+__device__ __forceinline__ void tile_pv(const bf16* Vt, const float (*s)[4], const float* base, float sl2, float* l,
+                                        float (*o)[4], int lane, int key_off) {
+    constexpr int DT = HD / 8;
+    const int mi = lane >> 3, mr = lane & 7;
 #pragma unroll
-    for (int kk = 0; kk < AM_TILE / 16; ++kk) {
+    for (int kk = 0; kk < KEYS / 16; ++kk) {
         uint32_t pf[4];
         float p[2][4];
 #pragma unroll
@@ -139,7 +147,7 @@ __device__ __forceinline__ void tile_step_impl(const uint32_t (*qf)[4], const bf
         pf[3] = pack_bf16(p[1][2], p[1][3]);
 #pragma unroll
         for (int jd = 0; jd < DT; jd += 2) {
-            const int key = 16 * kk + 8 * (mi & 1) + mr, chunk = jd + (mi >> 1);
+            const int key = key_off + 16 * kk + 8 * (mi & 1) + mr, chunk = jd + (mi >> 1);
             uint32_t b[4];
             ldmatrix_x4_trans(b, Vt + key * HD + ((chunk ^ (key & 7)) << 3));
             mma_16816(o[jd], pf, b[0], b[1]);
@@ -148,16 +156,13 @@ __device__ __forceinline__ void tile_step_impl(const uint32_t (*qf)[4], const bf
     }
 }
 
+// Both halves in a row, for a caller whose K and V tiles are both in shared memory already.
 template <int HD>
 __device__ __forceinline__ void tile_step(const uint32_t (*qf)[4], const bf16* Kt, const bf16* Vt, int key0, const int* row_pos,
                                           int len, int window, float sl2, float* m, float* l, float (*o)[4], int lane) {
-    tile_step_impl<HD, false>(qf, Kt, Vt, key0, row_pos, len, window, sl2, m, l, o, lane);
-}
-// The same for a warp that issued the tile's K and V copies itself, as two cp.async groups: it waits for each where it is needed.
-template <int HD>
-__device__ __forceinline__ void tile_step_split(const uint32_t (*qf)[4], const bf16* Kt, const bf16* Vt, int key0, const int* row_pos,
-                                                int len, int window, float sl2, float* m, float* l, float (*o)[4], int lane) {
-    tile_step_impl<HD, true>(qf, Kt, Vt, key0, row_pos, len, window, sl2, m, l, o, lane);
+    float s[AM_TILE / 8][4], base[2];
+    tile_scores<HD, AM_TILE>(qf, Kt, key0, row_pos, len, window, sl2, m, l, o, lane, 0, s, base);
+    tile_pv<HD, AM_TILE>(Vt, s, base, sl2, l, o, lane, 0);
 }
 
 // Q fragments of rows (g, g + 8) of a warp; q_lo / q_hi point at the rows' hd values (or null).
@@ -321,16 +326,48 @@ attn_mma_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
     const int tok_begin = run * split_tokens, tok_end = min(len, tok_begin + split_tokens);
     const int* pages = page_table + (size_t)b * table_width;
     const float sl2 = scale * 1.4426950408889634f;
-    for (int base = tok_begin; base < tok_end; base += AM_TILE) {
-        if (base + AM_TILE <= k_lo) continue;                                  // a page wholly before the window
-        const size_t src = ((size_t)pages[base / AM_TILE] * Hkv + kvh) * AM_TILE * HD;
-        const int n_valid = min(AM_TILE, len - base);
+    // The run's pages one after the other, through one K and one V buffer: as soon as the scores of a page are formed
+    // its K buffer takes the next page's K, and after O += P V its V buffer the next page's V, so that the copies of
+    // page i + 1 run under the arithmetic of page i.
+    bf16* k_tile = my_tiles;
+    bf16* v_tile = my_tiles + AM_TILE * HD;
+    int base_tok = max(tok_begin, (k_lo / AM_TILE) * AM_TILE);                 // pages wholly before the window are skipped
+    if (base_tok < tok_end) {
+        const size_t src = ((size_t)pages[base_tok / AM_TILE] * Hkv + kvh) * AM_TILE * HD;
+        const int n_valid = min(AM_TILE, len - base_tok);
+        load_tile<HD>(k_tile, k_pool + src, n_valid, lane, 32);
+        cp_async_commit();
+        load_tile<HD>(v_tile, v_pool + src, n_valid, lane, 32);
+        cp_async_commit();
+    }
+    for (; base_tok < tok_end; base_tok += AM_TILE) {
+        const int next_tok = base_tok + AM_TILE;
+        const bool more = next_tok < tok_end;
+        size_t src = 0;
+        int n_valid = 0;
+        if (more) {
+            src = ((size_t)pages[next_tok / AM_TILE] * Hkv + kvh) * AM_TILE * HD;
+            n_valid = min(AM_TILE, len - next_tok);
+        }
+        float s[AM_TILE / 8][4], sbase[2];
+        cp_async_wait<1>();                                                     // this page's K has landed (its V may not have)
         __syncwarp();
-        load_tile<HD>(my_tiles, k_pool + src, n_valid, lane, 32);
-        cp_async_commit();
-        load_tile<HD>(my_tiles + AM_TILE * HD, v_pool + src, n_valid, lane, 32);
-        cp_async_commit();
-        tile_step_split<HD>(qf, my_tiles, my_tiles + AM_TILE * HD, base, row_pos, len, window, sl2, m, l, o, lane);
+        tile_scores<HD, AM_TILE>(qf, k_tile, base_tok, row_pos, len, window, sl2, m, l, o, lane, 0, s, sbase);
+        __syncwarp();                                                           // every lane is done reading K
+        if (more) {
+            load_tile<HD>(k_tile, k_pool + src, n_valid, lane, 32);
+            cp_async_commit();
+            cp_async_wait<1>();                                                 // all but the copy just started: this page's V
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncwarp();
+        tile_pv<HD, AM_TILE>(v_tile, s, sbase, sl2, l, o, lane, 0);
+        __syncwarp();                                                           // every lane is done reading V
+        if (more) {
+            load_tile<HD>(v_tile, v_pool + src, n_valid, lane, 32);
+            cp_async_commit();
+        }
     }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {

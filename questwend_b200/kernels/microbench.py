@@ -75,7 +75,7 @@ def bench_gemm(M: int, N: int, K: int, impl: str, iters: int, dtype=torch.bfloat
             "GBps": nbytes / us / 1e3, "TFLOPs": 2.0 * M * N * K / us / 1e6}
 
 
-def bench_attn_decode(B, ctx, Hq, Hkv, hd, iters, dtype=torch.bfloat16, split=0) -> dict:
+def bench_attn_decode(B, ctx, Hq, Hkv, hd, iters, dtype=torch.bfloat16, split=0, runs_target=0, run_pages_max=0) -> dict:
     page = ops.PAGE_SIZE
     pages_per = math.ceil(ctx / page)
     per_copy = B * pages_per
@@ -93,6 +93,10 @@ def bench_attn_decode(B, ctx, Hq, Hkv, hd, iters, dtype=torch.bfloat16, split=0)
         how = dict(split_tokens=split, runs_target=1, run_pages_max=max(1, split // page))
     else:
         how = {}
+        if runs_target:
+            how["runs_target"] = runs_target
+        if run_pages_max:
+            how["run_pages_max"] = run_pages_max
     fn = lambda i: ops.attn_decode(q, k_pool, v_pool, tables[i], seq_len, 1 / math.sqrt(hd), ctx, **how)
     us = _time(fn, copies, iters)
     nbytes = 2 * B * ctx * Hkv * hd * elem
@@ -143,6 +147,8 @@ def main() -> int:
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--tile-n", type=int, default=None)
     ap.add_argument("--split", type=int, default=0, help="keys per run of the decode attention kernel (0: its own choice)")
+    ap.add_argument("--runs-target", type=int, default=0, help="tensor-core decode attention: about this many runs a sequence")
+    ap.add_argument("--run-pages-max", type=int, default=0, help="tensor-core decode attention: at most this many pages a run")
     args = ap.parse_args()
     dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
     if args.what == "gemm":
@@ -154,7 +160,8 @@ def main() -> int:
             r["name"] = name
             print(json.dumps(r))
     elif args.what == "attn_decode":
-        print(json.dumps(bench_attn_decode(args.batch, args.ctx, args.heads, args.kv_heads, args.head_dim, args.iters, dtype, args.split)))
+        print(json.dumps(bench_attn_decode(args.batch, args.ctx, args.heads, args.kv_heads, args.head_dim, args.iters, dtype, args.split,
+                                           args.runs_target, args.run_pages_max)))
     elif args.what == "attn_prefill":
         print(json.dumps(bench_attn_prefill(args.tokens, args.heads, args.kv_heads, args.head_dim, args.iters, dtype)))
     else:

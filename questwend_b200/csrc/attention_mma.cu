@@ -401,6 +401,7 @@ attn_mma_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
 // out = sum_r acc_r e^(m_r - M) / sum_r l_r e^(m_r - M) over the runs, in index order (as in attention.cu).
 // One block per (head, sequence); the runs' weights e^(m_r - M) are formed once, in shared memory.
 #define AM_COMBINE_THREADS 128
+#define AM_COMBINE_FAST 16         // up to this many runs are merged without shared memory
 __global__ void __launch_bounds__(AM_COMBINE_THREADS)
 attn_mma_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_m,
                         const float* __restrict__ part_l, const int* __restrict__ seq_len, bf16* __restrict__ out, int Hq,
@@ -416,6 +417,32 @@ attn_mma_combine_kernel(const float* __restrict__ part_acc, const float* __restr
     const int run_first = k_lo / split_tokens, run_end = min(max_runs, (len + split_tokens - 1) / split_tokens);
     if (run_end - run_first <= 1) return;                 // a single run wrote the output itself
     const size_t row = ((size_t)b * Hq + h) * max_runs;
+    const int n_runs = run_end - run_first;
+    if (n_runs <= AM_COMBINE_FAST && hd <= AM_COMBINE_THREADS) {
+        // Few runs (the usual case): every thread reads all maxima and sums itself and its own column of every partial
+        // result, all loads issued before the first use, so that the kernel costs one round trip to memory, not four.
+        const int d = threadIdx.x;
+        float mr[AM_COMBINE_FAST], lr[AM_COMBINE_FAST], ar[AM_COMBINE_FAST];
+#pragma unroll
+        for (int i = 0; i < AM_COMBINE_FAST; ++i) {
+            const bool in = i < n_runs;
+            mr[i] = in ? part_m[row + run_first + i] : -INFINITY;
+            lr[i] = in ? part_l[row + run_first + i] : 0.f;
+            ar[i] = in && d < hd ? part_acc[(row + run_first + i) * hd + d] : 0.f;
+        }
+        float M = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < AM_COMBINE_FAST; ++i) M = fmaxf(M, mr[i]);
+        float L = 0.f, a = 0.f;
+#pragma unroll
+        for (int i = 0; i < AM_COMBINE_FAST; ++i) {        // in run order, as the general path below
+            const float w = i < n_runs ? expf(mr[i] - M) : 0.f;
+            L += lr[i] * w;
+            a += ar[i] * w;
+        }
+        if (d < hd) out[((size_t)b * Hq + h) * hd + d] = __float2bfloat16_rn(a / L);
+        return;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float M = -INFINITY;
     for (int r = run_first + threadIdx.x; r < run_end; r += blockDim.x) M = fmaxf(M, part_m[row + r]);

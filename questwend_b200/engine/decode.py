@@ -56,6 +56,8 @@ class DecodeRunner:
         self.graphs: dict = {}
         self.slots: list = []
         self._pages_seen: list = []
+        self._room = 0              # steps that need no new page and no other graph (see step)
+        self._graph = None
         self.launches_per_step = 0
 
     # ------------------------------------------------------------------ binding a batch
@@ -80,6 +82,7 @@ class DecodeRunner:
         self.state.copy_(h, non_blocking=True)
         self.step_counter.fill_(step)
         self._pages_seen = [None] * cache.n_groups()
+        self._room = 0
         torch.cuda.current_stream().synchronize()      # the pinned buffer may be written again
 
     def set_tokens(self, tokens) -> None:
@@ -133,23 +136,32 @@ class DecodeRunner:
         """Run one decode step for the bound sequences; the sampled ids land in ``self.sampled``
         and become the next inputs."""
         cache = self.engine.cache
-        wants = {s: cache.length(s) + 1 for s in self.slots}
-        cache.reserve(wants)
-        for g in range(cache.n_groups()):
-            counts = [len(cache._groups[g].pages[s]) for s in self.slots]
-            if counts != self._pages_seen[g]:
-                self._pages_seen[g] = counts
-                self.tables[g].copy_(torch.from_numpy(cache.page_table_host(g, self.slots)))
-        bucket = math.ceil(max(wants.values()) / DECODE_SPLIT_TOKENS) * DECODE_SPLIT_TOKENS
+        if self._room <= 0:
+            # A sequence may need a page, or the longest one leaves the graph's bucket: look, and count the steps
+            # until either can happen again.  Nothing else changes between the steps of a bound batch.
+            lengths = [cache.length(s) for s in self.slots]
+            cache.reserve({s: n + 1 for s, n in zip(self.slots, lengths)})
+            room = cache.max_seq_len - max(lengths)          # reserve() refuses a longer sequence: let it look then
+            for g in range(cache.n_groups()):
+                counts = [len(cache._groups[g].pages[s]) for s in self.slots]
+                if counts != self._pages_seen[g]:
+                    self._pages_seen[g] = counts
+                    self.tables[g].copy_(torch.from_numpy(cache.page_table_host(g, self.slots)))
+                room = min(room, min(c * ops.PAGE_SIZE - n for c, n in zip(counts, lengths)))
+            self._bucket = math.ceil((max(lengths) + 1) / DECODE_SPLIT_TOKENS) * DECODE_SPLIT_TOKENS
+            self._room = min(room, self._bucket - max(lengths))
+            self._graph = None
+        self._room -= 1
         with torch.cuda.device(self.engine.device):
             if self.use_graph:
-                g = self.graphs.get(bucket)
-                if g is None:
-                    g = self.graphs[bucket] = self._capture(bucket)
-                g.replay()
+                if self._graph is None:
+                    self._graph = self.graphs.get(self._bucket)
+                    if self._graph is None:
+                        self._graph = self.graphs[self._bucket] = self._capture(self._bucket)
+                self._graph.replay()
             else:
                 before = ops.LAUNCHES[0]
-                self._forward_and_sample(bucket)
+                self._forward_and_sample(self._bucket)
                 self._advance()
                 self.launches_per_step = ops.LAUNCHES[0] - before
         for s in self.slots:

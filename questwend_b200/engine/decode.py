@@ -16,15 +16,23 @@ bucket of 32 (core/runtime.cpp:1768-1829), replayed as a CUDA graph inside ggml.
 from __future__ import annotations
 
 import gc
-import math
 
 import numpy as np
 import torch
 
 from ..kernels import ops
-from ..parts.attention import DECODE_SPLIT_TOKENS
 from ..parts.base import StepContext
 from ..sampling.params import SamplingParams
+
+
+MIN_BUCKET = 256
+
+
+def length_bucket(n_tokens: int) -> int:
+    """The bound on the sequences' length that a graph is captured for: the next power of two (at least 256).
+    The attention kernels size their grid and scratch by it and let the blocks beyond a sequence's keys return at once,
+    so a generous bound costs little, and a sequence that grows needs a new graph only when its length doubles."""
+    return max(MIN_BUCKET, 1 << max(0, n_tokens - 1).bit_length())
 
 
 class DecodeRunner:
@@ -54,6 +62,7 @@ class DecodeRunner:
         self.tokens_host = torch.zeros((B,), dtype=torch.int32).pin_memory()
         self.sampled_host = torch.zeros((B,), dtype=torch.int32).pin_memory()
         self.graphs: dict = {}
+        self._pool = None           # the graphs run one at a time: they share one pool of memory
         self.slots: list = []
         self._pages_seen: list = []
         self._room = 0              # steps that need no new page and no other graph (see step)
@@ -123,7 +132,9 @@ class DecodeRunner:
         gc.collect()
         gc.disable()
         try:
-            with torch.cuda.graph(g):
+            if self._pool is None:
+                self._pool = torch.cuda.graph_pool_handle()
+            with torch.cuda.graph(g, pool=self._pool):
                 self._forward_and_sample(bucket)
                 self._advance()
         finally:
@@ -148,7 +159,7 @@ class DecodeRunner:
                     self._pages_seen[g] = counts
                     self.tables[g].copy_(torch.from_numpy(cache.page_table_host(g, self.slots)))
                 room = min(room, min(c * ops.PAGE_SIZE - n for c, n in zip(counts, lengths)))
-            self._bucket = math.ceil((max(lengths) + 1) / DECODE_SPLIT_TOKENS) * DECODE_SPLIT_TOKENS
+            self._bucket = length_bucket(max(lengths) + 1)
             self._room = min(room, self._bucket - max(lengths))
             self._graph = None
         self._room -= 1

@@ -157,3 +157,10 @@ def test_sampling_params():
     assert SamplingParams(repeat_penalty=1.1).penalized and not SamplingParams(repeat_penalty=1.1, repeat_last_n=0).penalized
     with pytest.raises(ValueError):
         SamplingParams(repeat_penalty=0)
+
+
+def test_length_buckets_double():
+    """A decode graph is captured for a bound on the lengths; the bound doubles, so a growing sequence needs few graphs."""
+    from questwend_b200.engine.decode import length_bucket
+    assert [length_bucket(n) for n in (1, 255, 256, 257, 1024, 1025, 5000)] == [256, 256, 256, 512, 1024, 2048, 8192]
+    assert all(length_bucket(n) >= n for n in range(1, 3000, 7))

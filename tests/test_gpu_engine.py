@@ -121,6 +121,25 @@ def test_bfloat16_greedy_generation(folders, name):
     assert got == want
 
 
+@pytest.mark.parametrize("name,dtype", [("C", "bfloat16"), ("D", "bfloat16"), ("B", "float32")])
+def test_long_generation_from_graphs_matches_plain_steps(folders, name, dtype):
+    """300 new tokens for prompts of unequal lengths: every sequence crosses pages, runs of the decode kernels and the
+    graphs' length bounds (256, 512) at a different step.  The graph replays and the plain steps run the same kernels
+    on the same numbers, so the tokens are the same; the first ones are checked against the plain implementation."""
+    folder = folders[name, dtype]
+    cfg, w = pm.read_model_folder(folder)
+    rng = np.random.default_rng(21)
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (5, 200, 250, 64)]
+    eng = qw.Engine.from_folder(folder, dtype=dtype, max_tokens=4 * 640)
+    plain = qw.generate(eng, prompts, max_new_tokens=300, ignore_eos=True, use_graph=False)
+    graph = qw.generate(eng, prompts, max_new_tokens=300, ignore_eos=True, use_graph=True)
+    assert [r.tokens for r in graph] == [r.tokens for r in plain]
+    assert all(len(r.tokens) == 300 for r in graph)
+    first = pm.greedy_continue(cfg, w, prompts[0], 6, round16=None if dtype == "float32" else "bf16")
+    assert graph[0].tokens[:6] == first
+    assert eng.cache.free_pages() == [eng.cache.n_pages] * eng.cache.n_groups()
+
+
 def test_sampled_generation_is_a_function_of_the_seed(folders):
     folder = folders["A", "float32"]
     eng = qw.Engine.from_folder(folder, dtype="float32", max_tokens=1024, max_batch=3)

@@ -1,0 +1,53 @@
+"""One layer with the layer sizes of the largest model the library is measured on (width 4096, 32/8 heads of 128,
+feed-forward 12288) and a vocabulary that is no power of two: the kernels' tile loops, grids and strides run at the
+sizes they are tuned for, against the plain implementation (needs a B200; a 0.9 GB model folder in a temporary place)."""
+import numpy as np
+import pytest
+
+import plain_model as pm
+import questwend_b200 as qw
+from helpers import BF16_TOL, FP32_TOL, rel_err
+from questwend_b200.config import config_from_dict
+
+pytestmark = pytest.mark.gpu
+
+REAL = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": 1, "hidden_size": 4096,
+        "intermediate_size": 12288, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
+        "vocab_size": 32003, "rope_theta": 1e6, "rms_norm_eps": 1e-6, "tie_word_embeddings": False}
+
+
+@pytest.fixture(scope="module")
+def model(tmp_path_factory):
+    folder = str(tmp_path_factory.mktemp("real_sizes"))
+    qw.write_model_folder(folder, config_from_dict(REAL), seed=2, dtype="bfloat16")
+    cfg, w = pm.read_model_folder(folder)
+    return folder, cfg, w
+
+
+def run_cut(eng, toks, cuts):
+    (s,) = eng.open_sequences(1)
+    rows, pos = [], 0
+    for c in cuts:
+        rows.append(eng.step([qw.StepEntry(s, toks[pos:pos + c], list(range(c)))]).cpu().numpy())
+        pos += c
+    eng.close_sequences([s])
+    return np.concatenate(rows)
+
+
+def test_bfloat16_whole_and_cut(model):
+    folder, cfg, w = model
+    toks = np.random.default_rng(0).integers(0, REAL["vocab_size"], 700).tolist()
+    ref = pm.forward_logits(cfg, w, toks, round16="bf16")
+    eng = qw.Engine.from_folder(folder, dtype="bfloat16", max_tokens=2048)
+    # whole (the tcgen05 product and attention); a long prompt, a short one and single tokens; single tokens first
+    for cuts in ([700], [600, 60] + [1] * 40, [3] + [1] * 50 + [647]):
+        got = run_cut(eng, toks, cuts)
+        assert rel_err(got, ref) < BF16_TOL, cuts[:3]
+
+
+def test_float32_prompt_then_tokens(model):
+    folder, cfg, w = model
+    toks = np.random.default_rng(1).integers(0, REAL["vocab_size"], 200).tolist()
+    ref = pm.forward_logits(cfg, w, toks)
+    eng = qw.Engine.from_folder(folder, dtype="float32", max_tokens=1024)
+    assert rel_err(run_cut(eng, toks, [150] + [1] * 50), ref) < FP32_TOL

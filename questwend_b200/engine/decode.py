@@ -26,6 +26,7 @@ from ..sampling.params import SamplingParams
 
 
 MIN_BUCKET = 256
+GRAPH_AFTER = 2             # plain steps at a batch size and length bound before a graph is captured for them
 
 
 def length_bucket(n_tokens: int) -> int:
@@ -67,6 +68,7 @@ class DecodeRunner:
         self._pages_seen: list = []
         self._room = 0              # steps that need no new page and no other graph (see step)
         self._graph = None
+        self._plain_steps: dict = {}    # length bound -> plain steps run so far
         self.launches_per_step = 0
 
     # ------------------------------------------------------------------ binding a batch
@@ -164,17 +166,20 @@ class DecodeRunner:
             self._graph = None
         self._room -= 1
         with torch.cuda.device(self.engine.device):
-            if self.use_graph:
-                if self._graph is None:
-                    self._graph = self.graphs.get(self._bucket)
-                    if self._graph is None:
-                        self._graph = self.graphs[self._bucket] = self._capture(self._bucket)
+            if self.use_graph and self._graph is None:
+                self._graph = self.graphs.get(self._bucket)
+                if self._graph is None and self._plain_steps.get(self._bucket, 0) >= GRAPH_AFTER:
+                    # a capture costs about two steps: it pays only for a batch that stays (a batch whose sequences
+                    # end one after the other passes through many sizes for a step or two each)
+                    self._graph = self.graphs[self._bucket] = self._capture(self._bucket)
+            if self._graph is not None:
                 self._graph.replay()
             else:
                 before = ops.LAUNCHES[0]
                 self._forward_and_sample(self._bucket)
                 self._advance()
                 self.launches_per_step = ops.LAUNCHES[0] - before
+                self._plain_steps[self._bucket] = self._plain_steps.get(self._bucket, 0) + 1
         for s in self.slots:
             cache.advance(s, 1)
         self.engine.steps_run += 1

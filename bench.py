@@ -51,11 +51,13 @@ def load_peaks():
     try:
         with open(path) as f:
             d = json.load(f)
-        peaks = {k: float(d[k]) for k in ("hbm_gbs", "bf16_tflops") if k in d}
-        if len(peaks) == 2:
-            peaks["bf16_tflops_sustained"] = float(d.get("bf16_tflops_sustained", peaks["bf16_tflops"]))
+        def number(v):                       # a plain number, or an object that holds one under "value"
+            return float(v["value"] if isinstance(v, dict) else v)
+        peaks = {k: number(d[k]) for k in ("hbm_gbs", "bf16_tflops") if k in d}
+        if len(peaks) == 2 and all(v > 0 for v in peaks.values()):
+            peaks["bf16_tflops_sustained"] = number(d.get("bf16_tflops_sustained", peaks["bf16_tflops"]))
             return peaks, "measured"
-    except (OSError, ValueError, KeyError):
+    except Exception:                            # an unreadable file is no reason to lose the run: fall back
         pass
     return dict(FALLBACK_PEAKS), "fallback"
 

@@ -144,9 +144,11 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     unsigned char* v_tiles = k_tiles + AT_KV_STAGES * KV_BYTES;
     unsigned char* p_tile = v_tiles + AT_KV_STAGES * KV_BYTES;
     uint64_t* q_full = reinterpret_cast<uint64_t*>(p_tile + AtSmem<HD>::P_BYTES);
-    uint64_t* kv_full = q_full + 1;
-    uint64_t* kv_empty = kv_full + AT_KV_STAGES;
-    uint64_t* s_full = kv_empty + AT_KV_STAGES;          // [2]: the two S buffers
+    uint64_t* k_full = q_full + 1;                       // K and V have barriers of their own: a K buffer is free as soon
+    uint64_t* k_empty = k_full + AT_KV_STAGES;           // as its scores are formed, long before its tile's V buffer is
+    uint64_t* v_full = k_empty + AT_KV_STAGES;
+    uint64_t* v_empty = v_full + AT_KV_STAGES;
+    uint64_t* s_full = v_empty + AT_KV_STAGES;           // [2]: the two S buffers
     uint64_t* s_empty = s_full + 2;                      // [2]
     uint64_t* p_full = s_empty + 2;
     uint64_t* o_full = p_full + 1;
@@ -170,7 +172,10 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
     if (threadIdx.x == 0) {
         at_bar_init(q_full, 1);
-        for (int s = 0; s < AT_KV_STAGES; ++s) { at_bar_init(&kv_full[s], 1); at_bar_init(&kv_empty[s], 1); }
+        for (int s = 0; s < AT_KV_STAGES; ++s) {
+            at_bar_init(&k_full[s], 1); at_bar_init(&k_empty[s], 1);
+            at_bar_init(&v_full[s], 1); at_bar_init(&v_empty[s], 1);
+        }
         for (int i = 0; i < 2; ++i) { at_bar_init(&s_full[i], 1); at_bar_init(&s_empty[i], 4); }
         at_bar_init(p_full, 4);
         at_bar_init(o_full, 1);
@@ -194,23 +199,33 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             at_expect_tx(q_full, (uint32_t)AtSmem<HD>::Q_BYTES);
             for (int a = 0; a < ATOMS; ++a)             // rows (token, head of the group): a box of [128 / G tokens][G heads][64 d]
                 at_tma_3d(q_tile + (size_t)a * AT_ROWS * 128, &map_q, q_full, a * 64, kvh * G, t0 + q0);
+            // K of tile j + 1 goes out before V of tile j: its buffer is free earlier (after the scores of tile j - 1,
+            // not after the product of tile j - 2), and the tensor core wants it earlier (the scores run two tiles ahead).
             bool ok = true;
-            int issued = 0;
-            for (int j = 0; j < n_tiles && ok; ++j) {
+            int k_issued = 0, v_issued = 0;
+            auto load = [&](int j, bool is_k) -> bool {
                 const int s = j % AT_KV_STAGES;
-                if (j >= AT_KV_STAGES) ok = at_wait(&kv_empty[s], ((j / AT_KV_STAGES) - 1) & 1);
-                if (!ok) break;
-                const int row0 = (pages[tile_first + j] * Hkv + kvh) * AT_KEYS;      // the (page, head) block's first row
-                at_expect_tx(&kv_full[s], 2 * KV_BYTES);
-                for (int a = 0; a < ATOMS; ++a) {
-                    at_tma_2d(k_tiles + (size_t)s * KV_BYTES + (size_t)a * AT_KEYS * 128, &map_k, &kv_full[s], a * 64, row0);
-                    at_tma_2d(v_tiles + (size_t)s * KV_BYTES + (size_t)a * AT_KEYS * 128, &map_v, &kv_full[s], a * 64, row0);
-                }
-                issued = j + 1;
+                uint64_t* empty = is_k ? &k_empty[s] : &v_empty[s];
+                uint64_t* full = is_k ? &k_full[s] : &v_full[s];
+                if (j >= AT_KV_STAGES && !at_wait(empty, ((j / AT_KV_STAGES) - 1) & 1)) return false;
+                const int row0 = (pages[tile_first + j] * Hkv + kvh) * AT_KEYS;        // the (page, head) block's first row
+                unsigned char* dst = (is_k ? k_tiles : v_tiles) + (size_t)s * KV_BYTES;
+                at_expect_tx(full, KV_BYTES);
+                for (int a = 0; a < ATOMS; ++a)
+                    at_tma_2d(dst + (size_t)a * AT_KEYS * 128, is_k ? &map_k : &map_v, full, a * 64, row0);
+                if (is_k) k_issued = j + 1; else v_issued = j + 1;
+                return true;
+            };
+            ok = load(0, true);
+            for (int j = 0; j < n_tiles && ok; ++j) {
+                if (j + 1 < n_tiles) ok = load(j + 1, true);
+                if (ok) ok = load(j, false);
             }
             if (!ok) {
                 atomicExch(error, 1);
-                for (int j = max(0, issued - AT_KV_STAGES); j < issued; ++j) at_wait(&kv_full[j % AT_KV_STAGES], (j / AT_KV_STAGES) & 1);
+                // copies already issued still write shared memory: wait for them (bounded) before the block ends
+                for (int j = max(0, k_issued - AT_KV_STAGES); j < k_issued; ++j) at_wait(&k_full[j % AT_KV_STAGES], (j / AT_KV_STAGES) & 1);
+                for (int j = max(0, v_issued - AT_KV_STAGES); j < v_issued; ++j) at_wait(&v_full[j % AT_KV_STAGES], (j / AT_KV_STAGES) & 1);
             }
         }
     } else if (warp == 1) {
@@ -221,7 +236,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // S runs two tiles ahead of P V: while the softmax warps work on one S buffer the tensor core fills the other.
             auto issue_s = [&](int j) -> bool {
                 const int s = j % AT_KV_STAGES;
-                if (!at_wait(&kv_full[s], (j / AT_KV_STAGES) & 1)) return false;
+                if (!at_wait(&k_full[s], (j / AT_KV_STAGES) & 1)) return false;
                 if (j >= 2 && !at_wait(&s_empty[j & 1], ((j >> 1) - 1) & 1)) return false;
                 at_fence_after();
                 const unsigned char* kt = k_tiles + (size_t)s * KV_BYTES;
@@ -231,6 +246,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     const uint64_t db = at_desc_kmajor(kt + (size_t)(k / 4) * AT_KEYS * 128) + 2 * (k % 4);
                     at_mma(tmem_s + (uint32_t)(j & 1) * 64, da, db, idesc_s, k > 0 ? 1u : 0u);
                 }
+                at_commit(&k_empty[s]);                                                // K of this tile is read
                 at_commit(&s_full[j & 1]);
                 return true;
             };
@@ -238,7 +254,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (ok && n_tiles > 1) ok = issue_s(1);
             for (int j = 0; j < n_tiles && ok; ++j) {
                 const int s = j % AT_KV_STAGES;
-                ok = at_wait(p_full, j & 1);                                           // P of this tile is in shared memory
+                ok = at_wait(&v_full[s], (j / AT_KV_STAGES) & 1) && at_wait(p_full, j & 1);   // V has landed; P is in shared memory
                 if (!ok) break;
                 at_fence_after();
                 const unsigned char* vt = v_tiles + (size_t)s * KV_BYTES;
@@ -248,7 +264,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     const uint64_t db = at_desc_mnmajor(vt + (size_t)k * 16 * 128, AT_KEYS * 128);
                     at_mma(tmem_o, da, db, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
                 }
-                at_commit(&kv_empty[s]);                                               // K and V of this tile are read
+                at_commit(&v_empty[s]);                                                // V of this tile is read
                 at_commit(o_full);
                 if (j + 2 < n_tiles) ok = issue_s(j + 2);
             }

@@ -155,11 +155,13 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.z, kvh = blockIdx.y;
+    const int b = blockIdx.z, kvh = blockIdx.x;
     const int tok_per_block = AT_ROWS / G;
     const int t0 = cu_seqlens[b], n_new = cu_seqlens[b + 1] - t0;
-    // the last tokens see the most keys: their blocks go first, so that the long blocks do not form the tail of the launch
-    const int q0 = (int)(gridDim.x - 1 - blockIdx.x) * tok_per_block;
+    // The last tokens see the most keys: their blocks go first, so that the long blocks do not form the tail of the launch.
+    // Blocks start in the order of blockIdx.x, then y: the key/value head is x, so that the longest blocks of every head
+    // start before any short one.
+    const int q0 = (int)(gridDim.y - 1 - blockIdx.y) * tok_per_block;
     if (q0 >= n_new) return;
     const int p0 = pos0[b];
     const int len = p0 + n_new;
@@ -446,7 +448,7 @@ static int launch_attn_tc(const void* q, const void* k_pool, const void* v_pool,
     cudaError_t e = cudaFuncSetAttribute(attn_tc_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "attn_tc_prefill: %s", cudaGetErrorString(e));
     const int tok_per_block = AT_ROWS / G;
-    dim3 grid((max_new + tok_per_block - 1) / tok_per_block, Hkv, B);
+    dim3 grid(Hkv, (max_new + tok_per_block - 1) / tok_per_block, B);
     e = qwb_launch(attn_tc_prefill_kernel<HD>, grid, AT_THREADS, smem, stream, map_q, map_k, map_v, page_table, cu_seqlens, pos0,
                    (bf16*)out, Hq, Hkv, table_width, scale, window, G, error);
     if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "attn_tc_prefill: launch failed: %s", cudaGetErrorString(e));
@@ -464,7 +466,8 @@ extern "C" int qwb_attn_tc_prefill(const void* q, const void* k_pool, const void
     if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: %d query heads are not a multiple of %d key/value heads", Hq, Hkv);
     const int G = Hq / Hkv;
     if (G != 1 && G != 2 && G != 4 && G != 8 && G != 16) return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: %d query heads per key/value head; this kernel takes 1, 2, 4, 8 or 16", G);
-    if (B > 65535 || Hkv > 65535) return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: batch %d or heads %d above 65535", B, Hkv);
+    if (B > 65535 || (max_new + AT_ROWS / G - 1) / (AT_ROWS / G) > 65535)
+        return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: batch %d or %d new tokens of a sequence are more than the grid takes", B, max_new);
     if (!error) return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: an error word on the device is required");
     if ((uintptr_t)q % 16 || (uintptr_t)k_pool % 16 || (uintptr_t)v_pool % 16 || (uintptr_t)out % 16)
         return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: operands must be 16-byte aligned");

@@ -308,12 +308,15 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
                     for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[h][i]));
             } else {
+                // this row sees the tile's keys [first, end): one subtraction and one unsigned comparison per key
+                const int end = min(min(qp, len - 1) - key0 + 1, AT_KEYS);
+                const int first = window > 0 ? max(qp - window + 1 - key0, 0) : 0;
+                const unsigned span = end > first ? (unsigned)(end - first) : 0u;
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        const int key = key0 + 32 * h + i;
-                        const bool vis = key <= qp && key < len && (window <= 0 || key > qp - window);
+                        const bool vis = (unsigned)(32 * h + i - first) < span;
                         const float sc = vis ? __uint_as_float(sv[h][i]) : -INFINITY;
                         sv[h][i] = __float_as_uint(sc);
                         mx = fmaxf(mx, sc);

@@ -192,11 +192,13 @@ attn_mma_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* tiles = reinterpret_cast<bf16*>(smem_raw);                 // [2 buffers][K, V][64][HD]
     const int b = blockIdx.z;
-    const int kvh = blockIdx.y / chunks, chunk = blockIdx.y % chunks;
+    const int kvh = blockIdx.x / chunks, chunk = blockIdx.x % chunks;
     const int G = Hq / Hkv;
     const int tok_per_block = (AM_WARPS * 16) / Gc;
     const int t0 = cu_seqlens[b], n_new = cu_seqlens[b + 1] - t0;
-    const int q0 = blockIdx.x * tok_per_block;
+    // The last tokens see the most keys: their blocks start first (blocks start in the order of x, then y; the head is x),
+    // so that the long blocks do not form the tail of the launch.
+    const int q0 = (int)(gridDim.y - 1 - blockIdx.y) * tok_per_block;
     if (q0 >= n_new) return;
     const int p0 = pos0[b];
     const int len = p0 + n_new;
@@ -475,7 +477,8 @@ static int launch_prefill(const void* q, const void* k_pool, const void* v_pool,
     const size_t smem = (size_t)2 * 2 * AM_TILE * HD * sizeof(bf16);
     cudaError_t e = cudaFuncSetAttribute(attn_mma_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "attn_mma_prefill: %s", cudaGetErrorString(e));
-    dim3 grid((max_new + tok_per_block - 1) / tok_per_block, Hkv * chunks, B);
+    dim3 grid(Hkv * chunks, (max_new + tok_per_block - 1) / tok_per_block, B);
+    if (grid.y > 65535) return qwb_fail(QWB_ERR_ARG, "attn_mma_prefill: %d new tokens of a sequence are more than the grid takes", max_new);
     qwb_launch(attn_mma_prefill_kernel<HD>, grid, AM_WARPS * 32, smem, stream, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
         page_table, cu_seqlens, pos0, (bf16*)out, Hq, Hkv, table_width, scale, window, Gc, chunks);
     return qwb_check_launch("attn_mma_prefill");

@@ -1,8 +1,8 @@
 // Prefill attention on the fifth-generation tensor cores (tcgen05), bfloat16, head sizes 64 and 128, groups of
-// 1, 2, 4, 8 or 16 query heads per key/value head, pages of 64 keys.  Same contract as attn_prefill in attention.cu.
+// up to 64 query heads per key/value head, pages of 64 keys.  Same contract as attn_prefill in attention.cu.
 //
-// A block serves 128 rows = (128 / G tokens) x (the G query heads of one key/value head).  Per tile of 64 keys (one
-// cache page of that head):
+// A block serves (128 / G tokens, rounded down) x (the G query heads of one key/value head) rows, up to 128; with a
+// G that does not divide 128 the last rows of the 128 stay unused.  Per tile of 64 keys (one cache page of that head):
 //     S = Q K^T      tcgen05.mma, Q and K from shared memory (TMA, 128-byte swizzle), S in tensor memory (64 columns, two
 //                    buffers: the tensor core is up to two tiles ahead of the softmax)
 //     P = softmax    four warps, one thread per row: read S, mask, running maximum and sum in 32-bit, write P as
@@ -198,7 +198,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
     if (warp == 0) {
         if (lane == 0) {
-            at_expect_tx(q_full, (uint32_t)AtSmem<HD>::Q_BYTES);
+            at_expect_tx(q_full, (uint32_t)(tok_per_block * G * HD * 2));      // the box's bytes: with G no divisor of 128, fewer than 128 rows
             for (int a = 0; a < ATOMS; ++a)             // rows (token, head of the group): a box of [128 / G tokens][G heads][64 d]
                 at_tma_3d(q_tile + (size_t)a * AT_ROWS * 128, &map_q, q_full, a * 64, kvh * G, t0 + q0);
             // K of tile j + 1 goes out before V of tile j: its buffer is free earlier (after the scores of tile j - 1,
@@ -281,7 +281,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int lane_group = warp & 3;
         const int r = 32 * lane_group + lane;                                          // this thread's row = tensor-memory lane
         const int tok = q0 + r / G, head = kvh * G + r % G;
-        const bool row_ok = tok < n_new;
+        const bool row_ok = r < tok_per_block * G && tok < n_new;                      // rows beyond the box hold nothing
         const int qp = row_ok ? p0 + tok : -1;
         const uint32_t lane_off = (uint32_t)(32 * lane_group) << 16;
         const float sl2 = scale * 1.4426950408889634f;
@@ -468,7 +468,7 @@ extern "C" int qwb_attn_tc_prefill(const void* q, const void* k_pool, const void
     if (page_size != AT_KEYS) return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: page size %d is not %d", page_size, AT_KEYS);
     if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: %d query heads are not a multiple of %d key/value heads", Hq, Hkv);
     const int G = Hq / Hkv;
-    if (G != 1 && G != 2 && G != 4 && G != 8 && G != 16) return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: %d query heads per key/value head; this kernel takes 1, 2, 4, 8 or 16", G);
+    if (G > AT_ROWS / 2) return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: %d query heads per key/value head; this kernel takes up to %d", G, AT_ROWS / 2);
     if (B > 65535 || (max_new + AT_ROWS / G - 1) / (AT_ROWS / G) > 65535)
         return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: batch %d or %d new tokens of a sequence are more than the grid takes", B, max_new);
     if (!error) return qwb_fail(QWB_ERR_ARG, "attn_tc_prefill: an error word on the device is required");

@@ -194,7 +194,7 @@ def mma_attention_fits(dtype: torch.dtype, head_dim: int, page_size: int) -> boo
 
 def tc_attention_fits(dtype: torch.dtype, head_dim: int, page_size: int, group: int) -> bool:
     """Whether the tcgen05 prefill attention kernel takes this case."""
-    return mma_attention_fits(dtype, head_dim, page_size) and group in (1, 2, 4, 8, 16)
+    return mma_attention_fits(dtype, head_dim, page_size) and 1 <= group <= 64
 
 
 def attn_prefill(q, k_pool, v_pool, page_table, cu_seqlens, pos0, max_new: int, scale: float,

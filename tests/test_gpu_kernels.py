@@ -201,7 +201,9 @@ def test_attn_prefill_tensor_cores(Hq, Hkv, hd, window):
     _attn_prefill_case(torch.bfloat16, Hq, Hkv, hd, window, "mma")
 
 
-@pytest.mark.parametrize("Hq,Hkv,hd", [(8, 2, 64), (8, 1, 128), (4, 4, 128), (16, 1, 64), (32, 8, 128), (4, 2, 128)])
+@pytest.mark.parametrize("Hq,Hkv,hd", [(8, 2, 64), (8, 1, 128), (4, 4, 128), (16, 1, 64), (32, 8, 128), (4, 2, 128),
+                                       # heads per key/value head that do not divide the block's 128 rows
+                                       (6, 2, 128), (40, 8, 128), (7, 1, 64), (12, 1, 64), (33, 1, 128)])
 @pytest.mark.parametrize("window", [0, 37])
 def test_attn_prefill_tcgen05(Hq, Hkv, hd, window):
     _attn_prefill_case(torch.bfloat16, Hq, Hkv, hd, window, "tc")

@@ -6,7 +6,11 @@
 // Nothing is sorted.  The k-th largest logit and the top-p cut are found by radix
 // selection over an order-preserving 32-bit key of the logit (four passes of 8 bits
 // with a histogram of counts or of probability mass in shared memory); ties at a cut
-// are broken toward the lower token id.  The draw walks the kept tokens in id order with
+// are broken toward the lower token id.  Every warp fills a histogram of its own, and
+// the lanes of a warp that hit the same bin are added up by one of them first, so no
+// two threads ever write the same word and no atomic operation is needed: with a
+// vocabulary of 150,000 a histogram shared by the block, updated atomically, cost a
+// millisecond a cut.  Rows are read 16 bytes a load.  The draw walks the kept tokens in id order with
 // a uniform number from a counter-based generator (Philox 4x32-10) keyed by the seed,
 // the sequence's own index and the step, so a sequence's tokens do not depend on what
 // else is in the batch.
@@ -48,27 +52,93 @@ __device__ __forceinline__ bool kept(const Cut& c, uint32_t key, int id) {
     return key > c.key || (key == c.key && id <= c.id_limit);
 }
 
+#define SAMPLE_WARPS (SAMPLE_THREADS / 32)
+
+// Calls f(id, logit, valid) for the whole row.  All threads of the block make the same number of calls (valid is false
+// where a thread has no token), so f may use warp-wide operations.  16-byte loads where the row's address allows.
+template <typename F>
+__device__ __forceinline__ void for_each_logit(const float* row, int V, F f) {
+    const int tid = threadIdx.x, nthreads = blockDim.x;
+    int done = 0;
+    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        const int n4 = V >> 2;
+#pragma unroll 2
+        for (int base = 0; base < n4; base += nthreads) {
+            const int idx = base + tid;
+            const bool valid = idx < n4;
+            const float4 v = valid ? row4[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
+            f(4 * idx, v.x, valid);
+            f(4 * idx + 1, v.y, valid);
+            f(4 * idx + 2, v.z, valid);
+            f(4 * idx + 3, v.w, valid);
+        }
+        done = n4 << 2;
+    }
+    for (int base = done; base < V; base += nthreads) {
+        const int i = base + tid;
+        const bool valid = i < V;
+        f(i, valid ? row[i] : 0.f, valid);
+    }
+}
+
+// A double summed over the block, the warps' sums added in warp order (every thread gets the total).
+__device__ double block_sum(double s, double* red_d) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    __syncthreads();
+    if (lane == 0) red_d[warp] = s;
+    __syncthreads();
+    double total = 0.0;
+    for (int w = 0; w < (blockDim.x >> 5); ++w) total += red_d[w];
+    return total;
+}
+
 // Radix selection.  Among the tokens kept by `within`, finds the cut such that the kept
 // tokens above it, plus as many tokens at it as needed (lowest ids first), reach `target`:
 // a count (by_mass = false) or a probability mass (by_mass = true; mass of token i is
-// exp((l_i - lmax) / temperature)).
+// exp((l_i - lmax) / temperature)).  whist / whist_n: [warps][256], a histogram per warp.
 __device__ Cut radix_cut(const float* row, int V, const Cut within, bool by_mass, double target,
-                         float lmax, float inv_temp, double* hist, int* hist_n, double* sh_above, uint32_t* sh_prefix) {
-    const int tid = threadIdx.x;
+                         float lmax, float inv_temp, double* whist, int* whist_n, double* hist, int* hist_n,
+                         double* sh_above, uint32_t* sh_prefix) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    double* my_hist = whist + warp * 256;
+    int* my_n = whist_n + warp * 256;
     uint32_t prefix = 0, mask = 0;
     double above = 0.0;
     int n_at = 0;
     for (int shift = 24; shift >= 0; shift -= 8) {
-        for (int i = tid; i < 256; i += blockDim.x) { hist[i] = 0.0; hist_n[i] = 0; }
+        for (int i = tid; i < SAMPLE_WARPS * 256; i += blockDim.x) { whist[i] = 0.0; whist_n[i] = 0; }
         __syncthreads();
-        for (int i = tid; i < V; i += blockDim.x) {
-            const float l = row[i];
+        for_each_logit(row, V, [&](int i, float l, bool valid) {
             const uint32_t key = order_key(l);
-            if ((key & mask) == prefix && kept(within, key, i)) {
+            const bool hit = valid && (key & mask) == prefix && kept(within, key, i);
+            const unsigned hits = __ballot_sync(0xffffffffu, hit);
+            if (hits == 0u) return;                                   // the same for the whole warp
+            if (hit) {
                 const int bin = (key >> shift) & 255;
-                atomicAdd(&hist[bin], by_mass ? (double)expf((l - lmax) * inv_temp) : 1.0);
-                atomicAdd(&hist_n[bin], 1);
+                const unsigned peers = __match_any_sync(hits, bin);  // the lanes that hit this bin
+                double sum = (double)__popc(peers);
+                if (by_mass) {                                        // their masses, added in lane order
+                    const double m = (double)expf((l - lmax) * inv_temp);
+                    sum = 0.0;
+                    for (unsigned rest = peers; rest; rest &= rest - 1) sum += __shfl_sync(peers, m, __ffs(rest) - 1);
+                }
+                if (lane == __ffs(peers) - 1) {                       // one lane per bin: no two write the same word
+                    my_hist[bin] += sum;
+                    my_n[bin] += __popc(peers);
+                }
             }
+            __syncwarp();                                             // the next call may have another lane write this bin
+        });
+        __syncthreads();
+        for (int bin = tid; bin < 256; bin += blockDim.x) {          // the warps' histograms, added in warp order
+            double sum = 0.0;
+            int n = 0;
+            for (int w = 0; w < SAMPLE_WARPS; ++w) { sum += whist[w * 256 + bin]; n += whist_n[w * 256 + bin]; }
+            hist[bin] = sum;
+            hist_n[bin] = n;
         }
         __syncthreads();
         if (tid == 0) {
@@ -135,6 +205,9 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
               const unsigned int* __restrict__ step_add, int* __restrict__ out_ids, double* out_u) {
     pdl_wait();
     pdl_launch_dependents();
+    extern __shared__ __align__(8) unsigned char sample_smem[];      // a histogram per warp: [warps][256] masses, then counts
+    double* whist = reinterpret_cast<double*>(sample_smem);
+    int* whist_n = reinterpret_cast<int*>(whist + SAMPLE_WARPS * 256);
     __shared__ double hist[256];
     __shared__ int hist_n[256];
     __shared__ double sh_above;
@@ -142,7 +215,6 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
     __shared__ float red_v[32];
     __shared__ int red_i[32];
     __shared__ double red_d[SAMPLE_THREADS / 32];
-    __shared__ double warp_base[SAMPLE_THREADS / 32];
     __shared__ int sh_pick;
 
     const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -211,69 +283,91 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
     cut.key = 0u;
     cut.id_limit = V;
     if (top_k > 0 && top_k < V)
-        cut = radix_cut(row, V, cut, false, (double)top_k, best, inv_temp, hist, hist_n, &sh_above, &sh_prefix);
+        cut = radix_cut(row, V, cut, false, (double)top_k, best, inv_temp, whist, whist_n, hist, hist_n, &sh_above, &sh_prefix);
 
     auto block_mass = [&](const Cut& c) -> double {
-        double s = 0.0;
-        for (int i = tid; i < V; i += blockDim.x) {
-            const float l = row[i];
-            if (kept(c, order_key(l), i)) s += (double)expf((l - best) * inv_temp);
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-        __syncthreads();
-        if (lane == 0) red_d[warp] = s;
-        __syncthreads();
-        double total = 0.0;
-        for (int w = 0; w < (blockDim.x >> 5); ++w) total += red_d[w];
-        return total;
+        double mine = 0.0;
+        for_each_logit(row, V, [&](int i, float l, bool valid) {
+            if (valid && kept(c, order_key(l), i)) mine += (double)expf((l - best) * inv_temp);
+        });
+        return block_sum(mine, red_d);
     };
 
     if (top_p < 1.f) {
         const double total = block_mass(cut);
-        cut = radix_cut(row, V, cut, true, (double)top_p * total, best, inv_temp, hist, hist_n, &sh_above, &sh_prefix);
+        cut = radix_cut(row, V, cut, true, (double)top_p * total, best, inv_temp, whist, whist_n, hist, hist_n, &sh_above, &sh_prefix);
     }
 
-    // 5. one draw, walking the kept tokens in id order; each thread owns a run of ids
-    const int seg = (V + blockDim.x - 1) / blockDim.x;
-    const int i0 = min(V, tid * seg), i1 = min(V, i0 + seg);
-    double mine = 0.0;
-    for (int i = i0; i < i1; ++i) {
-        const float l = row[i];
-        if (kept(cut, order_key(l), i)) mine += (double)expf((l - best) * inv_temp);
-    }
-    double incl = mine;                                  // inclusive scan inside the warp
+    // 5. one draw, walking the kept tokens in id order.  Every warp owns a run of ids (a multiple of 128, so that its
+    // lanes read 16 bytes each, 4 ids in a row): first each warp adds up its run, then the one warp whose run holds the
+    // drawn point walks it again, 128 ids at a time with a scan over its lanes.
+    const int n_warps = (int)(blockDim.x >> 5);
+    const int per_warp = ((V + n_warps - 1) / n_warps + 127) / 128 * 128;
+    const int w0 = min(V, warp * per_warp), w1 = min(V, w0 + per_warp);
+    const bool vec = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
+    auto masses = [&](int i0, double* m) -> double {          // masses of the 4 ids from i0 on (0 where not kept), and their sum
+        float l4[4] = {0.f, 0.f, 0.f, 0.f};
+        if (vec && i0 + 3 < V) {
+            const float4 v = *reinterpret_cast<const float4*>(row + i0);
+            l4[0] = v.x; l4[1] = v.y; l4[2] = v.z; l4[3] = v.w;
+        } else {
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const double up = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += up;
+            for (int e = 0; e < 4; ++e) if (i0 + e < V) l4[e] = row[i0 + e];
+        }
+        double sum = 0.0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int i = i0 + e;
+            m[e] = (i < w1 && kept(cut, order_key(l4[e]), i)) ? (double)expf((l4[e] - best) * inv_temp) : 0.0;
+            sum += m[e];
+        }
+        return sum;
+    };
+    double mine = 0.0;
+    for (int c0 = w0; c0 < w1; c0 += 128) {
+        double m[4];
+        mine += masses(c0 + 4 * lane, m);
     }
-    if (lane == 31) red_d[warp] = incl;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+    if (lane == 0) red_d[warp] = mine;
     if (tid == 0) sh_pick = -1;
     __syncthreads();
-    if (tid == 0) {
-        double run = 0.0;
-        for (int w = 0; w < (blockDim.x >> 5); ++w) { warp_base[w] = run; run += red_d[w]; }
-        sh_above = run;                                   // the kept tokens' whole mass
+    double before_warp = 0.0, total = 0.0;
+    for (int w = 0; w < n_warps; ++w) {
+        if (w < warp) before_warp += red_d[w];
+        total += red_d[w];
     }
-    __syncthreads();
-    const double total = sh_above;
     const double u = philox_uniform(seed, (unsigned int)(sequence_index ? sequence_index[b] : b),
                                     step + (step_add ? *step_add : 0u));
     const double r = u * total;
-    const double before = warp_base[warp] + incl - mine;
-    if (mine > 0.0 && r > before && r <= before + mine) {
-        double run = before;
+    if (red_d[warp] > 0.0 && r > before_warp && r <= before_warp + red_d[warp]) {    // this warp's run holds the point
+        double running = before_warp;
         int pick = -1;
-        for (int i = i0; i < i1; ++i) {
-            const float l = row[i];
-            if (kept(cut, order_key(l), i)) {
-                run += (double)expf((l - best) * inv_temp);
-                pick = i;
-                if (run >= r) break;
+        for (int c0 = w0; c0 < w1 && pick < 0; c0 += 128) {
+            const int i0 = c0 + 4 * lane;
+            double m[4];
+            const double sum = masses(i0, m);
+            double incl = sum;                           // inclusive scan over the lanes
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const double up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += up;
             }
+            const double before = running + incl - sum;
+            int found = -1;
+            if (sum > 0.0 && r > before && r <= before + sum) {
+                double run = before;
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (m[e] > 0.0 && (found < 0 || run < r)) { run += m[e]; found = i0 + e; }
+            }
+            // at most one lane finds it; rounding at a chunk's edge may leave it to the next chunk or to the fallback
+            const unsigned who = __ballot_sync(0xffffffffu, found >= 0);
+            if (who) pick = __shfl_sync(0xffffffffu, found, __ffs(who) - 1);
+            running += __shfl_sync(0xffffffffu, incl, 31);
         }
-        sh_pick = pick;
+        if (lane == 0) sh_pick = pick;
     }
     __syncthreads();
     if (tid == 0) {
@@ -290,7 +384,14 @@ extern "C" int qwb_sample(float* logits, int B, int V, const int* recent, int wi
     if (V <= 0) return qwb_fail(QWB_ERR_ARG, "sample: bad vocabulary size %d", V);
     if (temperature > 0.f && !(top_p > 0.f)) return qwb_fail(QWB_ERR_ARG, "sample: top_p must be > 0, got %g", (double)top_p);
     if (repeat_penalty <= 0.f) return qwb_fail(QWB_ERR_ARG, "sample: repeat_penalty must be > 0, got %g", (double)repeat_penalty);
-    qwb_launch(sample_kernel, B, SAMPLE_THREADS, 0, stream, logits, V, recent, window, repeat_penalty, presence_penalty,
+    const size_t smem = (size_t)SAMPLE_WARPS * 256 * (sizeof(double) + sizeof(int));
+    static bool sized = false;
+    if (!sized) {
+        cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "sample: %s", cudaGetErrorString(e));
+        sized = true;
+    }
+    qwb_launch(sample_kernel, B, SAMPLE_THREADS, smem, stream, logits, V, recent, window, repeat_penalty, presence_penalty,
                                                    frequency_penalty, temperature, top_k, top_p, seed, sequence_index,
                                                    step, step_add, out_ids, out_u);
     return qwb_check_launch("sample");

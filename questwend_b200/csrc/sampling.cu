@@ -10,7 +10,9 @@
 // the lanes of a warp that hit the same bin are added up by one of them first, so no
 // two threads ever write the same word and no atomic operation is needed: with a
 // vocabulary of 150,000 a histogram shared by the block, updated atomically, cost a
-// millisecond a cut.  Rows are read 16 bytes a load.  The draw walks the kept tokens in id order with
+// millisecond a cut.  Rows are read 16 bytes a load.  When top-k leaves at most one token
+// per thread (the usual case: the reference's default is 40), the kept tokens are gathered
+// into shared memory and top-p and the draw are done there.  The draw walks the kept tokens in id order with
 // a uniform number from a counter-based generator (Philox 4x32-10) keyed by the seed,
 // the sequence's own index and the step, so a sequence's tokens do not depend on what
 // else is in the batch.
@@ -284,6 +286,86 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
     cut.id_limit = V;
     if (top_k > 0 && top_k < V)
         cut = radix_cut(row, V, cut, false, (double)top_k, best, inv_temp, whist, whist_n, hist, hist_n, &sh_above, &sh_prefix);
+
+    if (top_k > 0 && top_k < V && top_k <= SAMPLE_THREADS) {
+        // Few tokens are left (at most one per thread): they are gathered into shared memory, put in id order, and
+        // top-p and the draw are done on them there, instead of in further passes over the whole row.
+        int* cand_id = reinterpret_cast<int*>(sample_smem);              // as found
+        float* cand_l = reinterpret_cast<float*>(cand_id + SAMPLE_THREADS);
+        int* by_id = reinterpret_cast<int*>(cand_l + SAMPLE_THREADS);    // in id order
+        float* by_id_l = reinterpret_cast<float*>(by_id + SAMPLE_THREADS);
+        double* by_rank_m = reinterpret_cast<double*>(by_id_l + SAMPLE_THREADS);   // masses, largest logit first
+        __shared__ int cand_n, keep_n;
+        if (tid == 0) { cand_n = 0; sh_pick = -1; }
+        __syncthreads();
+        for_each_logit(row, V, [&](int i, float l, bool valid) {
+            if (valid && kept(cut, order_key(l), i)) {
+                const int slot = atomicAdd(&cand_n, 1);
+                if (slot < SAMPLE_THREADS) { cand_id[slot] = i; cand_l[slot] = l; }
+            }
+        });
+        __syncthreads();
+        const int n = min(cand_n, SAMPLE_THREADS);
+        if (tid < n) {                                                   // place by the number of smaller ids
+            const int id = cand_id[tid];
+            int pos = 0;
+            for (int j = 0; j < n; ++j) pos += cand_id[j] < id;
+            by_id[pos] = id;
+            by_id_l[pos] = cand_l[tid];
+        }
+        __syncthreads();
+        const bool have = tid < n;
+        const int id = have ? by_id[tid] : 0;
+        const float l = have ? by_id_l[tid] : 0.f;
+        const double m = have ? (double)expf((l - best) * inv_temp) : 0.0;
+        bool keep = have;
+        if (top_p < 1.f) {
+            const double total = block_sum(m, red_d);
+            if (have) {                                                  // rank: larger logits first, lower ids first among equals
+                int rank = 0;
+                for (int j = 0; j < n; ++j) rank += by_id_l[j] > l || (by_id_l[j] == l && by_id[j] < id);
+                by_rank_m[rank] = m;
+                cand_id[tid] = rank;                                     // (the gather's arrays are free again)
+            }
+            __syncthreads();
+            if (tid == 0) {                                              // the smallest prefix whose share reaches top_p
+                const double target = (double)top_p * total;
+                double run = 0.0;
+                int k = 0;
+                while (k < n) { run += by_rank_m[k++]; if (run >= target) break; }
+                keep_n = k < 1 ? 1 : k;
+            }
+            __syncthreads();
+            keep = have && cand_id[tid] < keep_n;
+        }
+        // the draw: a scan over the kept tokens in id order
+        const double mine = keep ? m : 0.0;
+        double incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const double up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        __syncthreads();
+        if (lane == 31) red_d[warp] = incl;
+        __syncthreads();
+        double before = 0.0, total = 0.0;
+        for (int w = 0; w < (blockDim.x >> 5); ++w) {
+            if (w < warp) before += red_d[w];
+            total += red_d[w];
+        }
+        before += incl - mine;
+        const double u = philox_uniform(seed, (unsigned int)(sequence_index ? sequence_index[b] : b),
+                                        step + (step_add ? *step_add : 0u));
+        const double r = u * total;
+        if (mine > 0.0 && r > before && r <= before + mine) sh_pick = id;
+        __syncthreads();
+        if (tid == 0) {
+            out_ids[b] = sh_pick >= 0 ? sh_pick : best_i;
+            if (out_u) out_u[b] = u;
+        }
+        return;
+    }
 
     auto block_mass = [&](const Cut& c) -> double {
         double mine = 0.0;

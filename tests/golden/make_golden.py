@@ -2,7 +2,7 @@
 """Makes tests/golden/qwen3_tiny_{A,B}.npz: the logits of kishida/questwend's own CPU code
 on the two tiny random models of the tests.
 
-    python tests/golden/make_golden.py [--reference /root/reference] [--build-dir DIR]
+    python tests/golden/make_golden.py --reference <checkout of kishida/questwend> [--build-dir DIR]
 
 It builds the reference's ``questwend_core`` library with CMake (CPU only, no network), compiles
 ``ref_driver.cpp`` against it, writes each tiny model with this library's random-weights mode
@@ -52,7 +52,7 @@ def gguf_name(hf: str) -> str:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="a checkout of kishida/questwend (read only)")
     ap.add_argument("--build-dir", default=os.path.join(tempfile.gettempdir(), "questwend_ref_build"))
     args = ap.parse_args()
     ref, bd = args.reference, args.build_dir

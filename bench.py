@@ -34,7 +34,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-QWEN3_8B = {                     # BASELINE.json configs[2]
+QWEN3_8B = {                     # the layer sizes of Qwen3-8B: the model this benchmark is quoted on
     "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
     "num_hidden_layers": 36, "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8,
     "head_dim": 128, "intermediate_size": 12288, "vocab_size": 151936, "rope_theta": 1e6,

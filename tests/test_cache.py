@@ -120,3 +120,51 @@ def test_sizes():
     assert pages_for(0) == 0 and pages_for(1) == 1 and pages_for(PAGE_SIZE) == 1 and pages_for(PAGE_SIZE + 1) == 2
     with pytest.raises(CacheError):
         _manager(max_tokens=0)
+
+
+def test_random_histories_lose_and_duplicate_nothing():
+    """Random sequences of open / reserve+advance / truncate / close, two groups (one with a window): after every
+    operation no page is held twice, held and free pages add up to the pool, and lengths fit the pages held."""
+    from hypothesis import given, settings, strategies as st
+
+    ops_strategy = st.lists(st.tuples(st.sampled_from(["open", "grow", "cut", "close"]), st.integers(0, 5),
+                                      st.integers(1, 3 * PAGE_SIZE)), min_size=1, max_size=60)
+
+    @settings(max_examples=60, deadline=None)
+    @given(ops_strategy, st.booleans())
+    def run(history, with_state):
+        units = [(KVSpec(2, 16), None, None), (KVSpec(1, 32, window=40), None, None)]
+        if with_state:                                 # a sequence with fixed-size state cannot be cut back: "cut" is refused
+            units.append((None, StateSpec((3,)), None))
+        m = _manager(units=units, max_tokens=10 * PAGE_SIZE, max_slots=5)
+        held = set()
+        for what, which, amount in history:
+            try:
+                if what == "open":
+                    held.update(m.open(1))
+                elif not held:
+                    continue
+                else:
+                    slot = sorted(held)[which % len(held)]
+                    if what == "grow":
+                        want = m.length(slot) + amount
+                        m.reserve({slot: want})
+                        m.advance(slot, amount)
+                    elif what == "cut":
+                        m.truncate(slot, min(m.length(slot), amount))
+                    else:
+                        m.close([slot])
+                        held.discard(slot)
+            except CacheError:
+                pass                                   # a refusal (full, too long, fixed-size state): nothing may change
+            assert m.slots.n_free == 5 - len(held)
+            for g in m._groups:
+                pages = [p for s in held for p in g.pages[s]]
+                assert len(pages) == len(set(pages))
+                assert len(pages) + g.pool.n_free == g.pool.n
+                for s in held:
+                    assert len(g.pages[s]) * PAGE_SIZE >= m.length(s)
+        m.close(sorted(held))
+        assert m.slots.n_free == 5 and all(g.pool.n_free == g.pool.n for g in m._groups)
+
+    run()

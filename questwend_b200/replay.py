@@ -35,7 +35,9 @@ def main(argv=None) -> int:
 
     from .engine.engine import Engine, StepEntry     # after parsing: --help needs no GPU
     os.makedirs(args.out, exist_ok=True)
-    engine = Engine.from_folder(args.model, dtype=args.dtype, device=args.device, max_tokens=args.max_tokens)
+    # every live request holds at least one page of 64 tokens, so there are never more of them than pages
+    engine = Engine.from_folder(args.model, dtype=args.dtype, device=args.device, max_tokens=args.max_tokens,
+                                max_batch=max(1, -(-args.max_tokens // 64)))
     slot_of: dict = {}
     for line in sys.stdin:
         line = line.strip()

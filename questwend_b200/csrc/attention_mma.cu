@@ -299,13 +299,15 @@ attn_mma_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
     pdl_wait();
     pdl_launch_dependents();
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    const int b = blockIdx.z, run = blockIdx.x;
+    // blocks start in the order of x, then y, then z: the run is z, so that the runs that only longer sequences have
+    // (blocks that find nothing to do) start last and keep no block with keys waiting
+    const int b = blockIdx.y, run = blockIdx.z;
     const int len = seq_len[b];
     const int split_tokens = run_pages_for(len, runs_target, run_pages_max) * AM_TILE;
     const int k_lo = window > 0 ? max(0, len - window) : 0;
     const int run_first = k_lo / split_tokens, run_end = min(max_runs, (len + split_tokens - 1) / split_tokens);
     if (run < run_first || run >= run_end) return;
-    const int kvh = blockIdx.y / chunks, chunk = blockIdx.y % chunks;
+    const int kvh = blockIdx.x / chunks, chunk = blockIdx.x % chunks;
     const int G = Hq / Hkv;
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     bf16* my_tiles = reinterpret_cast<bf16*>(smem_raw);                         // K then V
@@ -513,7 +515,7 @@ static int launch_decode(const void* q, const void* k_pool, const void* v_pool, 
     float* part_acc = scratch;
     float* part_m = scratch + (size_t)B * Hq * max_runs * HD;
     float* part_l = part_m + (size_t)B * Hq * max_runs;
-    dim3 grid(max_runs, Hkv * chunks, B);
+    dim3 grid(Hkv * chunks, B, max_runs);
     qwb_launch(attn_mma_decode_kernel<HD>, grid, 32, smem, stream, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
         page_table, seq_len, part_acc, part_m, part_l, (bf16*)out, Hq, Hkv, table_width, scale, window, runs_target, run_pages_max,
         max_runs, Gc, chunks);

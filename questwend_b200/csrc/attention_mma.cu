@@ -289,9 +289,113 @@ static int max_runs_for(int max_len, int runs_target, int run_pages_max) {
     return (pages + run_pages_max - 1) / run_pages_max;
 }
 
+// FUSED: the step's own q, k and v come as the q/k/v projection left them (32-bit, [B, (Hq + 2 Hkv) * HD], q heads first),
+// and the kernel does what a kernel of its own did before: per-head norm of q and k, rotation, and the cache write of
+// the new key and value.  Every block forms the rotated q of its heads itself (a rotation pair, d and d + HD / 2, lies in
+// one thread's fragment registers); the block whose run holds the new token forms k and v, writes them to the cache
+// and puts them into its shared tiles, where the copy from the cache brought what was there before.
+struct FusedQKV {
+    const float* qkv;
+    const float* q_w;           // per-head norm weights [HD], or null: no norm
+    const float* k_w;
+    const float* cos_t;         // [B, HD / 2] of each sequence's new position, or null: no rotation
+    const float* sin_t;
+    bf16* k_pool;               // the cache, to be written
+    bf16* v_pool;
+    float eps;
+    int store_kv;               // 0: the cache belongs to another layer's run and has the new token already
+};
+
 template <int HD>
+__device__ __forceinline__ void fused_q_frags(uint32_t (*qf)[4], const FusedQKV& f, const float* row_lo, const float* row_hi,
+                                              int b, int lane) {
+    constexpr int KS = HD / 16, HALF = HD / 2;
+    const int t = lane & 3;
+    const float* rows[2] = {row_lo, row_hi};
+    float v[2][KS][4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        float ss = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const int d = 16 * ks + 2 * t;
+            const float2 a = rows[h] ? *reinterpret_cast<const float2*>(rows[h] + d) : make_float2(0.f, 0.f);
+            const float2 c = rows[h] ? *reinterpret_cast<const float2*>(rows[h] + d + 8) : make_float2(0.f, 0.f);
+            v[h][ks][0] = a.x; v[h][ks][1] = a.y; v[h][ks][2] = c.x; v[h][ks][3] = c.y;
+            ss += a.x * a.x + a.y * a.y + c.x * c.x + c.y * c.y;
+        }
+        if (f.q_w) {                                      // the row's 4 threads hold its HD values between them
+            ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+            ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+            const float scale = rsqrtf(ss / (float)HD + f.eps);
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                const int d = 16 * ks + 2 * t;
+                const float2 wa = *reinterpret_cast<const float2*>(f.q_w + d), wc = *reinterpret_cast<const float2*>(f.q_w + d + 8);
+                v[h][ks][0] = v[h][ks][0] * scale * wa.x; v[h][ks][1] = v[h][ks][1] * scale * wa.y;
+                v[h][ks][2] = v[h][ks][2] * scale * wc.x; v[h][ks][3] = v[h][ks][3] * scale * wc.y;
+            }
+        }
+    }
+    if (f.cos_t) {
+        const float* cs = f.cos_t + (size_t)b * HALF;
+        const float* sn = f.sin_t + (size_t)b * HALF;
+#pragma unroll
+        for (int ks = 0; ks < KS / 2; ++ks) {
+            const int d = 16 * ks + 2 * t;
+            const float2 ca = *reinterpret_cast<const float2*>(cs + d), cc = *reinterpret_cast<const float2*>(cs + d + 8);
+            const float2 sa = *reinterpret_cast<const float2*>(sn + d), sc = *reinterpret_cast<const float2*>(sn + d + 8);
+            const float c4[4] = {ca.x, ca.y, cc.x, cc.y}, s4[4] = {sa.x, sa.y, sc.x, sc.y};
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float lo = v[h][ks][j], hi = v[h][ks + KS / 2][j];
+                    v[h][ks][j] = lo * c4[j] - hi * s4[j];
+                    v[h][ks + KS / 2][j] = lo * s4[j] + hi * c4[j];
+                }
+        }
+    }
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+        qf[ks][0] = pack_bf16(v[0][ks][0], v[0][ks][1]);
+        qf[ks][1] = pack_bf16(v[1][ks][0], v[1][ks][1]);
+        qf[ks][2] = pack_bf16(v[0][ks][2], v[0][ks][3]);
+        qf[ks][3] = pack_bf16(v[1][ks][2], v[1][ks][3]);
+    }
+}
+
+// The new token's key (is_k: with norm and rotation) or value, as bfloat16: lane L gets the values d0 = L * HD / 32 ...
+template <int HD>
+__device__ __forceinline__ void fused_new_row(const FusedQKV& f, const float* src, bool is_k, int b, int lane, float* y) {
+    constexpr int PER = HD / 32, HALF = HD / 2;
+    const int d0 = lane * PER;
+#pragma unroll
+    for (int e = 0; e < PER; ++e) y[e] = src[d0 + e];
+    if (!is_k) return;
+    if (f.k_w) {
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < PER; ++e) ss += y[e] * y[e];
+        ss = warp_sum(ss);
+        const float scale = rsqrtf(ss / (float)HD + f.eps);
+#pragma unroll
+        for (int e = 0; e < PER; ++e) y[e] = y[e] * scale * f.k_w[d0 + e];
+    }
+    if (f.cos_t) {
+        const int dr = d0 % HALF;                         // lanes 16.. hold the second half: their partners are lanes 0..15
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+            const float other = __shfl_xor_sync(0xffffffffu, y[e], 16);
+            const float c = f.cos_t[(size_t)b * HALF + dr + e], sn = f.sin_t[(size_t)b * HALF + dr + e];
+            y[e] = lane < 16 ? y[e] * c - other * sn : other * sn + y[e] * c;
+        }
+    }
+}
+
+template <int HD, bool FUSED>
 __global__ void __launch_bounds__(32)
-attn_mma_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+attn_mma_decode_kernel(const FusedQKV fused, const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                        const int* __restrict__ page_table, const int* __restrict__ seq_len, float* __restrict__ part_acc,
                        float* __restrict__ part_m, float* __restrict__ part_l, bf16* __restrict__ out, int Hq, int Hkv,
                        int table_width, float scale, int window, int runs_target, int run_pages_max, int max_runs, int Gc,
@@ -312,27 +416,12 @@ attn_mma_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     bf16* my_tiles = reinterpret_cast<bf16*>(smem_raw);                         // K then V
 
-    int row_pos[2];
-    const bf16* qrow[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const int r = g + 8 * h, head_in = chunk * Gc + r;
-        const bool ok = r < Gc && head_in < G;
-        row_pos[h] = ok ? len - 1 : -1;
-        qrow[h] = ok ? q + ((size_t)b * Hq + kvh * G + head_in) * HD : nullptr;
-    }
-    uint32_t qf[HD / 16][4];
-    load_q_frags<HD>(qf, qrow[0], qrow[1], lane);
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f}, o[HD / 8][4];
-#pragma unroll
-    for (int d = 0; d < HD / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
-
     const int tok_begin = run * split_tokens, tok_end = min(len, tok_begin + split_tokens);
     const int* pages = page_table + (size_t)b * table_width;
     const float sl2 = scale * 1.4426950408889634f;
     // The run's pages one after the other, through one K and one V buffer: as soon as the scores of a page are formed
     // its K buffer takes the next page's K, and after O += P V its V buffer the next page's V, so that the copies of
-    // page i + 1 run under the arithmetic of page i.
+    // page i + 1 run under the arithmetic of page i.  The first page's copies go out before anything else.
     bf16* k_tile = my_tiles;
     bf16* v_tile = my_tiles + AM_TILE * HD;
     int base_tok = max(tok_begin, (k_lo / AM_TILE) * AM_TILE);                 // pages wholly before the window are skipped
@@ -344,6 +433,52 @@ attn_mma_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
         load_tile<HD>(v_tile, v_pool + src, n_valid, lane, 32);
         cp_async_commit();
     }
+
+    int row_pos[2];
+    uint32_t qf[HD / 16][4];
+    {
+        const int n_all = Hq + 2 * Hkv;
+        const bf16* qrow[2];
+        const float* frow[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = g + 8 * h, head_in = chunk * Gc + r;
+            const bool ok = r < Gc && head_in < G;
+            row_pos[h] = ok ? len - 1 : -1;
+            qrow[h] = ok && !FUSED ? q + ((size_t)b * Hq + kvh * G + head_in) * HD : nullptr;
+            frow[h] = ok && FUSED ? fused.qkv + ((size_t)b * n_all + kvh * G + head_in) * HD : nullptr;
+        }
+        if (FUSED) fused_q_frags<HD>(qf, fused, frow[0], frow[1], b, lane);
+        else load_q_frags<HD>(qf, qrow[0], qrow[1], lane);
+    }
+    // FUSED: the new token's key and value, if its place lies in this run: into the cache (one block per key/value head
+    // writes) and, below, into the shared tiles of its page
+    const int new_pos = len - 1;
+    const bool has_new = FUSED && fused.store_kv && new_pos >= tok_begin && new_pos < tok_end;
+    float new_k[HD / 32], new_v[HD / 32];
+    if (has_new) {
+        const int n_all = Hq + 2 * Hkv;
+        fused_new_row<HD>(fused, fused.qkv + ((size_t)b * n_all + Hq + kvh) * HD, true, b, lane, new_k);
+        fused_new_row<HD>(fused, fused.qkv + ((size_t)b * n_all + Hq + Hkv + kvh) * HD, false, b, lane, new_v);
+        if (chunk == 0) {
+            const size_t at = (((size_t)pages[new_pos / AM_TILE] * Hkv + kvh) * AM_TILE + new_pos % AM_TILE) * HD + lane * (HD / 32);
+#pragma unroll
+            for (int e = 0; e < HD / 32; e += 2) {
+                *reinterpret_cast<uint32_t*>(fused.k_pool + at + e) = pack_bf16(new_k[e], new_k[e + 1]);
+                *reinterpret_cast<uint32_t*>(fused.v_pool + at + e) = pack_bf16(new_v[e], new_v[e + 1]);
+            }
+        }
+    }
+    // the new row's place in a shared tile (rows of HD values, 16-byte pieces XOR-swizzled by the row)
+    auto patch = [&](bf16* tile, const float* y) {
+        const int row = new_pos % AM_TILE, d0 = lane * (HD / 32);
+        bf16* dst = tile + row * HD + (((d0 >> 3) ^ (row & 7)) << 3) + (d0 & 7);
+#pragma unroll
+        for (int e = 0; e < HD / 32; e += 2) *reinterpret_cast<uint32_t*>(dst + e) = pack_bf16(y[e], y[e + 1]);
+    };
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f}, o[HD / 8][4];
+#pragma unroll
+    for (int d = 0; d < HD / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
     for (; base_tok < tok_end; base_tok += AM_TILE) {
         const int next_tok = base_tok + AM_TILE;
         const bool more = next_tok < tok_end;
@@ -356,6 +491,8 @@ attn_mma_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
         float s[AM_TILE / 8][4], sbase[2];
         cp_async_wait<1>();                                                     // this page's K has landed (its V may not have)
         __syncwarp();
+        const bool new_here = has_new && new_pos >= base_tok && new_pos < base_tok + AM_TILE;
+        if (new_here) { patch(k_tile, new_k); __syncwarp(); }
         tile_scores<HD, AM_TILE>(qf, k_tile, base_tok, row_pos, len, window, sl2, m, l, o, lane, 0, s, sbase);
         __syncwarp();                                                           // every lane is done reading K
         if (more) {
@@ -366,6 +503,7 @@ attn_mma_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
             cp_async_wait<0>();
         }
         __syncwarp();
+        if (new_here) { patch(v_tile, new_v); __syncwarp(); }
         tile_pv<HD, AM_TILE>(v_tile, s, sbase, sl2, l, o, lane, 0);
         __syncwarp();                                                           // every lane is done reading V
         if (more) {
@@ -504,19 +642,19 @@ extern "C" int qwb_attn_mma_prefill(const void* q, const void* k_pool, const voi
     return launch_prefill<128>(q, k_pool, v_pool, page_table, cu_seqlens, pos0, out, B, max_new, Hq, Hkv, table_width, scale, window, stream);
 }
 
-template <int HD>
-static int launch_decode(const void* q, const void* k_pool, const void* v_pool, const int* page_table, const int* seq_len,
-                         float* scratch, void* out, int B, int Hq, int Hkv, int table_width, float scale, int window,
-                         int runs_target, int run_pages_max, int max_runs, cudaStream_t stream) {
+template <int HD, bool FUSED>
+static int launch_decode(const FusedQKV& fused, const void* q, const void* k_pool, const void* v_pool, const int* page_table,
+                         const int* seq_len, float* scratch, void* out, int B, int Hq, int Hkv, int table_width, float scale,
+                         int window, int runs_target, int run_pages_max, int max_runs, cudaStream_t stream) {
     const int G = Hq / Hkv, Gc = group_chunk(G), chunks = (G + Gc - 1) / Gc;
     const size_t smem = (size_t)2 * AM_TILE * HD * sizeof(bf16);
-    cudaError_t e = cudaFuncSetAttribute(attn_mma_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_mma_decode_kernel<HD, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "attn_mma_decode: %s", cudaGetErrorString(e));
     float* part_acc = scratch;
     float* part_m = scratch + (size_t)B * Hq * max_runs * HD;
     float* part_l = part_m + (size_t)B * Hq * max_runs;
     dim3 grid(Hkv * chunks, B, max_runs);
-    qwb_launch(attn_mma_decode_kernel<HD>, grid, 32, smem, stream, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
+    qwb_launch(attn_mma_decode_kernel<HD, FUSED>, grid, 32, smem, stream, fused, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
         page_table, seq_len, part_acc, part_m, part_l, (bf16*)out, Hq, Hkv, table_width, scale, window, runs_target, run_pages_max,
         max_runs, Gc, chunks);
     if (int rc = qwb_check_launch("attn_mma_decode")) return rc;
@@ -535,6 +673,18 @@ extern "C" int qwb_attn_mma_decode_runs(int max_len, int runs_target, int run_pa
     return max_runs_for(max_len, runs_target, run_pages_max);
 }
 
+static int check_decode(int B, int Hq, int Hkv, int hd, int page_size, int runs_target, int run_pages_max, int max_len,
+                        const float* scratch, int* max_runs) {
+    if (int rc = check_sizes("attn_mma_decode", Hq, Hkv, hd, page_size, B)) return rc;
+    if (runs_target <= 0 || run_pages_max <= 0 || max_len <= 0)
+        return qwb_fail(QWB_ERR_ARG, "attn_mma_decode: %d runs of up to %d pages for up to %d keys", runs_target, run_pages_max, max_len);
+    *max_runs = max_runs_for(max_len, runs_target, run_pages_max);
+    if (*max_runs > 65535) return qwb_fail(QWB_ERR_ARG, "attn_mma_decode: %d runs of keys; at most 65535", *max_runs);
+    if ((size_t)*max_runs * sizeof(float) > 40 * 1024) return qwb_fail(QWB_ERR_ARG, "attn_mma_decode: %d runs of keys are too many to combine", *max_runs);
+    if (*max_runs > 1 && !scratch) return qwb_fail(QWB_ERR_ARG, "attn_mma_decode: %d runs need scratch memory", *max_runs);
+    return 0;
+}
+
 // bfloat16 only.  Arguments as qwb_attn_decode, but for how the keys are cut into runs: a sequence of p pages is cut into
 // runs of clamp(ceil(p / runs_target), 1, run_pages_max) pages (runs_target 1 gives runs of exactly run_pages_max pages);
 // max_len bounds every entry of seq_len.  scratch: B * Hq * runs(max_len) * (hd + 2) floats, unused with a single run.
@@ -543,13 +693,28 @@ extern "C" int qwb_attn_mma_decode(const void* q, const void* k_pool, const void
                                    int table_width, float scale, int window, int runs_target, int run_pages_max, int max_len,
                                    cudaStream_t stream) {
     if (B <= 0) return 0;
-    if (int rc = check_sizes("attn_mma_decode", Hq, Hkv, hd, page_size, B)) return rc;
-    if (runs_target <= 0 || run_pages_max <= 0 || max_len <= 0)
-        return qwb_fail(QWB_ERR_ARG, "attn_mma_decode: %d runs of up to %d pages for up to %d keys", runs_target, run_pages_max, max_len);
-    const int max_runs = max_runs_for(max_len, runs_target, run_pages_max);
-    if (max_runs > 65535) return qwb_fail(QWB_ERR_ARG, "attn_mma_decode: %d runs of keys; at most 65535", max_runs);
-    if ((size_t)max_runs * sizeof(float) > 40 * 1024) return qwb_fail(QWB_ERR_ARG, "attn_mma_decode: %d runs of keys are too many to combine", max_runs);
-    if (max_runs > 1 && !scratch) return qwb_fail(QWB_ERR_ARG, "attn_mma_decode: %d runs need scratch memory", max_runs);
-    if (hd == 64) return launch_decode<64>(q, k_pool, v_pool, page_table, seq_len, scratch, out, B, Hq, Hkv, table_width, scale, window, runs_target, run_pages_max, max_runs, stream);
-    return launch_decode<128>(q, k_pool, v_pool, page_table, seq_len, scratch, out, B, Hq, Hkv, table_width, scale, window, runs_target, run_pages_max, max_runs, stream);
+    int max_runs = 0;
+    if (int rc = check_decode(B, Hq, Hkv, hd, page_size, runs_target, run_pages_max, max_len, scratch, &max_runs)) return rc;
+    FusedQKV none = {};
+    if (hd == 64) return launch_decode<64, false>(none, q, k_pool, v_pool, page_table, seq_len, scratch, out, B, Hq, Hkv, table_width, scale, window, runs_target, run_pages_max, max_runs, stream);
+    return launch_decode<128, false>(none, q, k_pool, v_pool, page_table, seq_len, scratch, out, B, Hq, Hkv, table_width, scale, window, runs_target, run_pages_max, max_runs, stream);
+}
+
+// The same with the step's q, k and v taken from the q/k/v projection's 32-bit output qkv [B, (Hq + 2 Hkv) * hd]: per-head
+// norm of q and k (weights [hd], or null), rotation of all hd values by cos/sin [B, hd / 2] (or null), and, with store_kv,
+// the new key and value written into the cache at each sequence's position seq_len - 1, all inside the attention kernel.
+extern "C" int qwb_attn_mma_decode_fused(const float* qkv, const float* q_weight, const float* k_weight, const float* cos_t,
+                                         const float* sin_t, float eps, int store_kv, void* k_pool, void* v_pool,
+                                         const int* page_table, const int* seq_len, float* scratch, void* out, int B, int Hq,
+                                         int Hkv, int hd, int page_size, int table_width, float scale, int window,
+                                         int runs_target, int run_pages_max, int max_len, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    int max_runs = 0;
+    if (int rc = check_decode(B, Hq, Hkv, hd, page_size, runs_target, run_pages_max, max_len, scratch, &max_runs)) return rc;
+    if (!qkv || (uintptr_t)qkv % 8 || (q_weight && (uintptr_t)q_weight % 8) || (cos_t && ((uintptr_t)cos_t % 8 || (uintptr_t)sin_t % 8)))
+        return qwb_fail(QWB_ERR_ARG, "attn_mma_decode_fused: qkv, norm weights and cos/sin must be 8-byte aligned");
+    if ((cos_t == nullptr) != (sin_t == nullptr)) return qwb_fail(QWB_ERR_ARG, "attn_mma_decode_fused: cos and sin come together");
+    FusedQKV f = {qkv, q_weight, k_weight, cos_t, sin_t, (bf16*)k_pool, (bf16*)v_pool, eps, store_kv};
+    if (hd == 64) return launch_decode<64, true>(f, nullptr, k_pool, v_pool, page_table, seq_len, scratch, out, B, Hq, Hkv, table_width, scale, window, runs_target, run_pages_max, max_runs, stream);
+    return launch_decode<128, true>(f, nullptr, k_pool, v_pool, page_table, seq_len, scratch, out, B, Hq, Hkv, table_width, scale, window, runs_target, run_pages_max, max_runs, stream);
 }

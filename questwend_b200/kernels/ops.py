@@ -293,6 +293,53 @@ def attn_decode(q, k_pool, v_pool, page_table, seq_len, scale: float, max_len: i
     return out
 
 
+def attn_decode_fused(qkv: torch.Tensor, q_weight, k_weight, cos, sin, eps: float, k_pool, v_pool, page_table, seq_len,
+                      scale: float, max_len: int, n_heads: int, n_kv_heads: int, head_dim: int, window: int = 0,
+                      store_kv: bool = True, scratch: torch.Tensor | None = None,
+                      runs_target: int = MMA_RUNS_TARGET, run_pages_max: int = MMA_RUN_PAGES_MAX) -> torch.Tensor:
+    """``qk_norm_rope_store`` and ``attn_decode`` in one kernel, for a step of one token per sequence on the tensor-core
+    path (bfloat16 cache, head size 64 or 128, rotation over the whole head or none): ``qkv`` float32
+    [B, (Hq + 2 Hkv) * hd] is the q/k/v projection's output; the new keys and values are written into the cache at
+    position ``seq_len - 1`` (unless ``store_kv`` is False).  Returns [B, Hq * hd] bfloat16."""
+    _need(qkv, "qkv", torch.float32, 2)
+    _need(k_pool, "k_pool", torch.bfloat16, 4)
+    _need(v_pool, "v_pool", torch.bfloat16, 4)
+    _need(page_table, "page_table", torch.int32, 2)
+    _need(seq_len, "seq_len", torch.int32, 1)
+    B = qkv.shape[0]
+    if qkv.shape[1] != (n_heads + 2 * n_kv_heads) * head_dim or seq_len.numel() != B or page_table.shape[0] != B:
+        raise KernelError(f"attn_decode_fused: qkv {tuple(qkv.shape)}, {seq_len.numel()} lengths, page table "
+                          f"{tuple(page_table.shape)} do not fit {n_heads}+2x{n_kv_heads} heads of {head_dim}")
+    if not mma_attention_fits(k_pool.dtype, head_dim, k_pool.shape[2]):
+        raise KernelError(f"attn_decode_fused: head size {head_dim} with pages of {k_pool.shape[2]} is not taken")
+    if tuple(k_pool.shape[1:]) != (n_kv_heads, k_pool.shape[2], head_dim) or v_pool.shape != k_pool.shape:
+        raise KernelError(f"attn_decode_fused: cache pool {tuple(k_pool.shape)} does not fit {n_kv_heads} heads of {head_dim}")
+    for name, t in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if t is not None:
+            _need(t, name, torch.float32, 1)
+            if t.numel() != head_dim:
+                raise KernelError(f"attn_decode_fused: {name} has {t.numel()} entries for heads of {head_dim}")
+    if (q_weight is None) != (k_weight is None):
+        raise KernelError("attn_decode_fused: the norm weights of q and k come together")
+    if cos is not None:
+        _need(cos, "cos", torch.float32, 2)
+        _need(sin, "sin", torch.float32, 2)
+        if tuple(cos.shape) != (B, head_dim // 2) or sin.shape != cos.shape:
+            raise KernelError(f"attn_decode_fused: cos/sin {tuple(cos.shape)} do not fit {B} tokens and a rotation "
+                              f"over all {head_dim} values")
+    max_runs = max(1, mma_decode_runs(max_len, runs_target, run_pages_max))
+    need = attn_decode_scratch_floats(B, n_heads, head_dim, max_runs) if max_runs > 1 else 0
+    if need and (scratch is None or scratch.numel() < need):
+        scratch = torch.empty(need, dtype=torch.float32, device=qkv.device)
+    out = torch.empty((B, n_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    _call("attention_mma", "qwb_attn_mma_decode_fused", _ptr(qkv), _ptr(q_weight), _ptr(k_weight), _ptr(cos), _ptr(sin),
+          _f(eps), _i(1 if store_kv else 0), _ptr(k_pool), _ptr(v_pool), _ptr(page_table), _ptr(seq_len), _ptr(scratch),
+          _ptr(out), _i(B), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(k_pool.shape[2]), _i(page_table.shape[1]),
+          _f(scale), _i(window), _i(runs_target), _i(run_pages_max), _i(max_len), _stream(),
+          kernels=2 if max_runs > 1 else 1)
+    return out
+
+
 # ----------------------------------------------------------------------------- matrix products
 SMALL_M = 16            # at most this many rows go to the weight-streaming kernel
 

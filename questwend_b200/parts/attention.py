@@ -14,6 +14,10 @@ from .base import KVSpec, Mixer
 from .linear import kernel_modules as linear_modules, linear
 from .registry import register_mixer
 
+FUSED_DECODE_MAX_BATCH = ops.STREAM_M   # up to here a kernel less per layer pays (3-4 % of a small model's step); with more
+                                        # sequences every attention block repeating the work on q costs more than it saves.
+                                        # (The same bound as the few-rows products: beyond it a step's arithmetic differs
+                                        # in its last bits anyway.)
 DECODE_SPLIT_TOKENS = 256     # keys per run of the plain decode kernel; fixed, so results do not depend on the batch
                               # (the tensor-core kernel cuts by each sequence's own length: ops.attn_decode)
 
@@ -85,15 +89,23 @@ class GroupedQueryAttention(Mixer):
         if self.position is not None:
             cos, sin = self.position.prepare(ctx)
         table = ctx.page_tables[cache.group_id]
-        q = ops.qk_norm_rope_store(qkv, self.q_norm_w, self.k_norm_w, cos, sin, ctx.tok_seq, ctx.tok_pos, table,
-                                   cache.k_pool, cache.v_pool, self.n_heads, self.n_kv_heads, self.head_dim,
-                                   self.rotary_dim, self.eps, store_kv=cache.writable)
-        if ctx.single_token:
-            att = ops.attn_decode(q, cache.k_pool, cache.v_pool, table, ctx.seq_len, self.scale, ctx.max_len,
-                                  window=self.window, split_tokens=DECODE_SPLIT_TOKENS)
+        if (ctx.single_token and ctx.n_seqs <= FUSED_DECODE_MAX_BATCH and self.rotary_dim in (0, self.head_dim)
+                and ops.mma_attention_fits(cache.k_pool.dtype, self.head_dim, cache.k_pool.shape[2])):
+            # one token for each of a few sequences on the tensor-core path: norm, rotation and cache write happen inside
+            # the attention kernel
+            att = ops.attn_decode_fused(qkv, self.q_norm_w, self.k_norm_w, cos, sin, self.eps, cache.k_pool, cache.v_pool,
+                                        table, ctx.seq_len, self.scale, ctx.max_len, self.n_heads, self.n_kv_heads,
+                                        self.head_dim, window=self.window, store_kv=cache.writable)
         else:
-            att = ops.attn_prefill(q, cache.k_pool, cache.v_pool, table, ctx.cu_seqlens, ctx.pos0, ctx.max_new,
-                                   self.scale, window=self.window)
+            q = ops.qk_norm_rope_store(qkv, self.q_norm_w, self.k_norm_w, cos, sin, ctx.tok_seq, ctx.tok_pos, table,
+                                       cache.k_pool, cache.v_pool, self.n_heads, self.n_kv_heads, self.head_dim,
+                                       self.rotary_dim, self.eps, store_kv=cache.writable)
+            if ctx.single_token:
+                att = ops.attn_decode(q, cache.k_pool, cache.v_pool, table, ctx.seq_len, self.scale, ctx.max_len,
+                                      window=self.window, split_tokens=DECODE_SPLIT_TOKENS)
+            else:
+                att = ops.attn_prefill(q, cache.k_pool, cache.v_pool, table, ctx.cu_seqlens, ctx.pos0, ctx.max_new,
+                                       self.scale, window=self.window)
         if residual is not None:
             linear(att, self.w_o, add_to=residual)      # the residual sum, in the product's epilogue
             return None

@@ -279,6 +279,44 @@ def _attn_decode_case(dtype, Hq, Hkv, hd, window, split, page, impl, how=None):
     assert torch.equal(alone[0], out[3])
 
 
+@pytest.mark.parametrize("Hq,Hkv,hd", [(8, 2, 128), (4, 4, 64), (32, 1, 128), (6, 2, 64)])
+@pytest.mark.parametrize("norm,rotate,window", [(True, True, 0), (False, True, 0), (True, False, 90), (False, False, 0)])
+def test_attn_decode_with_norm_rotation_and_cache_write_inside(Hq, Hkv, hd, norm, rotate, window):
+    """The kernel that does the q/k norm, the rotation and the cache write itself against the two kernels it replaces:
+    the same attention output, and the same new keys and values in the cache (also where the new token opens a page)."""
+    lens = [1, 64, 65, 300, 129, 700, 128]
+    B = len(lens)
+    rng = np.random.default_rng(Hq + hd)
+    _, k, v = (rounded(a, torch.bfloat16) for a in make_qkv(lens, Hq, Hkv, hd, hd + Hq))
+    k_pool, table = paged(k, Hkv, hd, torch.bfloat16, seed=4)
+    v_pool, _ = paged(v, Hkv, hd, torch.bfloat16, seed=4)
+    qkv = torch.from_numpy(rng.normal(size=(B, (Hq + 2 * Hkv) * hd)).astype(np.float32)).to(DEV)
+    qw = torch.from_numpy(1 + 0.1 * rng.normal(size=hd).astype(np.float32)).to(DEV) if norm else None
+    kw = torch.from_numpy(1 + 0.1 * rng.normal(size=hd).astype(np.float32)).to(DEV) if norm else None
+    seq_len = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    tok_seq = torch.arange(B, dtype=torch.int32, device=DEV)
+    tok_pos = (seq_len - 1).contiguous()
+    cos = sin = None
+    if rotate:
+        inv = torch.tensor(1e4 ** (-2.0 * np.arange(hd // 2) / hd), dtype=torch.float64, device=DEV)
+        cos, sin = ops.rope_table(tok_pos, inv)
+    scale = 1 / math.sqrt(hd)
+    k1, v1 = k_pool.clone(), v_pool.clone()
+    q = ops.qk_norm_rope_store(qkv, qw, kw, cos, sin, tok_seq, tok_pos, table, k1, v1, Hq, Hkv, hd, hd if rotate else 0, 1e-5)
+    want = ops.attn_decode(q, k1, v1, table, seq_len, scale, max(lens), window=window)
+    k2, v2 = k_pool.clone(), v_pool.clone()
+    got = ops.attn_decode_fused(qkv, qw, kw, cos, sin, 1e-5, k2, v2, table, seq_len, scale, max(lens), Hq, Hkv, hd, window=window)
+    close(got, f64(want), torch.bfloat16)
+    assert (f64(k2) - f64(k1)).__abs__().max() <= 2.0 ** -7 * np.abs(f64(k1)[f64(k1) < 1e3]).max()     # a bfloat16 step at most
+    assert torch.equal(v2, v1)
+    # the cache of another layer's run is read, not written
+    k3, v3 = k1.clone(), v1.clone()
+    again = ops.attn_decode_fused(qkv, qw, kw, cos, sin, 1e-5, k3, v3, table, seq_len, scale, max(lens), Hq, Hkv, hd,
+                                  window=window, store_kv=False)
+    assert torch.equal(k3, k1) and torch.equal(v3, v1)
+    close(again, f64(want), torch.bfloat16)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_one_far_key_among_hundreds(dtype):
     """Random scores hide a key that is read from the wrong place: make one far key's score stand out,

@@ -75,7 +75,8 @@ def bench_gemm(M: int, N: int, K: int, impl: str, iters: int, dtype=torch.bfloat
             "GBps": nbytes / us / 1e3, "TFLOPs": 2.0 * M * N * K / us / 1e6}
 
 
-def bench_attn_decode(B, ctx, Hq, Hkv, hd, iters, dtype=torch.bfloat16, split=0, runs_target=0, run_pages_max=0) -> dict:
+def bench_attn_decode(B, ctx, Hq, Hkv, hd, iters, dtype=torch.bfloat16, split=0, runs_target=0, run_pages_max=0,
+                      fused=False) -> dict:
     page = ops.PAGE_SIZE
     pages_per = math.ceil(ctx / page)
     per_copy = B * pages_per
@@ -98,9 +99,17 @@ def bench_attn_decode(B, ctx, Hq, Hkv, hd, iters, dtype=torch.bfloat16, split=0,
         if run_pages_max:
             how["run_pages_max"] = run_pages_max
     fn = lambda i: ops.attn_decode(q, k_pool, v_pool, tables[i], seq_len, 1 / math.sqrt(hd), ctx, **how)
+    if fused:       # the kernel that also norms and rotates q and k and writes the new key and value (what a step of few sequences runs)
+        how.pop("split_tokens", None)
+        qkv = torch.randn(B, (Hq + 2 * Hkv) * hd, device="cuda")
+        w = torch.ones(hd, device="cuda")
+        inv = torch.tensor([1e6 ** (-2.0 * i / hd) for i in range(hd // 2)], dtype=torch.float64, device="cuda")
+        cos, sin = ops.rope_table(seq_len - 1, inv)
+        fn = lambda i: ops.attn_decode_fused(qkv, w, w, cos, sin, 1e-6, k_pool, v_pool, tables[i], seq_len, 1 / math.sqrt(hd), ctx,
+                                             Hq, Hkv, hd, **how)
     us = _time(fn, copies, iters)
     nbytes = 2 * B * ctx * Hkv * hd * elem
-    return {"kernel": "attn_decode", "B": B, "ctx": ctx, "Hq": Hq, "Hkv": Hkv, "hd": hd, "us": us, "bytes": nbytes,
+    return {"kernel": "attn_decode_fused" if fused else "attn_decode", "B": B, "ctx": ctx, "Hq": Hq, "Hkv": Hkv, "hd": hd, "us": us, "bytes": nbytes,
             "GBps": nbytes / us / 1e3}
 
 
@@ -149,6 +158,7 @@ def main() -> int:
     ap.add_argument("--split", type=int, default=0, help="keys per run of the decode attention kernel (0: its own choice)")
     ap.add_argument("--runs-target", type=int, default=0, help="tensor-core decode attention: about this many runs a sequence")
     ap.add_argument("--run-pages-max", type=int, default=0, help="tensor-core decode attention: at most this many pages a run")
+    ap.add_argument("--fused", action="store_true", help="decode attention with the q/k norm, rotation and cache write inside")
     args = ap.parse_args()
     dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
     if args.what == "gemm":
@@ -161,7 +171,7 @@ def main() -> int:
             print(json.dumps(r))
     elif args.what == "attn_decode":
         print(json.dumps(bench_attn_decode(args.batch, args.ctx, args.heads, args.kv_heads, args.head_dim, args.iters, dtype, args.split,
-                                           args.runs_target, args.run_pages_max)))
+                                           args.runs_target, args.run_pages_max, args.fused)))
     elif args.what == "attn_prefill":
         print(json.dumps(bench_attn_prefill(args.tokens, args.heads, args.kv_heads, args.head_dim, args.iters, dtype)))
     else:

@@ -1,9 +1,9 @@
 """Matrix products y = x W^T with 32-bit sums and a 32-bit result.
 
 Few rows (a decode step) go to the hand-written weight-streaming kernels: bfloat16
-with up to 16 rows to the tensor-core one (mma.sync), which also folds the residual
-sum or the gated SiLU into its epilogue; float32 (and odd inner sizes) with up to 16
-rows to the plain one.  More rows go to the library product, as in the reference,
+with up to 8 rows (up to 16 for matrices of at most 16 M weights) to the tensor-core
+one (mma.sync), which also folds the residual sum or the gated SiLU into its
+epilogue; float32 (and odd inner sizes) with few rows to the plain one.  More rows go to the library product, as in the reference,
 whose dispatcher sends up to 16 rows to its own kernels and the rest to cuBLAS
 (ggml-cuda/ggml-cuda.cu:1812-1866); the residual sum rides in the library call
 (beta = 1).  The exception is the gate/up projection of many bfloat16 rows: the
@@ -33,6 +33,15 @@ def require_true_fp32() -> None:
     torch.set_float32_matmul_precision("highest")
 
 
+STREAM_MAX_ROWS = 8         # up to here the own weight-streaming product is always the fastest.  With 9 to 16 rows (its
+STREAM_WIDE_MAX_WEIGHT = 1 << 24   # two-tile form) it still is for matrices of up to 16 M weights (the 0.6B model's, an
+                            # 8B model's o projection); beyond, the library is: at 16 rows the down projection of Qwen3-8B
+                            # (50 M weights) takes 30.7 us against 21.2 us
+
+
+def _stream_rows(M: int, weight: torch.Tensor) -> bool:
+    return M <= STREAM_MAX_ROWS or (M <= ops.STREAM_M and weight.numel() <= STREAM_WIDE_MAX_WEIGHT)
+
 TC_SWIGLU_MIN_ROWS = 512    # from here on the tcgen05 gate/up product with the SiLU in its epilogue beats library + kernel
 
 
@@ -46,11 +55,12 @@ def linear(x: torch.Tensor, weight: torch.Tensor, add_to: torch.Tensor | None = 
     """x [M, K] (the weight's dtype) times weight [N, K] transposed -> float32 [M, N].
     With ``add_to`` (float32 [M, N]) the product is added onto it in place and it is returned."""
     M, K = x.shape
-    if weight.dtype == torch.bfloat16 and M <= ops.STREAM_M and K % 8 == 0:
+    bf16 = weight.dtype == torch.bfloat16
+    if bf16 and _stream_rows(M, weight) and K % 8 == 0:
         return ops.gemm_stream(x, weight, residual=add_to)
-    if M <= ops.SMALL_M:
+    if M <= (STREAM_MAX_ROWS if bf16 else ops.SMALL_M):       # float32; bfloat16 rows whose length is no multiple of 8
         return ops.gemm_small(x, weight, residual=add_to)
-    if weight.dtype == torch.bfloat16:
+    if bf16:
         if add_to is not None:
             return torch.addmm(add_to, x, weight.t(), out_dtype=torch.float32, out=add_to)
         return torch.mm(x, weight.t(), out_dtype=torch.float32)
@@ -65,7 +75,7 @@ def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor, out_dtype: torc
     first; ``ops.GATE_UP_GROUP``: gate and up rows interleaved in groups of that many features, which lets the products
     with a fused epilogue find a feature's gate and up in one thread."""
     if interleave == ops.GATE_UP_GROUP and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16:
-        if x.shape[0] <= ops.STREAM_M and x.shape[1] % 8 == 0:
+        if _stream_rows(x.shape[0], weight_gate_up) and x.shape[1] % 8 == 0:
             return ops.gemm_stream_swiglu(x, weight_gate_up)
         if x.shape[0] >= TC_SWIGLU_MIN_ROWS and x.shape[1] % 8 == 0:
             return ops.gemm_tc(x, weight_gate_up, epilogue="swiglu", tile_n=256)

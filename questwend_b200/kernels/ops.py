@@ -30,7 +30,13 @@ def _dt(t: torch.dtype) -> int:
     raise KernelError(f"kernels take float32 or bfloat16, got {t}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> ctypes.c_void_p:
+    """The current stream of the current device (also inside a graph capture, which runs on a stream of its own)."""
+    if _raw_stream is not None:                      # the handle itself: a tenth of the cost of making a Stream object
+        return ctypes.c_void_p(_raw_stream(torch.cuda.current_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -52,12 +58,18 @@ def _need(t: torch.Tensor, name: str, dtype=None, ndim=None):
 LAUNCHES = [0]          # kernels of this library launched so far (through these entry points)
 
 
+_FUNCTIONS: dict = {}    # (module, name) -> (library, its function), looked up once
+
+
 def _call(module: str, fn: str, *args, kernels: int = 1):
-    lib = load_module(module)
-    rc = getattr(lib, fn)(*args)
+    entry = _FUNCTIONS.get((module, fn))
+    if entry is None:
+        lib = load_module(module)
+        entry = _FUNCTIONS[module, fn] = (lib, getattr(lib, fn))
+    rc = entry[1](*args)
     LAUNCHES[0] += kernels
     if rc != 0:
-        raise KernelError(lib.qwb_last_error().decode("utf-8", "replace") or f"{fn} failed with code {rc}")
+        raise KernelError(entry[0].qwb_last_error().decode("utf-8", "replace") or f"{fn} failed with code {rc}")
 
 
 _i = ctypes.c_int

@@ -137,19 +137,29 @@ gemm_stream_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const
     }
 }
 
+// u, w: blocks of 32 k that a warp keeps in flight, and warps per block of threads; 0, 0: chosen here.
 template <bool SWIGLU>
 static int launch_stream(const bf16* xp, const bf16* wp, const float* residual, float* y, bf16* act, int M, int N, int K,
-                         cudaStream_t stream) {
+                         int u, int w, cudaStream_t stream) {
     const int grid = (N + GS_ROWS - 1) / GS_ROWS;
     // How deep each warp prefetches (U blocks of 32 k) and how many warps split K, by what measured best at the sizes of
     // a Qwen3-8B decode step: long rows want deep prefetch; short rows with few blocks want more warps; else shallow.
-#define GS_GO(NT, U, WARPS) \
-    qwb_launch_early(gemm_stream_kernel<NT, U, WARPS, SWIGLU>, grid, WARPS * 32, 0, stream, xp, wp, residual, y, act, M, N, K)
-#define GS_PICK(NT)                                      \
-    do {                                                 \
-        if (K >= 8192) GS_GO(NT, 8, 8);                  \
-        else if (N <= 4096) GS_GO(NT, 2, 16);            \
-        else GS_GO(NT, 2, 8);                            \
+    // (Other shapes have other optima, and for some the library wins: a caller that measures passes its choice.)
+    if (u == 0 && w == 0) {
+        if (K >= 8192) { u = 8; w = 8; }
+        else if (N <= 4096) { u = 2; w = 16; }
+        else { u = 2; w = 8; }
+    }
+#define GS_GO(NT, U, WARPS) qwb_launch_early(gemm_stream_kernel<NT, U, WARPS, SWIGLU>, grid, WARPS * 32, 0, stream, xp, wp, residual, y, act, M, N, K)
+#define GS_PICK(NT)                                                  \
+    do {                                                             \
+        if (u == 2 && w == 8) GS_GO(NT, 2, 8);                       \
+        else if (u == 4 && w == 8) GS_GO(NT, 4, 8);                  \
+        else if (u == 8 && w == 8) GS_GO(NT, 8, 8);                  \
+        else if (u == 2 && w == 16) GS_GO(NT, 2, 16);                \
+        else if (u == 4 && w == 16) GS_GO(NT, 4, 16);                \
+        else if (u == 2 && w == 32) GS_GO(NT, 2, 32);                \
+        else return qwb_fail(QWB_ERR_ARG, "gemm_stream: no kernel with %d blocks in flight and %d warps", u, w);  \
     } while (0)
     if (M <= 8) GS_PICK(1);
     else GS_PICK(2);
@@ -166,17 +176,18 @@ static int check_stream(const void* x, const void* W, int M, int K) {
 }
 
 extern "C" int qwb_gemm_stream(const void* x, const void* W, const float* residual, float* y, int M, int N, int K,
-                               cudaStream_t stream) {
+                               int u, int w, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (int rc = check_stream(x, W, M, K)) return rc;
-    return launch_stream<false>((const bf16*)x, (const bf16*)W, residual, y, nullptr, M, N, K, stream);
+    return launch_stream<false>((const bf16*)x, (const bf16*)W, residual, y, nullptr, M, N, K, u, w, stream);
 }
 
 // W [2 F, K]: for every 8 features their 8 gate rows, then their 8 up rows (F a multiple of 8).
 // act bfloat16 [M, F] = silu(x gate^T) * (x up^T).
-extern "C" int qwb_gemm_stream_swiglu(const void* x, const void* W, void* act, int M, int F, int K, cudaStream_t stream) {
+extern "C" int qwb_gemm_stream_swiglu(const void* x, const void* W, void* act, int M, int F, int K, int u, int w,
+                                      cudaStream_t stream) {
     if (M <= 0 || F <= 0) return 0;
     if (F % 8) return qwb_fail(QWB_ERR_ARG, "gemm_stream: %d features are not a multiple of 8", F);
     if (int rc = check_stream(x, W, M, K)) return rc;
-    return launch_stream<true>((const bf16*)x, (const bf16*)W, nullptr, nullptr, (bf16*)act, M, 2 * F, K, stream);
+    return launch_stream<true>((const bf16*)x, (const bf16*)W, nullptr, nullptr, (bf16*)act, M, 2 * F, K, u, w, stream);
 }

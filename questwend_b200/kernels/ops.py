@@ -378,9 +378,13 @@ def gemm_small(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor | N
 STREAM_M = 16           # at most this many bfloat16 rows go to the tensor-core weight-streaming kernel
 
 
+STREAM_CONFIGS = ((2, 8), (4, 8), (8, 8), (2, 16), (4, 16), (2, 32))   # (blocks of 32 k in flight per warp, warps) that exist
+
+
 def gemm_stream(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor | None = None,
-                out: torch.Tensor | None = None) -> torch.Tensor:
-    """bfloat16 x [M, K] times bfloat16 weight [N, K] transposed, as float32 [M, N] (+ residual), M <= 16."""
+                out: torch.Tensor | None = None, config: tuple | None = None) -> torch.Tensor:
+    """bfloat16 x [M, K] times bfloat16 weight [N, K] transposed, as float32 [M, N] (+ residual), M <= 16.
+    ``config``: one of ``STREAM_CONFIGS`` (default: the kernel's own choice by shape)."""
     _need(x, "x", torch.bfloat16, 2)
     _need(weight, "weight", torch.bfloat16, 2)
     M, K = x.shape
@@ -392,12 +396,13 @@ def gemm_stream(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor | 
     _need(out, "out", torch.float32, 2)
     if residual is not None:
         _need(residual, "residual", torch.float32, 2)
+    u, w = config or (0, 0)
     _call("gemm_stream", "qwb_gemm_stream", _ptr(x), _ptr(weight), _ptr(residual), _ptr(out), _i(M), _i(N), _i(K),
-          _stream())
+          _i(u), _i(w), _stream())
     return out
 
 
-def gemm_stream_swiglu(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+def gemm_stream_swiglu(x: torch.Tensor, weight: torch.Tensor, config: tuple | None = None) -> torch.Tensor:
     """silu(x gate^T) * (x up^T) as bfloat16 [M, F] for bfloat16 x [M, K], M <= 16, and the weight [2F, K] with gate and up
     rows interleaved in groups of 8 features (``interleave_gate_up``)."""
     _need(x, "x", torch.bfloat16, 2)
@@ -407,7 +412,8 @@ def gemm_stream_swiglu(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
         raise KernelError(f"gemm_stream_swiglu: x is {tuple(x.shape)}, the weight {tuple(weight.shape)}")
     F = weight.shape[0] // 2
     out = torch.empty((M, F), dtype=torch.bfloat16, device=x.device)
-    _call("gemm_stream", "qwb_gemm_stream_swiglu", _ptr(x), _ptr(weight), _ptr(out), _i(M), _i(F), _i(K), _stream())
+    u, w = config or (0, 0)
+    _call("gemm_stream", "qwb_gemm_stream_swiglu", _ptr(x), _ptr(weight), _ptr(out), _i(M), _i(F), _i(K), _i(u), _i(w), _stream())
     return out
 
 

@@ -17,6 +17,8 @@ reduced-precision (TF32) mode is switched off and checked at every call.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..kernels import ops
@@ -42,6 +44,76 @@ STREAM_WIDE_MAX_WEIGHT = 1 << 24   # two-tile form) it still is for matrices of 
 def _stream_rows(M: int, weight: torch.Tensor) -> bool:
     return M <= STREAM_MAX_ROWS or (M <= ops.STREAM_M and weight.numel() <= STREAM_WIDE_MAX_WEIGHT)
 
+
+# Which few-rows product is fastest depends on the matrix: at 8 rows the own kernel needs 19 us for Qwen3-8B's down
+# projection where the library needs 31, and 62 us for Qwen3-32B's where the library needs 45.  So for matrices large
+# enough to matter, the first step that meets a shape (rows up to 8, or 9 to 16; plain, residual-add or SwiGLU) times
+# the candidates once, each on a cold L2 as inside a step, and the choice is kept for the process.
+TUNE_MIN_WEIGHT_BYTES = 8 << 20     # smaller matrices stay in L2 anyway and every choice is at its launch floor
+TUNE = os.environ.get("QWB200_TUNE", "1") != "0"
+LIBRARY_MUST_WIN_BY = 0.90          # the own kernel starts under the tail of the kernel before it, the library's does not
+CHANGE_MUST_WIN_BY = 0.92           # what the usual choice must lose by before another is taken
+_CHOICES: dict = {}                 # (device, N, K, rows, kind) -> ("stream", (u, w) or None) | ("library", None)
+
+
+def _library(x, weight, add_to, kind, interleave):
+    if kind == "swiglu":
+        return ops.silu_mul(torch.mm(x, weight.t(), out_dtype=torch.float32), torch.bfloat16, interleave)
+    if add_to is not None:
+        return torch.addmm(add_to, x, weight.t(), out_dtype=torch.float32, out=add_to)
+    return torch.mm(x, weight.t(), out_dtype=torch.float32)
+
+
+def _stream(x, weight, add_to, kind, config):
+    if kind == "swiglu":
+        return ops.gemm_stream_swiglu(x, weight, config=config)
+    return ops.gemm_stream(x, weight, residual=add_to, config=config)
+
+
+def _measure(weight: torch.Tensor, rows: int, kind: str, default, static) -> tuple:
+    N, K = weight.shape
+    x = torch.randn(rows, K, device=weight.device).to(torch.bfloat16)
+    res = torch.zeros(rows, N, device=weight.device) if kind == "add" else None
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device=weight.device)      # larger than L2
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def time_of(fn) -> float:
+        times = []
+        for i in range(7):
+            flush.zero_()
+            start.record()
+            fn()
+            end.record()
+            end.synchronize()
+            if i >= 2:
+                times.append(start.elapsed_time(end))
+        return sorted(times)[len(times) // 2]
+
+    timed = {("stream", cfg): time_of(lambda: _stream(x, weight, res, kind, cfg)) for cfg in ops.STREAM_CONFIGS}
+    # the library's kernel starts only when the kernel before it has ended, the own one under its tail: count that
+    timed[("library", None)] = time_of(lambda: _library(x, weight, res, kind, ops.GATE_UP_GROUP)) / LIBRARY_MUST_WIN_BY
+    usual = ("stream", default) if static[0] == "stream" else ("library", None)
+    best = min(timed, key=timed.get)
+    # only a clear win changes the usual choice: timings of single kernels are not quite what a step sees
+    return best if timed[best] < CHANGE_MUST_WIN_BY * timed[usual] else (static[0], default if static[0] == "stream" else None)
+
+
+def _few_rows_choice(M: int, weight: torch.Tensor, kind: str) -> tuple:
+    """("stream", config or None) or ("library", None) for M <= 16 rows of this weight."""
+    static = ("stream", None) if _stream_rows(M, weight) else ("library", None)
+    if not TUNE or weight.numel() * weight.element_size() < TUNE_MIN_WEIGHT_BYTES:
+        return static
+    rows = STREAM_MAX_ROWS if M <= STREAM_MAX_ROWS else ops.STREAM_M
+    key = (weight.device.index, weight.shape[0], weight.shape[1], rows, kind)
+    choice = _CHOICES.get(key)
+    if choice is None:
+        if torch.cuda.is_current_stream_capturing():
+            return static                                # no measuring inside a capture (plain steps come before it)
+        N, K = weight.shape
+        default = (8, 8) if K >= 8192 else ((2, 16) if N <= 4096 else (2, 8))      # the kernel's own choice by shape
+        choice = _CHOICES[key] = _measure(weight, rows, kind, default, static)
+    return choice
+
 TC_SWIGLU_MIN_ROWS = 512    # from here on the tcgen05 gate/up product with the SiLU in its epilogue beats library + kernel
 
 
@@ -56,9 +128,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, add_to: torch.Tensor | None = 
     With ``add_to`` (float32 [M, N]) the product is added onto it in place and it is returned."""
     M, K = x.shape
     bf16 = weight.dtype == torch.bfloat16
-    if bf16 and _stream_rows(M, weight) and K % 8 == 0:
-        return ops.gemm_stream(x, weight, residual=add_to)
-    if M <= (STREAM_MAX_ROWS if bf16 else ops.SMALL_M):       # float32; bfloat16 rows whose length is no multiple of 8
+    if bf16 and M <= ops.STREAM_M and K % 8 == 0:
+        how, config = _few_rows_choice(M, weight, "plain" if add_to is None else "add")
+        if how == "stream":
+            return ops.gemm_stream(x, weight, residual=add_to, config=config)
+    elif M <= (STREAM_MAX_ROWS if bf16 else ops.SMALL_M):     # float32; bfloat16 rows whose length is no multiple of 8
         return ops.gemm_small(x, weight, residual=add_to)
     if bf16:
         if add_to is not None:
@@ -75,8 +149,10 @@ def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor, out_dtype: torc
     first; ``ops.GATE_UP_GROUP``: gate and up rows interleaved in groups of that many features, which lets the products
     with a fused epilogue find a feature's gate and up in one thread."""
     if interleave == ops.GATE_UP_GROUP and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16:
-        if _stream_rows(x.shape[0], weight_gate_up) and x.shape[1] % 8 == 0:
-            return ops.gemm_stream_swiglu(x, weight_gate_up)
+        if x.shape[0] <= ops.STREAM_M and x.shape[1] % 8 == 0:
+            how, config = _few_rows_choice(x.shape[0], weight_gate_up, "swiglu")
+            if how == "stream":
+                return ops.gemm_stream_swiglu(x, weight_gate_up, config=config)
         if x.shape[0] >= TC_SWIGLU_MIN_ROWS and x.shape[1] % 8 == 0:
             return ops.gemm_tc(x, weight_gate_up, epilogue="swiglu", tile_n=256)
     return ops.silu_mul(linear(x, weight_gate_up), out_dtype, interleave)

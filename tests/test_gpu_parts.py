@@ -155,6 +155,31 @@ def test_block_part(dtype):
     assert rel_err(f64(h_dev) + (0 if delta is None else f64(delta)), ref) < tol(dtype)
 
 
+def test_few_row_products_choose_by_measuring(monkeypatch):
+    """For large matrices the first call times the candidates and keeps the choice; whatever is chosen, the numbers are
+    those of the product (a 20 MB matrix here, with the limit lowered so that it counts as large)."""
+    from questwend_b200.parts import linear as L
+    monkeypatch.setattr(L, "TUNE", True)
+    monkeypatch.setattr(L, "TUNE_MIN_WEIGHT_BYTES", 1 << 20)
+    monkeypatch.setattr(L, "_CHOICES", {})
+    g = torch.Generator().manual_seed(0)
+    w = (torch.randn(2560, 4096, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    for rows in (3, 8, 12):
+        x = torch.randn(rows, 4096, generator=g).to(torch.bfloat16).to(DEV)
+        ref = f64(x) @ f64(w).T
+        out = L.linear(x, w)
+        assert rel_err(f64(out), ref) < FP32_TOL * 4                      # 32-bit sums of exact products
+        base = torch.randn(rows, 2560, generator=g).to(DEV)
+        added = L.linear(x, w, add_to=base.clone())
+        assert rel_err(f64(added), f64(base) + ref) < FP32_TOL * 4
+    keys = sorted(k[1:] for k in L._CHOICES)
+    assert keys == [(2560, 4096, 8, "add"), (2560, 4096, 8, "plain"), (2560, 4096, 16, "add"), (2560, 4096, 16, "plain")]
+    assert all(v[0] in ("stream", "library") for v in L._CHOICES.values())
+    gu = L.linear_swiglu(x, w, torch.bfloat16, interleave=8)             # 1280 features, gate and up interleaved in eights
+    y = ref.reshape(rows, 160, 2, 8)
+    assert rel_err(f64(gu), pm.swiglu(y[:, :, 0], y[:, :, 1]).reshape(rows, 1280)) < BF16_TOL
+
+
 # ----------------------------------------------------------------------------- a toy architecture, defined here
 class RunningMeanMixer(Mixer):
     """y_t = mean(x_0..x_t) W.  Keeps, per sequence, the running sum and the count: fixed-size state,

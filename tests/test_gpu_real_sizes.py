@@ -1,4 +1,4 @@
-"""One layer with the layer sizes of real models (widths 1024, 4096 and 5120; 16/8, 32/8 and 64/8 heads of 128) and a
+"""One layer with the layer sizes of real models (widths 1024, 4096 and 5120; 16/8, 32/8, 40/8 and 64/8 heads of 128) and a
 vocabulary that is no power of two: the kernels' tile loops, grids and strides run at the sizes they are tuned for,
 against the plain implementation (needs a B200; model folders of up to 1.3 GB in a temporary place)."""
 import numpy as np
@@ -17,8 +17,10 @@ def real(hidden, heads, kv_heads, inter, tied):
             "vocab_size": 32003, "rope_theta": 1e6, "rms_norm_eps": 1e-6, "tie_word_embeddings": tied}
 
 
-# the layer sizes of Qwen3-0.6B (2 query heads a key/value head, q wider than the model, tied head), 8B (4) and 32B (8)
-REAL = {"0.6b": real(1024, 16, 8, 3072, True), "8b": real(4096, 32, 8, 12288, False), "32b": real(5120, 64, 8, 25600, False)}
+# the layer sizes of Qwen3-0.6B (2 query heads a key/value head, q wider than the model, tied head), 8B (4), 14B (5: no
+# divisor of the attention kernel's 128 rows) and 32B (8)
+REAL = {"0.6b": real(1024, 16, 8, 3072, True), "8b": real(4096, 32, 8, 12288, False),
+        "14b": real(5120, 40, 8, 17408, False), "32b": real(5120, 64, 8, 25600, False)}
 
 
 @pytest.fixture(scope="module", params=sorted(REAL))

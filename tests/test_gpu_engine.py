@@ -71,8 +71,9 @@ def test_first_tokens_of_a_sequence(folders, name, dtype):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["C", "D"])
 def test_long_prompts_in_one_step(folders, name, dtype):
-    """A step of 690 rows (prompts of 640 and 50 tokens): enough rows for the kernels that only prefill of many
-    tokens reaches (the tcgen05 gate/up product and attention), then a second step that continues from the cache."""
+    """A step of 690 rows (prompts of 640 and 50 tokens): many row blocks and key tiles for the tcgen05 attention and the
+    library products, then a second step that continues from the cache.  (The tcgen05 gate/up product wants a model
+    width of 2,048 and more: the tests at real layer sizes reach it.)"""
     folder = folders[name, dtype]
     cfg, w = pm.read_model_folder(folder)
     eng = qw.Engine.from_folder(folder, dtype=dtype, max_tokens=1024)

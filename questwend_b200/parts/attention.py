@@ -14,10 +14,10 @@ from .base import KVSpec, Mixer
 from .linear import kernel_modules as linear_modules, linear
 from .registry import register_mixer
 
-FUSED_DECODE_MAX_BATCH = ops.STREAM_M   # up to here a kernel less per layer pays (3-4 % of a small model's step); with more
-                                        # sequences every attention block repeating the work on q costs more than it saves.
-                                        # (The same bound as the few-rows products: beyond it a step's arithmetic differs
-                                        # in its last bits anyway.)
+FUSED_DECODE_MAX_BATCH = 16     # up to here a kernel less per layer pays (3-4 % of a small model's step); with more sequences
+                                # every attention block repeating the work on q costs more than it saves (measured at 64).
+                                # (Beyond a few rows a step's products change kernels too, so a step's arithmetic differs in
+                                # its last bits between small and large batches anyway.)
 DECODE_SPLIT_TOKENS = 256     # keys per run of the plain decode kernel; fixed, so results do not depend on the batch
                               # (the tensor-core kernel cuts by each sequence's own length: ops.attn_decode)
 

@@ -241,26 +241,45 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
         __syncthreads();
     }
 
-    // 2. maximum, lowest id among equals
+    // 2. maximum, lowest id among equals.  With a small top-k ahead, the same pass counts the tokens by the top byte of
+    // their key (a histogram per warp, the lanes that hit a bin counted by one of them).
+    const bool small_k = temperature > 0.f && top_k > 0 && top_k < V && top_k <= SAMPLE_THREADS;
+    int* top_hist = reinterpret_cast<int*>(sample_smem);                 // [warps][256], the first 32 KB
     float best = -INFINITY;
     int best_i = 0x7fffffff;
-    int scalar_from = 0;
-    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {  // 16-byte loads, four in flight per thread: one block reads a row of
-        const float4* row4 = reinterpret_cast<const float4*>(row);   // 150,000 logits in a few microseconds
-        const int n4 = V >> 2;
+    if (small_k) {
+        for (int i = tid; i < SAMPLE_WARPS * 256; i += blockDim.x) top_hist[i] = 0;
+        __syncthreads();
+        int* my_hist = top_hist + warp * 256;
+        for_each_logit(row, V, [&](int i, float l, bool valid) {
+            if (valid && (l > best || (l == best && i < best_i))) { best = l; best_i = i; }
+            const unsigned live = __ballot_sync(0xffffffffu, valid);
+            if (valid) {
+                const int bin = (int)(order_key(l) >> 24);
+                const unsigned peers = __match_any_sync(live, bin);
+                if (lane == __ffs(peers) - 1) my_hist[bin] += __popc(peers);
+            }
+            __syncwarp();
+        });
+    } else {
+        int scalar_from = 0;
+        if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {  // 16-byte loads, four in flight per thread: one block reads a row
+            const float4* row4 = reinterpret_cast<const float4*>(row);   // of 150,000 logits in a few microseconds
+            const int n4 = V >> 2;
 #pragma unroll 4
-        for (int i = tid; i < n4; i += blockDim.x) {
-            const float4 v = row4[i];
-            const float l4[4] = {v.x, v.y, v.z, v.w};
+            for (int i = tid; i < n4; i += blockDim.x) {
+                const float4 v = row4[i];
+                const float l4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-                if (l4[e] > best || (l4[e] == best && 4 * i + e < best_i)) { best = l4[e]; best_i = 4 * i + e; }
+                for (int e = 0; e < 4; ++e)
+                    if (l4[e] > best || (l4[e] == best && 4 * i + e < best_i)) { best = l4[e]; best_i = 4 * i + e; }
+            }
+            scalar_from = n4 << 2;
         }
-        scalar_from = n4 << 2;
-    }
-    for (int i = scalar_from + tid; i < V; i += blockDim.x) {
-        const float l = row[i];
-        if (l > best || (l == best && i < best_i)) { best = l; best_i = i; }
+        for (int i = scalar_from + tid; i < V; i += blockDim.x) {
+            const float l = row[i];
+            if (l > best || (l == best && i < best_i)) { best = l; best_i = i; }
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -284,26 +303,102 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
     Cut cut;
     cut.key = 0u;
     cut.id_limit = V;
-    if (top_k > 0 && top_k < V)
+    if (!small_k && top_k > 0 && top_k < V)
         cut = radix_cut(row, V, cut, false, (double)top_k, best, inv_temp, whist, whist_n, hist, hist_n, &sh_above, &sh_prefix);
 
-    if (top_k > 0 && top_k < V && top_k <= SAMPLE_THREADS) {
-        // Few tokens are left (at most one per thread): they are gathered into shared memory, put in id order, and
-        // top-p and the draw are done on them there, instead of in further passes over the whole row.
-        int* cand_id = reinterpret_cast<int*>(sample_smem);              // as found
+    if (small_k) {
+        // Few tokens will be left (at most one per thread).  The histogram of the first pass says in which bin of the top
+        // byte the k-th largest key lies; if that bin and the bins above it hold few tokens, a second pass gathers those into
+        // shared memory and everything else (the exact cut, ties, top-p, the draw) happens there.  Otherwise the general
+        // selection runs and a pass gathers the kept tokens.  Either way the row is not read again after that.
+        constexpr int CAND_MAX = 8192;
+        float* wide_l = reinterpret_cast<float*>(sample_smem + 32768);    // gathered candidates: the last 64 KB
+        int* wide_id = reinterpret_cast<int*>(wide_l + CAND_MAX);
+        int* cand_id = reinterpret_cast<int*>(sample_smem);               // the kept tokens, as found: over the histogram
         float* cand_l = reinterpret_cast<float*>(cand_id + SAMPLE_THREADS);
-        int* by_id = reinterpret_cast<int*>(cand_l + SAMPLE_THREADS);    // in id order
+        int* by_id = reinterpret_cast<int*>(cand_l + SAMPLE_THREADS);     // in id order
         float* by_id_l = reinterpret_cast<float*>(by_id + SAMPLE_THREADS);
         double* by_rank_m = reinterpret_cast<double*>(by_id_l + SAMPLE_THREADS);   // masses, largest logit first
-        __shared__ int cand_n, keep_n;
-        if (tid == 0) { cand_n = 0; sh_pick = -1; }
+        __shared__ int cand_n, keep_n, wide_n, sh_bin, sh_above_n, sh_at_n, sh_limit;
         __syncthreads();
-        for_each_logit(row, V, [&](int i, float l, bool valid) {
-            if (valid && kept(cut, order_key(l), i)) {
-                const int slot = atomicAdd(&cand_n, 1);
-                if (slot < SAMPLE_THREADS) { cand_id[slot] = i; cand_l[slot] = l; }
+        for (int bin = tid; bin < 256; bin += blockDim.x) {               // the warps' counts, added up
+            int n = 0;
+            for (int w = 0; w < SAMPLE_WARPS; ++w) n += top_hist[w * 256 + bin];
+            hist_n[bin] = n;
+        }
+        if (tid == 0) { cand_n = 0; wide_n = 0; sh_pick = -1; }
+        __syncthreads();
+        if (tid == 0) {
+            int run = 0, bin = 255;
+            for (; bin > 0 && run + hist_n[bin] < top_k; --bin) run += hist_n[bin];
+            sh_bin = bin;                                                 // the k-th largest key has this top byte
+            sh_above_n = run;
+            sh_at_n = hist_n[bin];
+        }
+        __syncthreads();
+        const int cut_bin = sh_bin, above_bin = sh_above_n;
+        if (above_bin + sh_at_n <= CAND_MAX) {
+            for_each_logit(row, V, [&](int i, float l, bool valid) {
+                if (valid && (int)(order_key(l) >> 24) >= cut_bin) {
+                    const int slot = atomicAdd(&wide_n, 1);
+                    if (slot < CAND_MAX) { wide_id[slot] = i; wide_l[slot] = l; }
+                }
+            });
+            __syncthreads();
+            const int n_wide = min(wide_n, CAND_MAX);
+            // the exact cut among the tokens of the cut bin: three more bytes of the key, on the gathered tokens
+            uint32_t prefix = (uint32_t)cut_bin << 24, mask = 0xFF000000u;
+            int above = above_bin;
+            for (int shift = 16; shift >= 0; shift -= 8) {
+                for (int bin = tid; bin < 256; bin += blockDim.x) hist_n[bin] = 0;
+                __syncthreads();
+                for (int e = tid; e < n_wide; e += blockDim.x) {
+                    const uint32_t key = order_key(wide_l[e]);
+                    if ((key & mask) == prefix) atomicAdd(&hist_n[(key >> shift) & 255], 1);
+                }
+                __syncthreads();
+                if (tid == 0) {
+                    int run = above, bin = 255;
+                    for (; bin > 0 && run + hist_n[bin] < top_k; --bin) run += hist_n[bin];
+                    sh_bin = bin;
+                    sh_above_n = run;
+                    sh_at_n = hist_n[bin];
+                }
+                __syncthreads();
+                prefix |= (uint32_t)sh_bin << shift;
+                mask |= 255u << shift;
+                above = sh_above_n;
+                __syncthreads();
             }
-        });
+            const int n_at = sh_at_n, needed = max(1, top_k - above);   // tokens with exactly the cut key, and how many are kept
+            if (tid == 0) sh_limit = V;
+            __syncthreads();
+            if (needed < n_at) {                                          // a tie across the cut: the lowest ids
+                for (int e = tid; e < n_wide; e += blockDim.x) {
+                    if (order_key(wide_l[e]) != prefix) continue;
+                    int rank = 0;
+                    for (int j = 0; j < n_wide; ++j) rank += order_key(wide_l[j]) == prefix && wide_id[j] < wide_id[e];
+                    if (rank == needed - 1) sh_limit = wide_id[e];
+                }
+            }
+            __syncthreads();
+            cut.key = prefix;
+            cut.id_limit = sh_limit;
+            for (int e = tid; e < n_wide; e += blockDim.x) {
+                if (kept(cut, order_key(wide_l[e]), wide_id[e])) {
+                    const int slot = atomicAdd(&cand_n, 1);
+                    if (slot < SAMPLE_THREADS) { cand_id[slot] = wide_id[e]; cand_l[slot] = wide_l[e]; }
+                }
+            }
+        } else {
+            cut = radix_cut(row, V, cut, false, (double)top_k, best, inv_temp, whist, whist_n, hist, hist_n, &sh_above, &sh_prefix);
+            for_each_logit(row, V, [&](int i, float l, bool valid) {
+                if (valid && kept(cut, order_key(l), i)) {
+                    const int slot = atomicAdd(&cand_n, 1);
+                    if (slot < SAMPLE_THREADS) { cand_id[slot] = i; cand_l[slot] = l; }
+                }
+            });
+        }
         __syncthreads();
         const int n = min(cand_n, SAMPLE_THREADS);
         if (tid < n) {                                                   // place by the number of smaller ids

@@ -530,6 +530,36 @@ def test_ties_at_the_cut_go_to_the_lower_ids():
     assert ids == {10, 20, 30}                                           # 3 of 4 equal shares reach 0.6
 
 
+@pytest.mark.parametrize("case", ["spread", "one_binade", "tie_in_the_gathered", "negative"])
+def test_small_top_k_on_a_large_vocabulary(case):
+    """A small top-k settles the cut on the tokens whose key shares the cut's top byte, gathered once, when they are few
+    (spread), and by the general selection when they are many (all logits in [2, 8): one top byte)."""
+    V, n, k = 40003, 3000, 37
+    rng = np.random.default_rng(len(case))
+    if case == "spread":
+        row = (rng.normal(size=V) * 2.5).astype(np.float32)
+    elif case == "one_binade":
+        row = rng.uniform(2.0, 7.9, size=V).astype(np.float32)
+    elif case == "negative":
+        row = (-rng.uniform(2.0, 7.9, size=V)).astype(np.float32)
+    else:
+        row = np.full(V, -5.0, dtype=np.float32)
+        row[rng.choice(V, size=3000, replace=False)] = 3.0               # the cut falls among 3000 equal logits
+        row[[5, 20000, 39999]] = 4.0
+    probs = pm.candidate_probabilities(row, 0.9, top_k=k, top_p=0.97)
+    lg = torch.from_numpy(row).to(DEV).repeat(n, 1)
+    seq = torch.arange(n, dtype=torch.int32, device=DEV)
+    u = torch.zeros(n, dtype=torch.float64, device=DEV)
+    ids = ops.sample(lg, 0.9, top_k=k, top_p=0.97, seed=5, sequence_index=seq, out_u=u).cpu().numpy()
+    cum = np.cumsum(probs)
+    walk = np.searchsorted(cum, u.cpu().numpy() * cum[-1], side="left")
+    assert set(ids) <= set(np.nonzero(probs)[0])
+    assert (walk == ids).mean() > 0.999
+    only_k = ops.sample(lg, 0.9, top_k=k, top_p=1.0, seed=6, sequence_index=seq).cpu().numpy()
+    kept = set(np.nonzero(pm.candidate_probabilities(row, 0.9, top_k=k, top_p=1.0))[0])
+    assert set(only_k) <= kept and len(set(only_k)) > len(kept) // 2
+
+
 def test_penalties():
     V = 200
     rng = np.random.default_rng(5)

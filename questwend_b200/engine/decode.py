@@ -17,7 +17,6 @@ from __future__ import annotations
 
 import gc
 
-import numpy as np
 import torch
 
 from ..kernels import ops

@@ -12,7 +12,6 @@ returns the last position's logits only (core/runtime.h:52-54).
 """
 from __future__ import annotations
 
-import time
 from dataclasses import dataclass, field
 
 import numpy as np

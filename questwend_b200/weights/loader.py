@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import torch
 
-from .manifest import MATRIX, TABLE, VECTOR, TensorSpec
+from .manifest import MATRIX, TABLE, TensorSpec
 from .safetensors_io import SafetensorsFolder
 
 

@@ -94,7 +94,7 @@ def test_unequal_prompts_stops_and_early_ends():
     later = [e for e in eng.log if e[0] == "step" and e is not first][0]
     assert all(n == 1 for _, n in later[1])
     # sequences that end leave the batch: the number of sequences in a step never grows inside a batch
-    sizes, prev = [], None
+    prev = None
     for e in eng.log:
         if e[0] == "open":
             prev = None

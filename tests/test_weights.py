@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 import torch
 
-import questwend_b200 as qw
+import questwend_b200  # noqa: F401
 from questwend_b200.config import config_from_dict, get_architecture
 from questwend_b200.weights import (MATRIX, VECTOR, SafetensorsError, SafetensorsFile, TensorSpec, WeightsError,
                                     held_dtype, load_tensors, random_tensors, write_safetensors)

@@ -12,7 +12,6 @@ named so that pytest collects it last.
 import ctypes
 import math
 
-import numpy as np
 import pytest
 import torch
 

@@ -97,6 +97,32 @@ __device__ double block_sum(double s, double* red_d) {
     return total;
 }
 
+// Counts by bin, the highest bins first: the bin in which the running count (from `above` on) reaches k, the count before
+// that bin and the bin's own; bin 0 if it never does.  For one whole warp: lane l looks at bins 255 - 8 l down to 248 - 8 l.
+__device__ void find_count_bin(const int* hist_n, int above, int k, int* out_bin, int* out_above, int* out_at) {
+    const int lane = threadIdx.x & 31;
+    int n[8], local = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { n[j] = hist_n[255 - 8 * lane - j]; local += n[j]; }
+    int incl = local;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+    }
+    const int before = above + incl - local;
+    const unsigned crossing = __ballot_sync(0xffffffffu, before < k && before + local >= k);
+    const int owner = crossing ? __ffs(crossing) - 1 : 31;
+    if (lane == owner) {
+        int run = before, j = 0;
+        for (; j < 7 && run + n[j] < k; ++j) run += n[j];
+        if (!crossing) { j = 7; run = before + local - n[7]; }          // never reached: bin 0, all the others above it
+        *out_bin = 255 - 8 * lane - j;
+        *out_above = run;
+        *out_at = n[j];
+    }
+}
+
 // Radix selection.  Among the tokens kept by `within`, finds the cut such that the kept
 // tokens above it, plus as many tokens at it as needed (lowest ids first), reach `target`:
 // a count (by_mass = false) or a probability mass (by_mass = true; mass of token i is
@@ -196,6 +222,145 @@ __device__ Cut radix_cut(const float* row, int V, const Cut within, bool by_mass
     return cut;
 }
 
+#define SAMPLE_CAND_MAX 8192        // tokens that the small top-k path gathers at most
+#define SPLIT_THREADS 256
+#define SPLIT_WARPS (SPLIT_THREADS / 32)
+
+// What the split kernels leave for a row, for the sampling kernel to go on from (count null: it scans the row itself).
+struct Gathered {
+    const float* best;      // [B] the row's maximum
+    const int* best_i;      // [B] its id, the lowest among equals
+    const int* info;        // [B][4]: the top byte of the k-th largest key, the tokens above that byte, 1 if they did not fit
+    int* count;             // [B] tokens gathered; the sampling kernel sets it back to 0
+    const int* id;          // [B][SAMPLE_CAND_MAX]
+    const float* logit;     // [B][SAMPLE_CAND_MAX]
+};
+
+// Penalties over the recent tokens, each distinct token once, for the tokens in [i0, i1) of the row.
+__device__ void apply_penalties(float* row, int i0, int i1, const int* rec, int window, float repeat_penalty,
+                                float presence_penalty, float frequency_penalty) {
+    for (int i = threadIdx.x; i < window; i += blockDim.x) {
+        const int tok = rec[i];
+        if (tok < i0 || tok >= i1) continue;
+        bool first = true;
+        for (int j = 0; j < i; ++j) if (rec[j] == tok) { first = false; break; }
+        if (!first) continue;
+        int count = 0;
+        for (int j = i; j < window; ++j) count += rec[j] == tok;
+        float l = row[tok];
+        if (repeat_penalty != 1.f) l = l > 0.f ? l / repeat_penalty : l * repeat_penalty;
+        l -= presence_penalty + frequency_penalty * (float)count;
+        row[tok] = l;
+    }
+}
+
+// With few rows, one block per row leaves most of the GPU idle while it reads 150,000 logits four times over.  For a
+// small top-k the row is therefore cut into chunks, grid (chunks, B): this kernel applies the penalties to its chunk and
+// leaves the chunk's maximum and its count of tokens by the top byte of their key; sample_gather_kernel adds the counts
+// up, finds the byte of the k-th largest key and gathers the tokens from that byte up; sample_kernel goes on from there.
+__global__ void __launch_bounds__(SPLIT_THREADS)
+sample_scan_kernel(float* logits, int V, int chunk, const int* __restrict__ recent, int window, float repeat_penalty,
+                   float presence_penalty, float frequency_penalty, float* __restrict__ part_best,
+                   int* __restrict__ part_best_i, int* __restrict__ part_hist) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ int whist[SPLIT_WARPS][256];
+    __shared__ float red_v[SPLIT_WARPS];
+    __shared__ int red_i[SPLIT_WARPS];
+    const int c = blockIdx.x, b = blockIdx.y, n_chunks = gridDim.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float* row = logits + (size_t)b * V;
+    const int i0 = min(V, c * chunk), i1 = min(V, i0 + chunk);
+    if (recent && window > 0 && (repeat_penalty != 1.f || presence_penalty != 0.f || frequency_penalty != 0.f))
+        apply_penalties(row, i0, i1, recent + (size_t)b * window, window, repeat_penalty, presence_penalty, frequency_penalty);
+    for (int i = tid; i < SPLIT_WARPS * 256; i += blockDim.x) (&whist[0][0])[i] = 0;
+    __syncthreads();
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    int* my_hist = whist[warp];
+    for_each_logit(row + i0, i1 - i0, [&](int i, float l, bool valid) {
+        if (valid && (l > best || (l == best && i0 + i < best_i))) { best = l; best_i = i0 + i; }
+        const unsigned live = __ballot_sync(0xffffffffu, valid);
+        if (valid) {
+            const int bin = (int)(order_key(l) >> 24);
+            const unsigned peers = __match_any_sync(live, bin);
+            if (lane == __ffs(peers) - 1) my_hist[bin] += __popc(peers);
+        }
+        __syncwarp();
+    });
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    if (lane == 0) { red_v[warp] = best; red_i[warp] = best_i; }
+    __syncthreads();
+    if (tid == 0) {
+        for (int w = 1; w < SPLIT_WARPS; ++w)
+            if (red_v[w] > best || (red_v[w] == best && red_i[w] < best_i)) { best = red_v[w]; best_i = red_i[w]; }
+        part_best[(size_t)b * n_chunks + c] = best;
+        part_best_i[(size_t)b * n_chunks + c] = best_i;
+    }
+    for (int bin = tid; bin < 256; bin += blockDim.x) {
+        int n = 0;
+        for (int w = 0; w < SPLIT_WARPS; ++w) n += whist[w][bin];
+        part_hist[((size_t)b * n_chunks + c) * 256 + bin] = n;
+    }
+}
+
+__global__ void __launch_bounds__(SPLIT_THREADS)
+sample_gather_kernel(const float* __restrict__ logits, int V, int chunk, int top_k, const float* __restrict__ part_best,
+                     const int* __restrict__ part_best_i, const int* __restrict__ part_hist, float* __restrict__ best_out,
+                     int* __restrict__ best_i_out, int* __restrict__ info, int* count, int* __restrict__ cand_id,
+                     float* __restrict__ cand_l) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ int hist_n[256];
+    __shared__ int sh_bin, sh_above, sh_at, sh_fits;
+    const int c = blockIdx.x, b = blockIdx.y, n_chunks = gridDim.x, tid = threadIdx.x;
+    for (int bin = tid; bin < 256; bin += blockDim.x) {
+        int n = 0;
+        for (int k = 0; k < n_chunks; ++k) n += part_hist[((size_t)b * n_chunks + k) * 256 + bin];
+        hist_n[bin] = n;
+    }
+    __syncthreads();
+    if (tid < 32) find_count_bin(hist_n, 0, top_k, &sh_bin, &sh_above, &sh_at);   // the k-th largest key has this top byte
+    __syncthreads();
+    if (tid == 0) {
+        const int bin = sh_bin, run = sh_above;
+        sh_fits = run + sh_at <= SAMPLE_CAND_MAX;
+        if (c == 0) {
+            float best = part_best[(size_t)b * n_chunks];
+            int best_i = part_best_i[(size_t)b * n_chunks];
+            for (int k = 1; k < n_chunks; ++k) {
+                const float v = part_best[(size_t)b * n_chunks + k];
+                const int vi = part_best_i[(size_t)b * n_chunks + k];
+                if (v > best || (v == best && vi < best_i)) { best = v; best_i = vi; }
+            }
+            best_out[b] = best;
+            best_i_out[b] = best_i;
+            info[4 * b] = bin;
+            info[4 * b + 1] = run;
+            info[4 * b + 2] = sh_fits ? 0 : 1;
+            info[4 * b + 3] = 0;
+        }
+    }
+    __syncthreads();
+    if (!sh_fits) return;                                                // the sampling kernel does this row by itself
+    const int cut_bin = sh_bin;
+    const float* row = logits + (size_t)b * V;
+    const int i0 = min(V, c * chunk), i1 = min(V, i0 + chunk);
+    for_each_logit(row + i0, i1 - i0, [&](int i, float l, bool valid) {
+        if (valid && (int)(order_key(l) >> 24) >= cut_bin) {
+            const int slot = atomicAdd(&count[b], 1);
+            if (slot < SAMPLE_CAND_MAX) {
+                cand_id[(size_t)b * SAMPLE_CAND_MAX + slot] = i0 + i;
+                cand_l[(size_t)b * SAMPLE_CAND_MAX + slot] = l;
+            }
+        }
+    });
+}
+
 // logits [B, V] float (changed in place when penalties apply); recent [B, window] token ids
 // seen lately, -1 where empty; sequence_index [B] and step (+ *step_add, if given: a counter on
 // the device, for steps replayed from a CUDA graph) key the random stream; out_ids [B];
@@ -204,7 +369,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, float repeat_penalty,
               float presence_penalty, float frequency_penalty, float temperature, int top_k, float top_p,
               unsigned long long seed, const int* __restrict__ sequence_index, unsigned int step,
-              const unsigned int* __restrict__ step_add, int* __restrict__ out_ids, double* out_u) {
+              const unsigned int* __restrict__ step_add, int* __restrict__ out_ids, double* out_u, const Gathered pre) {
     pdl_wait();
     pdl_launch_dependents();
     extern __shared__ __align__(8) unsigned char sample_smem[];      // a histogram per warp: [warps][256] masses, then counts
@@ -222,22 +387,12 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
     const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float* row = logits + (size_t)b * V;
 
+    // The split kernels have been over this row (penalties, maximum, the tokens from the cut's top byte up gathered)?
+    const bool given = pre.count != nullptr && pre.info[4 * b + 2] == 0;
+
     // 1. penalties over the recent tokens, each distinct token once
-    if (recent && window > 0 && (repeat_penalty != 1.f || presence_penalty != 0.f || frequency_penalty != 0.f)) {
-        const int* rec = recent + (size_t)b * window;
-        for (int i = tid; i < window; i += blockDim.x) {
-            const int tok = rec[i];
-            if (tok < 0 || tok >= V) continue;
-            bool first = true;
-            for (int j = 0; j < i; ++j) if (rec[j] == tok) { first = false; break; }
-            if (!first) continue;
-            int count = 0;
-            for (int j = i; j < window; ++j) count += rec[j] == tok;
-            float l = row[tok];
-            if (repeat_penalty != 1.f) l = l > 0.f ? l / repeat_penalty : l * repeat_penalty;
-            l -= presence_penalty + frequency_penalty * (float)count;
-            row[tok] = l;
-        }
+    if (!pre.count && recent && window > 0 && (repeat_penalty != 1.f || presence_penalty != 0.f || frequency_penalty != 0.f)) {
+        apply_penalties(row, 0, V, recent + (size_t)b * window, window, repeat_penalty, presence_penalty, frequency_penalty);
         __syncthreads();
     }
 
@@ -247,7 +402,9 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
     int* top_hist = reinterpret_cast<int*>(sample_smem);                 // [warps][256], the first 32 KB
     float best = -INFINITY;
     int best_i = 0x7fffffff;
-    if (small_k) {
+    if (given) {
+        // nothing to read
+    } else if (small_k) {
         for (int i = tid; i < SAMPLE_WARPS * 256; i += blockDim.x) top_hist[i] = 0;
         __syncthreads();
         int* my_hist = top_hist + warp * 256;
@@ -292,6 +449,7 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
     best = red_v[0]; best_i = red_i[0];
     for (int w = 1; w < (blockDim.x >> 5); ++w)
         if (red_v[w] > best || (red_v[w] == best && red_i[w] < best_i)) { best = red_v[w]; best_i = red_i[w]; }
+    if (given) { best = pre.best[b]; best_i = pre.best_i[b]; }
     if (best_i == 0x7fffffff) best_i = 0;            // a row of NaN or -inf: the reference's loop keeps 0
     if (temperature <= 0.f) {
         if (tid == 0) out_ids[b] = best_i;
@@ -311,7 +469,7 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
         // byte the k-th largest key lies; if that bin and the bins above it hold few tokens, a second pass gathers those into
         // shared memory and everything else (the exact cut, ties, top-p, the draw) happens there.  Otherwise the general
         // selection runs and a pass gathers the kept tokens.  Either way the row is not read again after that.
-        constexpr int CAND_MAX = 8192;
+        constexpr int CAND_MAX = SAMPLE_CAND_MAX;
         float* wide_l = reinterpret_cast<float*>(sample_smem + 32768);    // gathered candidates: the last 64 KB
         int* wide_id = reinterpret_cast<int*>(wide_l + CAND_MAX);
         int* cand_id = reinterpret_cast<int*>(sample_smem);               // the kept tokens, as found: over the histogram
@@ -321,29 +479,40 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
         double* by_rank_m = reinterpret_cast<double*>(by_id_l + SAMPLE_THREADS);   // masses, largest logit first
         __shared__ int cand_n, keep_n, wide_n, sh_bin, sh_above_n, sh_at_n, sh_limit;
         __syncthreads();
-        for (int bin = tid; bin < 256; bin += blockDim.x) {               // the warps' counts, added up
-            int n = 0;
-            for (int w = 0; w < SAMPLE_WARPS; ++w) n += top_hist[w * 256 + bin];
-            hist_n[bin] = n;
-        }
+        if (!given)
+            for (int bin = tid; bin < 256; bin += blockDim.x) {           // the warps' counts, added up
+                int n = 0;
+                for (int w = 0; w < SAMPLE_WARPS; ++w) n += top_hist[w * 256 + bin];
+                hist_n[bin] = n;
+            }
         if (tid == 0) { cand_n = 0; wide_n = 0; sh_pick = -1; }
         __syncthreads();
-        if (tid == 0) {
-            int run = 0, bin = 255;
-            for (; bin > 0 && run + hist_n[bin] < top_k; --bin) run += hist_n[bin];
-            sh_bin = bin;                                                 // the k-th largest key has this top byte
-            sh_above_n = run;
-            sh_at_n = hist_n[bin];
+        if (given) {
+            if (tid == 0) {
+                sh_bin = pre.info[4 * b];
+                sh_above_n = pre.info[4 * b + 1];
+                sh_at_n = 0;
+                wide_n = min(pre.count[b], CAND_MAX);
+            }
+        } else if (tid < 32) {
+            find_count_bin(hist_n, 0, top_k, &sh_bin, &sh_above_n, &sh_at_n);   // the k-th largest key has this top byte
         }
         __syncthreads();
         const int cut_bin = sh_bin, above_bin = sh_above_n;
         if (above_bin + sh_at_n <= CAND_MAX) {
-            for_each_logit(row, V, [&](int i, float l, bool valid) {
-                if (valid && (int)(order_key(l) >> 24) >= cut_bin) {
-                    const int slot = atomicAdd(&wide_n, 1);
-                    if (slot < CAND_MAX) { wide_id[slot] = i; wide_l[slot] = l; }
+            if (given) {
+                for (int e = tid; e < wide_n; e += blockDim.x) {
+                    wide_id[e] = pre.id[(size_t)b * CAND_MAX + e];
+                    wide_l[e] = pre.logit[(size_t)b * CAND_MAX + e];
                 }
-            });
+            } else {
+                for_each_logit(row, V, [&](int i, float l, bool valid) {
+                    if (valid && (int)(order_key(l) >> 24) >= cut_bin) {
+                        const int slot = atomicAdd(&wide_n, 1);
+                        if (slot < CAND_MAX) { wide_id[slot] = i; wide_l[slot] = l; }
+                    }
+                });
+            }
             __syncthreads();
             const int n_wide = min(wide_n, CAND_MAX);
             // the exact cut among the tokens of the cut bin: three more bytes of the key, on the gathered tokens
@@ -357,13 +526,7 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
                     if ((key & mask) == prefix) atomicAdd(&hist_n[(key >> shift) & 255], 1);
                 }
                 __syncthreads();
-                if (tid == 0) {
-                    int run = above, bin = 255;
-                    for (; bin > 0 && run + hist_n[bin] < top_k; --bin) run += hist_n[bin];
-                    sh_bin = bin;
-                    sh_above_n = run;
-                    sh_at_n = hist_n[bin];
-                }
+                if (tid < 32) find_count_bin(hist_n, above, top_k, &sh_bin, &sh_above_n, &sh_at_n);
                 __syncthreads();
                 prefix |= (uint32_t)sh_bin << shift;
                 mask |= 255u << shift;
@@ -458,6 +621,7 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
         if (tid == 0) {
             out_ids[b] = sh_pick >= 0 ? sh_pick : best_i;
             if (out_u) out_u[b] = u;
+            if (pre.count) pre.count[b] = 0;                             // as the next launch expects it
         }
         return;
     }
@@ -553,10 +717,35 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
     }
 }
 
+// How the row is cut for the split kernels: 0 chunks = one block does the whole row.
+static int split_chunks(int B, int V, float temperature, int top_k) {
+    if (!(temperature > 0.f) || top_k <= 0 || top_k >= V || top_k > SAMPLE_THREADS) return 0;
+    static int n_sm = 0;
+    if (!n_sm) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
+    }
+    int chunks = 4 * n_sm / B;                                       // four blocks of 256 threads find room on an SM
+    if (chunks > 32) chunks = 32;
+    if (chunks > V / 2048) chunks = V / 2048;
+    return chunks < 2 ? 0 : chunks;
+}
+
+// Bytes of scratch that qwb_sample wants for these arguments (0: none); 16-byte aligned memory, any contents.
+extern "C" int qwb_sample_scratch_bytes(int B, int V, float temperature, int top_k) {
+    const int chunks = split_chunks(B, V, temperature, top_k);     // at most 32 chunks of at most 296 rows: 20 MB
+    if (!chunks) return 0;
+    return B * chunks * (256 + 2) * 4 + B * (2 + 4) * 4 + B * SAMPLE_CAND_MAX * 8;
+}
+
+// scratch: qwb_sample_scratch_bytes() bytes, or null (then a block does a whole row whatever the arguments);
+// counters: [B] int, zero before the first call (the kernels leave them zero), needed with scratch.
 extern "C" int qwb_sample(float* logits, int B, int V, const int* recent, int window, float repeat_penalty,
                           float presence_penalty, float frequency_penalty, float temperature, int top_k, float top_p,
                           unsigned long long seed, const int* sequence_index, unsigned int step,
-                          const unsigned int* step_add, int* out_ids, double* out_u, cudaStream_t stream) {
+                          const unsigned int* step_add, int* out_ids, double* out_u, void* scratch, int* counters,
+                          cudaStream_t stream) {
     if (B <= 0) return 0;
     if (V <= 0) return qwb_fail(QWB_ERR_ARG, "sample: bad vocabulary size %d", V);
     if (temperature > 0.f && !(top_p > 0.f)) return qwb_fail(QWB_ERR_ARG, "sample: top_p must be > 0, got %g", (double)top_p);
@@ -568,8 +757,32 @@ extern "C" int qwb_sample(float* logits, int B, int V, const int* recent, int wi
         if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "sample: %s", cudaGetErrorString(e));
         sized = true;
     }
+    Gathered pre = {};
+    const int chunks = scratch && counters ? split_chunks(B, V, temperature, top_k) : 0;
+    if (chunks) {
+        if ((uintptr_t)scratch % 16) return qwb_fail(QWB_ERR_ARG, "sample: the scratch memory must be 16-byte aligned");
+        int* part_hist = reinterpret_cast<int*>(scratch);
+        float* part_best = reinterpret_cast<float*>(part_hist + (size_t)B * chunks * 256);
+        int* part_best_i = reinterpret_cast<int*>(part_best + (size_t)B * chunks);
+        float* best = reinterpret_cast<float*>(part_best_i + (size_t)B * chunks);
+        int* best_i = reinterpret_cast<int*>(best + B);
+        int* info = best_i + B;
+        int* cand_id = info + 4 * (size_t)B;
+        float* cand_l = reinterpret_cast<float*>(cand_id + (size_t)B * SAMPLE_CAND_MAX);
+        const int chunk = ((V + chunks - 1) / chunks + 3) / 4 * 4;       // a multiple of 4: 16-byte loads stay possible
+        qwb_launch(sample_scan_kernel, dim3(chunks, B), SPLIT_THREADS, 0, stream, logits, V, chunk, recent, window, repeat_penalty,
+                   presence_penalty, frequency_penalty, part_best, part_best_i, part_hist);
+        qwb_launch(sample_gather_kernel, dim3(chunks, B), SPLIT_THREADS, 0, stream, (const float*)logits, V, chunk, top_k,
+                   (const float*)part_best, (const int*)part_best_i, (const int*)part_hist, best, best_i, info, counters, cand_id, cand_l);
+        pre.best = best;
+        pre.best_i = best_i;
+        pre.info = info;
+        pre.count = counters;
+        pre.id = cand_id;
+        pre.logit = cand_l;
+    }
     qwb_launch(sample_kernel, B, SAMPLE_THREADS, smem, stream, logits, V, recent, window, repeat_penalty, presence_penalty,
                                                    frequency_penalty, temperature, top_k, top_p, seed, sequence_index,
-                                                   step, step_add, out_ids, out_u);
+                                                   step, step_add, out_ids, out_u, pre);
     return qwb_check_launch("sample");
 }

@@ -61,11 +61,16 @@ LAUNCHES = [0]          # kernels of this library launched so far (through these
 _FUNCTIONS: dict = {}    # (module, name) -> (library, its function), looked up once
 
 
-def _call(module: str, fn: str, *args, kernels: int = 1):
+def _lookup(module: str, fn: str):
     entry = _FUNCTIONS.get((module, fn))
     if entry is None:
         lib = load_module(module)
         entry = _FUNCTIONS[module, fn] = (lib, getattr(lib, fn))
+    return entry
+
+
+def _call(module: str, fn: str, *args, kernels: int = 1):
+    entry = _lookup(module, fn)
     rc = entry[1](*args)
     LAUNCHES[0] += kernels
     if rc != 0:
@@ -483,8 +488,9 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int = 0, top_p: floa
            sequence_index: torch.Tensor | None = None, step: int = 0, recent: torch.Tensor | None = None,
            repeat_penalty: float = 1.0, presence_penalty: float = 0.0, frequency_penalty: float = 0.0,
            out_u: torch.Tensor | None = None, step_add: torch.Tensor | None = None,
-           out: torch.Tensor | None = None) -> torch.Tensor:
-    """One token id per row of float32 ``logits`` [B, V] (changed in place by penalties)."""
+           out: torch.Tensor | None = None, split: bool = True) -> torch.Tensor:
+    """One token id per row of float32 ``logits`` [B, V] (changed in place by penalties).
+    ``split`` False: one block per row whatever the sizes (the result is the same)."""
     _need(logits, "logits", torch.float32, 2)
     B, V = logits.shape
     window = 0
@@ -497,11 +503,28 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int = 0, top_p: floa
         _need(out_u, "out_u", torch.float64, 1)
     if out is None:
         out = torch.empty((B,), dtype=torch.int32, device=logits.device)
+    # few rows and a small top-k: the kernels cut every row into chunks and want scratch memory for what the chunks find
+    scratch_bytes = _lookup("sampling", "qwb_sample_scratch_bytes")[1](_i(B), _i(V), _f(temperature), _i(top_k)) if split else 0
+    scratch = counters = None
+    if scratch_bytes:
+        scratch = torch.empty((scratch_bytes,), dtype=torch.uint8, device=logits.device)
+        counters = _sample_counters(logits.device, B)
     _call("sampling", "qwb_sample", _ptr(logits), _i(B), _i(V), _ptr(recent), _i(window), _f(repeat_penalty),
           _f(presence_penalty), _f(frequency_penalty), _f(temperature), _i(top_k), _f(top_p),
           ctypes.c_ulonglong(seed & (2 ** 64 - 1)), _ptr(sequence_index), ctypes.c_uint(step & 0xFFFFFFFF),
-          _ptr(step_add), _ptr(out), _ptr(out_u), _stream())
+          _ptr(step_add), _ptr(out), _ptr(out_u), _ptr(scratch), _ptr(counters), _stream(), kernels=3 if scratch_bytes else 1)
     return out
+
+
+_SAMPLE_COUNTERS: dict = {}     # device -> zeros [rows]: the split sampling kernels count into them and leave them zero
+
+
+def _sample_counters(device, rows: int) -> torch.Tensor:
+    key = torch.device(device).index or 0
+    have = _SAMPLE_COUNTERS.get(key)
+    if have is None or have.numel() < rows:
+        have = _SAMPLE_COUNTERS[key] = torch.zeros((max(rows, 256),), dtype=torch.int32, device=device)
+    return have
 
 
 def decode_advance(sampled, token_ids, tok_pos, pos0, seq_len, step_counter=None, recent=None, n_seen=None) -> None:

@@ -560,6 +560,45 @@ def test_small_top_k_on_a_large_vocabulary(case):
     assert set(only_k) <= kept and len(set(only_k)) > len(kept) // 2
 
 
+@pytest.mark.parametrize("B,V", [(1, 151936), (5, 40003), (8, 8200), (64, 20000)])
+@pytest.mark.parametrize("case", ["spread", "one_binade", "tie_in_the_gathered"])
+def test_few_rows_cut_into_chunks_sample_the_same(B, V, case):
+    """Few rows and a small top-k: every row is cut into chunks for more blocks than rows.  Same ids as one block per row,
+    the same logits after the penalties, and the draw is the walk through the plain implementation's candidates."""
+    k = 29
+    rng = np.random.default_rng(B + len(case))
+    if case == "spread":
+        rows = (rng.normal(size=(B, V)) * 2.5).astype(np.float32)
+    elif case == "one_binade":
+        rows = rng.uniform(2.0, 7.9, size=(B, V)).astype(np.float32)        # too many tokens share the cut's top byte
+    else:
+        rows = np.full((B, V), -5.0, dtype=np.float32)
+        for r in rows:
+            r[rng.choice(V, size=2000, replace=False)] = 3.0
+            r[rng.choice(V, size=3, replace=False)] = 4.0
+    recent = rng.integers(0, V, size=(B, 12)).astype(np.int32)
+    recent[:, 3] = recent[:, 7]                                             # a token seen twice
+    recent[:, 5] = -1
+    recent[0, 0] = int(np.argmax(rows[0]))                                  # the mode itself is penalized
+    pen = dict(repeat_penalty=1.2, presence_penalty=0.3, frequency_penalty=0.1)
+    seq = torch.arange(B, dtype=torch.int32, device=DEV)
+    rec = torch.from_numpy(recent).to(DEV)
+    for step in range(6):
+        a, b = torch.from_numpy(rows).to(DEV), torch.from_numpy(rows).to(DEV)
+        u = torch.zeros(B, dtype=torch.float64, device=DEV)
+        ids = ops.sample(a, 0.9, top_k=k, top_p=0.97, seed=3, sequence_index=seq, step=step, recent=rec, out_u=u, **pen)
+        one = ops.sample(b, 0.9, top_k=k, top_p=0.97, seed=3, sequence_index=seq, step=step, recent=rec, split=False, **pen)
+        assert torch.equal(ids, one) and torch.equal(a, b)
+        for r in range(B):
+            want = pm.penalized_logits(rows[r], [t for t in recent[r] if t >= 0], repeat_penalty=1.2, presence=0.3, frequency=0.1)
+            assert np.abs(f64(a[r]) - want).max() < 1e-5
+            probs = pm.candidate_probabilities(f64(a[r]).astype(np.float32), 0.9, top_k=k, top_p=0.97)
+            cum = np.cumsum(probs)
+            assert int(np.searchsorted(cum, float(u[r]) * cum[-1], side="left")) == int(ids[r])
+    # the counters are back at zero: the next call, with other sizes, starts clean
+    assert int(ops._sample_counters(DEV, B).abs().sum()) == 0
+
+
 def test_penalties():
     V = 200
     rng = np.random.default_rng(5)

@@ -516,14 +516,18 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int = 0, top_p: floa
     return out
 
 
-_SAMPLE_COUNTERS: dict = {}     # device -> zeros [rows]: the split sampling kernels count into them and leave them zero
+SAMPLE_SPLIT_MAX_ROWS = 1024    # the split sampling kernels are used for fewer rows than this (for about 4 x SMs / 2 at most)
+_SAMPLE_COUNTERS: dict = {}     # device -> zeros [SAMPLE_SPLIT_MAX_ROWS]: the split sampling kernels count into them and
+                                # leave them zero; made once and kept, since captured graphs hold their address
 
 
 def _sample_counters(device, rows: int) -> torch.Tensor:
+    if rows > SAMPLE_SPLIT_MAX_ROWS:
+        raise KernelError(f"sample: {rows} rows cannot be cut into chunks (at most {SAMPLE_SPLIT_MAX_ROWS})")
     key = torch.device(device).index or 0
     have = _SAMPLE_COUNTERS.get(key)
-    if have is None or have.numel() < rows:
-        have = _SAMPLE_COUNTERS[key] = torch.zeros((max(rows, 256),), dtype=torch.int32, device=device)
+    if have is None:
+        have = _SAMPLE_COUNTERS[key] = torch.zeros((SAMPLE_SPLIT_MAX_ROWS,), dtype=torch.int32, device=device)
     return have
 
 

@@ -98,12 +98,13 @@ __device__ double block_sum(double s, double* red_d) {
 }
 
 // Counts by bin, the highest bins first: the bin in which the running count (from `above` on) reaches k, the count before
-// that bin and the bin's own; bin 0 if it never does.  For one whole warp: lane l looks at bins 255 - 8 l down to 248 - 8 l.
+// that bin and the bin's own; bin 0 if it never does.  For one whole warp: lane l looks at the PER_LANE bins from
+// 32 PER_LANE - 1 - PER_LANE l downwards.
+template <int PER_LANE>
 __device__ void find_count_bin(const int* hist_n, int above, int k, int* out_bin, int* out_above, int* out_at) {
-    const int lane = threadIdx.x & 31;
-    int n[8], local = 0;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { n[j] = hist_n[255 - 8 * lane - j]; local += n[j]; }
+    const int lane = threadIdx.x & 31, top = 32 * PER_LANE - 1 - PER_LANE * lane;
+    int local = 0;
+    for (int j = 0; j < PER_LANE; ++j) local += hist_n[top - j];
     int incl = local;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -115,11 +116,11 @@ __device__ void find_count_bin(const int* hist_n, int above, int k, int* out_bin
     const int owner = crossing ? __ffs(crossing) - 1 : 31;
     if (lane == owner) {
         int run = before, j = 0;
-        for (; j < 7 && run + n[j] < k; ++j) run += n[j];
-        if (!crossing) { j = 7; run = before + local - n[7]; }          // never reached: bin 0, all the others above it
-        *out_bin = 255 - 8 * lane - j;
+        for (; j < PER_LANE - 1 && run + hist_n[top - j] < k; ++j) run += hist_n[top - j];
+        if (!crossing) { j = PER_LANE - 1; run = before + local - hist_n[top - j]; }   // never reached: bin 0, the others above it
+        *out_bin = top - j;
         *out_above = run;
-        *out_at = n[j];
+        *out_at = hist_n[top - j];
     }
 }
 
@@ -225,15 +226,20 @@ __device__ Cut radix_cut(const float* row, int V, const Cut within, bool by_mass
 #define SAMPLE_CAND_MAX 8192        // tokens that the small top-k path gathers at most
 #define SPLIT_THREADS 256
 #define SPLIT_WARPS (SPLIT_THREADS / 32)
+#define SPLIT_BITS 10               // the split kernels count the tokens by the top 10 bits of their key
+#define SPLIT_BINS (1 << SPLIT_BITS)
 
 // What the split kernels leave for a row, for the sampling kernel to go on from (count null: it scans the row itself).
 struct Gathered {
     const float* best;      // [B] the row's maximum
     const int* best_i;      // [B] its id, the lowest among equals
-    const int* info;        // [B][4]: the top byte of the k-th largest key, the tokens above that byte, 1 if they did not fit
+    const int* info;        // [B][4]: the top SPLIT_BITS bits of the k-th largest key, the tokens above those, 1 if they did not fit
     int* count;             // [B] tokens gathered; the sampling kernel sets it back to 0
+    int* hist;              // [B][SPLIT_BINS] the row's counts; the sampling kernel sets them back to 0
     const int* id;          // [B][SAMPLE_CAND_MAX]
     const float* logit;     // [B][SAMPLE_CAND_MAX]
+    const double* mass;     // [B][n_chunks] the chunks' sums of exp((l - best) / temperature) over all their tokens, or null
+    int n_chunks;
 };
 
 // Penalties over the recent tokens, each distinct token once, for the tokens in [i0, i1) of the row.
@@ -256,15 +262,16 @@ __device__ void apply_penalties(float* row, int i0, int i1, const int* rec, int 
 
 // With few rows, one block per row leaves most of the GPU idle while it reads 150,000 logits four times over.  For a
 // small top-k the row is therefore cut into chunks, grid (chunks, B): this kernel applies the penalties to its chunk and
-// leaves the chunk's maximum and its count of tokens by the top byte of their key; sample_gather_kernel adds the counts
-// up, finds the byte of the k-th largest key and gathers the tokens from that byte up; sample_kernel goes on from there.
+// leaves the chunk's maximum and adds its counts of tokens by the top 10 bits of their key onto the row's; sample_gather_kernel
+// finds the bin of the k-th largest key and gathers the tokens from that bin up; sample_kernel goes on from there.
 __global__ void __launch_bounds__(SPLIT_THREADS)
 sample_scan_kernel(float* logits, int V, int chunk, const int* __restrict__ recent, int window, float repeat_penalty,
                    float presence_penalty, float frequency_penalty, float* __restrict__ part_best,
-                   int* __restrict__ part_best_i, int* __restrict__ part_hist) {
+                   int* __restrict__ part_best_i, int* row_hist) {
     pdl_wait();
     pdl_launch_dependents();
-    __shared__ int whist[SPLIT_WARPS][256];
+    constexpr int BITS = SPLIT_BITS, BINS = SPLIT_BINS;
+    __shared__ int whist[SPLIT_WARPS][BINS];
     __shared__ float red_v[SPLIT_WARPS];
     __shared__ int red_i[SPLIT_WARPS];
     const int c = blockIdx.x, b = blockIdx.y, n_chunks = gridDim.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -272,7 +279,7 @@ sample_scan_kernel(float* logits, int V, int chunk, const int* __restrict__ rece
     const int i0 = min(V, c * chunk), i1 = min(V, i0 + chunk);
     if (recent && window > 0 && (repeat_penalty != 1.f || presence_penalty != 0.f || frequency_penalty != 0.f))
         apply_penalties(row, i0, i1, recent + (size_t)b * window, window, repeat_penalty, presence_penalty, frequency_penalty);
-    for (int i = tid; i < SPLIT_WARPS * 256; i += blockDim.x) (&whist[0][0])[i] = 0;
+    for (int i = tid; i < SPLIT_WARPS * BINS; i += blockDim.x) (&whist[0][0])[i] = 0;
     __syncthreads();
     float best = -INFINITY;
     int best_i = 0x7fffffff;
@@ -281,7 +288,7 @@ sample_scan_kernel(float* logits, int V, int chunk, const int* __restrict__ rece
         if (valid && (l > best || (l == best && i0 + i < best_i))) { best = l; best_i = i0 + i; }
         const unsigned live = __ballot_sync(0xffffffffu, valid);
         if (valid) {
-            const int bin = (int)(order_key(l) >> 24);
+            const int bin = (int)(order_key(l) >> (32 - BITS));
             const unsigned peers = __match_any_sync(live, bin);
             if (lane == __ffs(peers) - 1) my_hist[bin] += __popc(peers);
         }
@@ -301,48 +308,48 @@ sample_scan_kernel(float* logits, int V, int chunk, const int* __restrict__ rece
         part_best[(size_t)b * n_chunks + c] = best;
         part_best_i[(size_t)b * n_chunks + c] = best_i;
     }
-    for (int bin = tid; bin < 256; bin += blockDim.x) {
+    for (int bin = tid; bin < BINS; bin += blockDim.x) {                 // onto the row's counts (integers: any order gives the same)
         int n = 0;
         for (int w = 0; w < SPLIT_WARPS; ++w) n += whist[w][bin];
-        part_hist[((size_t)b * n_chunks + c) * 256 + bin] = n;
+        if (n) atomicAdd(&row_hist[(size_t)b * BINS + bin], n);
     }
 }
 
 __global__ void __launch_bounds__(SPLIT_THREADS)
 sample_gather_kernel(const float* __restrict__ logits, int V, int chunk, int top_k, const float* __restrict__ part_best,
-                     const int* __restrict__ part_best_i, const int* __restrict__ part_hist, float* __restrict__ best_out,
+                     const int* __restrict__ part_best_i, const int* __restrict__ row_hist, float* __restrict__ best_out,
                      int* __restrict__ best_i_out, int* __restrict__ info, int* count, int* __restrict__ cand_id,
-                     float* __restrict__ cand_l) {
+                     float* __restrict__ cand_l, double* __restrict__ part_mass, float inv_temp) {
     pdl_wait();
     pdl_launch_dependents();
-    __shared__ int hist_n[256];
+    constexpr int BITS = SPLIT_BITS, BINS = SPLIT_BINS;
+    __shared__ int hist_n[BINS];
     __shared__ int sh_bin, sh_above, sh_at, sh_fits;
+    __shared__ float sh_best;
+    __shared__ double red_d[SPLIT_WARPS];
     const int c = blockIdx.x, b = blockIdx.y, n_chunks = gridDim.x, tid = threadIdx.x;
-    for (int bin = tid; bin < 256; bin += blockDim.x) {
-        int n = 0;
-        for (int k = 0; k < n_chunks; ++k) n += part_hist[((size_t)b * n_chunks + k) * 256 + bin];
-        hist_n[bin] = n;
-    }
+    for (int bin = tid; bin < BINS; bin += blockDim.x) hist_n[bin] = row_hist[(size_t)b * BINS + bin];
     __syncthreads();
-    if (tid < 32) find_count_bin(hist_n, 0, top_k, &sh_bin, &sh_above, &sh_at);   // the k-th largest key has this top byte
+    if (tid < 32) find_count_bin<BINS / 32>(hist_n, 0, top_k, &sh_bin, &sh_above, &sh_at);   // the k-th largest key's bin
     __syncthreads();
     if (tid == 0) {
         const int bin = sh_bin, run = sh_above;
         sh_fits = run + sh_at <= SAMPLE_CAND_MAX;
+        float best = part_best[(size_t)b * n_chunks];
+        int best_i = part_best_i[(size_t)b * n_chunks];
+        for (int k = 1; k < n_chunks; ++k) {
+            const float v = part_best[(size_t)b * n_chunks + k];
+            const int vi = part_best_i[(size_t)b * n_chunks + k];
+            if (v > best || (v == best && vi < best_i)) { best = v; best_i = vi; }
+        }
+        sh_best = best;
         if (c == 0) {
-            float best = part_best[(size_t)b * n_chunks];
-            int best_i = part_best_i[(size_t)b * n_chunks];
-            for (int k = 1; k < n_chunks; ++k) {
-                const float v = part_best[(size_t)b * n_chunks + k];
-                const int vi = part_best_i[(size_t)b * n_chunks + k];
-                if (v > best || (v == best && vi < best_i)) { best = v; best_i = vi; }
-            }
             best_out[b] = best;
             best_i_out[b] = best_i;
             info[4 * b] = bin;
             info[4 * b + 1] = run;
             info[4 * b + 2] = sh_fits ? 0 : 1;
-            info[4 * b + 3] = 0;
+            info[4 * b + 3] = BITS;
         }
     }
     __syncthreads();
@@ -350,15 +357,38 @@ sample_gather_kernel(const float* __restrict__ logits, int V, int chunk, int top
     const int cut_bin = sh_bin;
     const float* row = logits + (size_t)b * V;
     const int i0 = min(V, c * chunk), i1 = min(V, i0 + chunk);
+    const float best = sh_best;
+    double mass = 0.0;
     for_each_logit(row + i0, i1 - i0, [&](int i, float l, bool valid) {
-        if (valid && (int)(order_key(l) >> 24) >= cut_bin) {
+        if (valid && (int)(order_key(l) >> (32 - BITS)) >= cut_bin) {
             const int slot = atomicAdd(&count[b], 1);
             if (slot < SAMPLE_CAND_MAX) {
                 cand_id[(size_t)b * SAMPLE_CAND_MAX + slot] = i0 + i;
                 cand_l[(size_t)b * SAMPLE_CAND_MAX + slot] = l;
             }
         }
+        if (part_mass && valid) mass += (double)expf((l - best) * inv_temp);
     });
+    if (part_mass) {                                                     // top-p over the whole row wants the whole row's mass
+        mass = block_sum(mass, red_d);
+        if (tid == 0) part_mass[(size_t)b * n_chunks + c] = mass;
+    }
+}
+
+// `count` (a power of two) 64-bit words in shared memory into ascending order (a bitonic network); the whole block calls it.
+__device__ void sort_words(unsigned long long* w, int count) {
+    for (int k = 2; k <= count; k <<= 1)
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int i = threadIdx.x; i < count; i += blockDim.x) {
+                const int other = i ^ j;
+                if (other > i) {
+                    const bool ascending = (i & k) == 0;
+                    const unsigned long long a = w[i], o = w[other];
+                    if ((a > o) == ascending) { w[i] = o; w[other] = a; }
+                }
+            }
+            __syncthreads();
+        }
 }
 
 // logits [B, V] float (changed in place when penalties apply); recent [B, window] token ids
@@ -387,8 +417,10 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
     const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float* row = logits + (size_t)b * V;
 
-    // The split kernels have been over this row (penalties, maximum, the tokens from the cut's top byte up gathered)?
+    // The split kernels have been over this row (penalties, maximum, the tokens from the cut's bin up gathered)?
     const bool given = pre.count != nullptr && pre.info[4 * b + 2] == 0;
+    if (pre.count)
+        for (int bin = tid; bin < SPLIT_BINS; bin += blockDim.x) pre.hist[(size_t)b * SPLIT_BINS + bin] = 0;   // for the next launch
 
     // 1. penalties over the recent tokens, each distinct token once
     if (!pre.count && recent && window > 0 && (repeat_penalty != 1.f || presence_penalty != 0.f || frequency_penalty != 0.f)) {
@@ -399,12 +431,16 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
     // 2. maximum, lowest id among equals.  With a small top-k ahead, the same pass counts the tokens by the top byte of
     // their key (a histogram per warp, the lanes that hit a bin counted by one of them).
     const bool small_k = temperature > 0.f && top_k > 0 && top_k < V && top_k <= SAMPLE_THREADS;
+    // top-p with no top-k is first tried on the SAMPLE_THREADS most likely tokens: it nearly always ends among them
+    const bool p_try = temperature > 0.f && top_p < 1.f && !(top_k > 0 && top_k < V) && V > SAMPLE_THREADS;
+    const bool narrow = small_k || p_try;
+    const int k_eff = small_k ? top_k : SAMPLE_THREADS;
     int* top_hist = reinterpret_cast<int*>(sample_smem);                 // [warps][256], the first 32 KB
     float best = -INFINITY;
     int best_i = 0x7fffffff;
     if (given) {
         // nothing to read
-    } else if (small_k) {
+    } else if (narrow) {
         for (int i = tid; i < SAMPLE_WARPS * 256; i += blockDim.x) top_hist[i] = 0;
         __syncthreads();
         int* my_hist = top_hist + warp * 256;
@@ -464,7 +500,15 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
     if (!small_k && top_k > 0 && top_k < V)
         cut = radix_cut(row, V, cut, false, (double)top_k, best, inv_temp, whist, whist_n, hist, hist_n, &sh_above, &sh_prefix);
 
-    if (small_k) {
+    auto block_mass = [&](const Cut& c) -> double {
+        double mine = 0.0;
+        for_each_logit(row, V, [&](int i, float l, bool valid) {
+            if (valid && kept(c, order_key(l), i)) mine += (double)expf((l - best) * inv_temp);
+        });
+        return block_sum(mine, red_d);
+    };
+
+    if (narrow) {
         // Few tokens will be left (at most one per thread).  The histogram of the first pass says in which bin of the top
         // byte the k-th largest key lies; if that bin and the bins above it hold few tokens, a second pass gathers those into
         // shared memory and everything else (the exact cut, ties, top-p, the draw) happens there.  Otherwise the general
@@ -477,7 +521,7 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
         int* by_id = reinterpret_cast<int*>(cand_l + SAMPLE_THREADS);     // in id order
         float* by_id_l = reinterpret_cast<float*>(by_id + SAMPLE_THREADS);
         double* by_rank_m = reinterpret_cast<double*>(by_id_l + SAMPLE_THREADS);   // masses, largest logit first
-        __shared__ int cand_n, keep_n, wide_n, sh_bin, sh_above_n, sh_at_n, sh_limit;
+        __shared__ int cand_n, keep_n, wide_n, sh_bin, sh_above_n, sh_at_n, sh_limit, sh_beyond;
         __syncthreads();
         if (!given)
             for (int bin = tid; bin < 256; bin += blockDim.x) {           // the warps' counts, added up
@@ -485,7 +529,7 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
                 for (int w = 0; w < SAMPLE_WARPS; ++w) n += top_hist[w * 256 + bin];
                 hist_n[bin] = n;
             }
-        if (tid == 0) { cand_n = 0; wide_n = 0; sh_pick = -1; }
+        if (tid == 0) { cand_n = 0; wide_n = 0; sh_pick = -1; sh_beyond = 0; }
         __syncthreads();
         if (given) {
             if (tid == 0) {
@@ -495,7 +539,7 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
                 wide_n = min(pre.count[b], CAND_MAX);
             }
         } else if (tid < 32) {
-            find_count_bin(hist_n, 0, top_k, &sh_bin, &sh_above_n, &sh_at_n);   // the k-th largest key has this top byte
+            find_count_bin<8>(hist_n, 0, k_eff, &sh_bin, &sh_above_n, &sh_at_n);   // the k-th largest key has this top byte
         }
         __syncthreads();
         const int cut_bin = sh_bin, above_bin = sh_above_n;
@@ -515,25 +559,39 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
             }
             __syncthreads();
             const int n_wide = min(wide_n, CAND_MAX);
-            // the exact cut among the tokens of the cut bin: three more bytes of the key, on the gathered tokens
-            uint32_t prefix = (uint32_t)cut_bin << 24, mask = 0xFF000000u;
+            if (p_try && given && pre.mass) {
+                // top-p alone: if even all the gathered tokens do not reach the share, the general way has to do it
+                double all = 0.0, got = 0.0;
+                for (int c = 0; c < pre.n_chunks; ++c) all += pre.mass[(size_t)b * pre.n_chunks + c];
+                for (int e = tid; e < n_wide; e += blockDim.x) got += (double)expf((wide_l[e] - best) * inv_temp);
+                got = block_sum(got, red_d);
+                if (tid == 0 && got < (double)top_p * all * (1.0 - 1e-9)) sh_beyond = 1;
+                __syncthreads();
+            }
+            if (!sh_beyond) {
+            // the exact cut among the tokens of the cut bin: the rest of the key, up to 8 bits at a time, on the gathered tokens
+            int low = given ? 32 - SPLIT_BITS : 24;                       // bits of the key not yet decided
+            uint32_t prefix = (uint32_t)cut_bin << low, mask = ~0u << low;
             int above = above_bin;
-            for (int shift = 16; shift >= 0; shift -= 8) {
+            while (low > 0) {
+                const int width = min(8, low), shift = low - width;
+                const uint32_t field = (1u << width) - 1u;
                 for (int bin = tid; bin < 256; bin += blockDim.x) hist_n[bin] = 0;
                 __syncthreads();
                 for (int e = tid; e < n_wide; e += blockDim.x) {
                     const uint32_t key = order_key(wide_l[e]);
-                    if ((key & mask) == prefix) atomicAdd(&hist_n[(key >> shift) & 255], 1);
+                    if ((key & mask) == prefix) atomicAdd(&hist_n[(key >> shift) & field], 1);
                 }
                 __syncthreads();
-                if (tid < 32) find_count_bin(hist_n, above, top_k, &sh_bin, &sh_above_n, &sh_at_n);
+                if (tid < 32) find_count_bin<8>(hist_n, above, k_eff, &sh_bin, &sh_above_n, &sh_at_n);
                 __syncthreads();
                 prefix |= (uint32_t)sh_bin << shift;
-                mask |= 255u << shift;
+                mask |= field << shift;
                 above = sh_above_n;
+                low = shift;
                 __syncthreads();
             }
-            const int n_at = sh_at_n, needed = max(1, top_k - above);   // tokens with exactly the cut key, and how many are kept
+            const int n_at = sh_at_n, needed = max(1, k_eff - above);   // tokens with exactly the cut key, and how many are kept
             if (tid == 0) sh_limit = V;
             __syncthreads();
             if (needed < n_at) {                                          // a tie across the cut: the lowest ids
@@ -553,7 +611,8 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
                     if (slot < SAMPLE_THREADS) { cand_id[slot] = wide_id[e]; cand_l[slot] = wide_l[e]; }
                 }
             }
-        } else {
+            }
+        } else if (small_k) {
             cut = radix_cut(row, V, cut, false, (double)top_k, best, inv_temp, whist, whist_n, hist, hist_n, &sh_above, &sh_prefix);
             for_each_logit(row, V, [&](int i, float l, bool valid) {
                 if (valid && kept(cut, order_key(l), i)) {
@@ -561,15 +620,32 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
                     if (slot < SAMPLE_THREADS) { cand_id[slot] = i; cand_l[slot] = l; }
                 }
             });
+        } else if (tid == 0) {
+            sh_beyond = 1;                                               // too many tokens share the top byte: the general way
         }
         __syncthreads();
         const int n = min(cand_n, SAMPLE_THREADS);
-        if (tid < n) {                                                   // place by the number of smaller ids
-            const int id = cand_id[tid];
-            int pos = 0;
-            for (int j = 0; j < n; ++j) pos += cand_id[j] < id;
-            by_id[pos] = id;
-            by_id_l[pos] = cand_l[tid];
+        int padded = 1;
+        while (padded < n) padded <<= 1;
+        unsigned long long* words = reinterpret_cast<unsigned long long*>(wide_l);   // (the gathered tokens are done with)
+        const bool few = n <= 128;      // few tokens: each counts those before it; many: a sorting network (a barrier per stage)
+        if (few) {
+            if (tid < n) {                                               // into id order
+                const int id = cand_id[tid];
+                int pos = 0;
+                for (int j = 0; j < n; ++j) pos += cand_id[j] < id;
+                by_id[pos] = id;
+                by_id_l[pos] = cand_l[tid];
+            }
+        } else {
+            for (int i = tid; i < padded; i += blockDim.x)
+                words[i] = i < n ? ((unsigned long long)(uint32_t)cand_id[i] << 32) | __float_as_uint(cand_l[i]) : ~0ull;
+            __syncthreads();
+            sort_words(words, padded);
+            if (tid < n) {
+                by_id[tid] = (int)(words[tid] >> 32);
+                by_id_l[tid] = __uint_as_float((uint32_t)words[tid]);
+            }
         }
         __syncthreads();
         const bool have = tid < n;
@@ -577,62 +653,101 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
         const float l = have ? by_id_l[tid] : 0.f;
         const double m = have ? (double)expf((l - best) * inv_temp) : 0.0;
         bool keep = have;
-        if (top_p < 1.f) {
-            const double total = block_sum(m, red_d);
-            if (have) {                                                  // rank: larger logits first, lower ids first among equals
-                int rank = 0;
-                for (int j = 0; j < n; ++j) rank += by_id_l[j] > l || (by_id_l[j] == l && by_id[j] < id);
-                by_rank_m[rank] = m;
-                cand_id[tid] = rank;                                     // (the gather's arrays are free again)
+        if (top_p < 1.f && !sh_beyond) {
+            double total = block_sum(m, red_d);
+            if (p_try) {                                                 // the share is of the whole row's mass
+                Cut all;
+                all.key = 0u;
+                all.id_limit = V;
+                if (given && pre.mass) {
+                    total = 0.0;
+                    for (int c = 0; c < pre.n_chunks; ++c) total += pre.mass[(size_t)b * pre.n_chunks + c];
+                } else {
+                    total = block_mass(all);
+                }
             }
+            // rank: larger logits first, lower ids (= earlier places in id order) first among equals
+            if (few) {
+                if (have) {
+                    int rank = 0;
+                    for (int j = 0; j < n; ++j) rank += by_id_l[j] > l || (by_id_l[j] == l && j < tid);
+                    by_rank_m[rank] = m;
+                    cand_id[tid] = rank;                                 // (the gather's arrays are free again)
+                }
+            } else {
+                for (int i = tid; i < padded; i += blockDim.x)
+                    words[i] = i < n ? ((unsigned long long)(uint32_t)~order_key(by_id_l[i]) << 32) | (unsigned)i : ~0ull;
+                __syncthreads();
+                sort_words(words, padded);
+                if (have) {
+                    const int place = (int)(uint32_t)words[tid];         // the token of rank tid
+                    by_rank_m[tid] = (double)expf((by_id_l[place] - best) * inv_temp);
+                    cand_id[place] = tid;
+                }
+            }
+            if (tid == 0) keep_n = n + 1;
             __syncthreads();
-            if (tid == 0) {                                              // the smallest prefix whose share reaches top_p
-                const double target = (double)top_p * total;
-                double run = 0.0;
-                int k = 0;
-                while (k < n) { run += by_rank_m[k++]; if (run >= target) break; }
-                keep_n = k < 1 ? 1 : k;
+            {                                                            // the smallest prefix whose share reaches top_p:
+                const double target = (double)top_p * total;             // a scan over the masses in rank order
+                const double mr = tid < n ? by_rank_m[tid] : 0.0;
+                double incl = mr;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const double up = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += up;
+                }
+                if (lane == 31) red_d[warp] = incl;
+                __syncthreads();
+                for (int w = 0; w < warp; ++w) incl += red_d[w];
+                if (tid < n && incl >= target) atomicMin(&keep_n, tid + 1);
+                __syncthreads();
+                if (tid == 0) {
+                    if (keep_n > n) {                                    // never reached
+                        if (p_try) sh_beyond = 1;                        // the prefix ends beyond these tokens: the general way
+                        keep_n = n;                                      // (else: rounding left the total short; keep all)
+                    }
+                    if (keep_n < 1) keep_n = 1;
+                }
             }
             __syncthreads();
             keep = have && cand_id[tid] < keep_n;
         }
-        // the draw: a scan over the kept tokens in id order
-        const double mine = keep ? m : 0.0;
-        double incl = mine;
+        if (!sh_beyond) {
+            // the draw: a scan over the kept tokens in id order
+            const double mine = keep ? m : 0.0;
+            double incl = mine;
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const double up = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += up;
+            for (int o = 1; o < 32; o <<= 1) {
+                const double up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += up;
+            }
+            __syncthreads();
+            if (lane == 31) red_d[warp] = incl;
+            __syncthreads();
+            double before = 0.0, total = 0.0;
+            for (int w = 0; w < (blockDim.x >> 5); ++w) {
+                if (w < warp) before += red_d[w];
+                total += red_d[w];
+            }
+            before += incl - mine;
+            const double u = philox_uniform(seed, (unsigned int)(sequence_index ? sequence_index[b] : b),
+                                            step + (step_add ? *step_add : 0u));
+            const double r = u * total;
+            if (mine > 0.0 && r > before && r <= before + mine) sh_pick = id;
+            __syncthreads();
+            if (tid == 0) {
+                out_ids[b] = sh_pick >= 0 ? sh_pick : best_i;
+                if (out_u) out_u[b] = u;
+                if (pre.count) pre.count[b] = 0;                         // as the next launch expects it
+            }
+            return;
         }
+        // top-p alone, and its tokens are more than were looked at: start again with every token
         __syncthreads();
-        if (lane == 31) red_d[warp] = incl;
-        __syncthreads();
-        double before = 0.0, total = 0.0;
-        for (int w = 0; w < (blockDim.x >> 5); ++w) {
-            if (w < warp) before += red_d[w];
-            total += red_d[w];
-        }
-        before += incl - mine;
-        const double u = philox_uniform(seed, (unsigned int)(sequence_index ? sequence_index[b] : b),
-                                        step + (step_add ? *step_add : 0u));
-        const double r = u * total;
-        if (mine > 0.0 && r > before && r <= before + mine) sh_pick = id;
-        __syncthreads();
-        if (tid == 0) {
-            out_ids[b] = sh_pick >= 0 ? sh_pick : best_i;
-            if (out_u) out_u[b] = u;
-            if (pre.count) pre.count[b] = 0;                             // as the next launch expects it
-        }
-        return;
+        if (tid == 0 && pre.count) pre.count[b] = 0;
+        cut.key = 0u;
+        cut.id_limit = V;
     }
-
-    auto block_mass = [&](const Cut& c) -> double {
-        double mine = 0.0;
-        for_each_logit(row, V, [&](int i, float l, bool valid) {
-            if (valid && kept(c, order_key(l), i)) mine += (double)expf((l - best) * inv_temp);
-        });
-        return block_sum(mine, red_d);
-    };
 
     if (top_p < 1.f) {
         const double total = block_mass(cut);
@@ -718,8 +833,10 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
 }
 
 // How the row is cut for the split kernels: 0 chunks = one block does the whole row.
-static int split_chunks(int B, int V, float temperature, int top_k) {
-    if (!(temperature > 0.f) || top_k <= 0 || top_k >= V || top_k > SAMPLE_THREADS) return 0;
+static int split_chunks(int B, int V, float temperature, int top_k, float top_p) {
+    const bool small_k = top_k > 0 && top_k < V && top_k <= SAMPLE_THREADS;
+    const bool p_try = top_p < 1.f && !(top_k > 0 && top_k < V) && V > SAMPLE_THREADS;      // as in sample_kernel
+    if (!(temperature > 0.f) || !(small_k || p_try)) return 0;
     static int n_sm = 0;
     if (!n_sm) {
         int dev = 0;
@@ -729,18 +846,20 @@ static int split_chunks(int B, int V, float temperature, int top_k) {
     int chunks = 4 * n_sm / B;                                       // four blocks of 256 threads find room on an SM
     if (chunks > 32) chunks = 32;
     if (chunks > V / 2048) chunks = V / 2048;
-    return chunks < 2 ? 0 : chunks;
+    // With fewer than 16 chunks a row (more than 37 rows on 148 SMs, or a small vocabulary) the three kernels cost more
+    // than they save: measured 87 against 64 us at 64 rows of 151,936 logits, 41 against 63 us at 16 rows.
+    return chunks < 16 ? 0 : chunks;
 }
 
 // Bytes of scratch that qwb_sample wants for these arguments (0: none); 16-byte aligned memory, any contents.
-extern "C" int qwb_sample_scratch_bytes(int B, int V, float temperature, int top_k) {
-    const int chunks = split_chunks(B, V, temperature, top_k);     // at most 32 chunks of at most 296 rows: 20 MB
+extern "C" int qwb_sample_scratch_bytes(int B, int V, float temperature, int top_k, float top_p) {
+    const int chunks = split_chunks(B, V, temperature, top_k, top_p);     // at most 32 chunks of at most 296 rows: 20 MB
     if (!chunks) return 0;
-    return B * chunks * (256 + 2) * 4 + B * (2 + 4) * 4 + B * SAMPLE_CAND_MAX * 8;
+    return B * chunks * (2 + 2) * 4 + B * (2 + 4) * 4 + B * SAMPLE_CAND_MAX * 8;
 }
 
 // scratch: qwb_sample_scratch_bytes() bytes, or null (then a block does a whole row whatever the arguments);
-// counters: [B] int, zero before the first call (the kernels leave them zero), needed with scratch.
+// counters: [B][1 + 1024] int, zero before the first call (the kernels leave them zero), needed with scratch.
 extern "C" int qwb_sample(float* logits, int B, int V, const int* recent, int window, float repeat_penalty,
                           float presence_penalty, float frequency_penalty, float temperature, int top_k, float top_p,
                           unsigned long long seed, const int* sequence_index, unsigned int step,
@@ -758,11 +877,13 @@ extern "C" int qwb_sample(float* logits, int B, int V, const int* recent, int wi
         sized = true;
     }
     Gathered pre = {};
-    const int chunks = scratch && counters ? split_chunks(B, V, temperature, top_k) : 0;
+    const int chunks = scratch && counters ? split_chunks(B, V, temperature, top_k, top_p) : 0;
     if (chunks) {
         if ((uintptr_t)scratch % 16) return qwb_fail(QWB_ERR_ARG, "sample: the scratch memory must be 16-byte aligned");
-        int* part_hist = reinterpret_cast<int*>(scratch);
-        float* part_best = reinterpret_cast<float*>(part_hist + (size_t)B * chunks * 256);
+        const bool small_k = top_k > 0 && top_k < V && top_k <= SAMPLE_THREADS;
+        double* part_mass = reinterpret_cast<double*>(scratch);
+        float* part_best = reinterpret_cast<float*>(part_mass + (size_t)B * chunks);
+        int* row_hist = counters + B;
         int* part_best_i = reinterpret_cast<int*>(part_best + (size_t)B * chunks);
         float* best = reinterpret_cast<float*>(part_best_i + (size_t)B * chunks);
         int* best_i = reinterpret_cast<int*>(best + B);
@@ -771,15 +892,19 @@ extern "C" int qwb_sample(float* logits, int B, int V, const int* recent, int wi
         float* cand_l = reinterpret_cast<float*>(cand_id + (size_t)B * SAMPLE_CAND_MAX);
         const int chunk = ((V + chunks - 1) / chunks + 3) / 4 * 4;       // a multiple of 4: 16-byte loads stay possible
         qwb_launch(sample_scan_kernel, dim3(chunks, B), SPLIT_THREADS, 0, stream, logits, V, chunk, recent, window, repeat_penalty,
-                   presence_penalty, frequency_penalty, part_best, part_best_i, part_hist);
-        qwb_launch(sample_gather_kernel, dim3(chunks, B), SPLIT_THREADS, 0, stream, (const float*)logits, V, chunk, top_k,
-                   (const float*)part_best, (const int*)part_best_i, (const int*)part_hist, best, best_i, info, counters, cand_id, cand_l);
+                   presence_penalty, frequency_penalty, part_best, part_best_i, row_hist);
+        qwb_launch(sample_gather_kernel, dim3(chunks, B), SPLIT_THREADS, 0, stream, (const float*)logits, V, chunk,
+                   small_k ? top_k : SAMPLE_THREADS, (const float*)part_best, (const int*)part_best_i, (const int*)row_hist, best,
+                   best_i, info, counters, cand_id, cand_l, small_k ? (double*)nullptr : part_mass, 1.f / temperature);
         pre.best = best;
         pre.best_i = best_i;
         pre.info = info;
         pre.count = counters;
+        pre.hist = row_hist;
         pre.id = cand_id;
         pre.logit = cand_l;
+        pre.mass = small_k ? nullptr : part_mass;
+        pre.n_chunks = chunks;
     }
     qwb_launch(sample_kernel, B, SAMPLE_THREADS, smem, stream, logits, V, recent, window, repeat_penalty, presence_penalty,
                                                    frequency_penalty, temperature, top_k, top_p, seed, sequence_index,

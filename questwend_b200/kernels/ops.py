@@ -504,7 +504,8 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int = 0, top_p: floa
     if out is None:
         out = torch.empty((B,), dtype=torch.int32, device=logits.device)
     # few rows and a small top-k: the kernels cut every row into chunks and want scratch memory for what the chunks find
-    scratch_bytes = _lookup("sampling", "qwb_sample_scratch_bytes")[1](_i(B), _i(V), _f(temperature), _i(top_k)) if split else 0
+    scratch_bytes = (_lookup("sampling", "qwb_sample_scratch_bytes")[1](_i(B), _i(V), _f(temperature), _i(top_k), _f(top_p))
+                     if split else 0)
     scratch = counters = None
     if scratch_bytes:
         scratch = torch.empty((scratch_bytes,), dtype=torch.uint8, device=logits.device)
@@ -516,9 +517,10 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int = 0, top_p: floa
     return out
 
 
-SAMPLE_SPLIT_MAX_ROWS = 1024    # the split sampling kernels are used for fewer rows than this (for about 4 x SMs / 2 at most)
-_SAMPLE_COUNTERS: dict = {}     # device -> zeros [SAMPLE_SPLIT_MAX_ROWS]: the split sampling kernels count into them and
-                                # leave them zero; made once and kept, since captured graphs hold their address
+SAMPLE_SPLIT_MAX_ROWS = 592     # the split sampling kernels are used for fewer rows than this (four blocks an SM, two chunks a row)
+_SAMPLE_COUNTERS: dict = {}     # device -> zeros [SAMPLE_SPLIT_MAX_ROWS * 1025]: the split sampling kernels count into them (a
+                                # counter and 1,024 bins a row) and leave them zero; made once and kept, since captured
+                                # graphs hold their address
 
 
 def _sample_counters(device, rows: int) -> torch.Tensor:
@@ -527,7 +529,7 @@ def _sample_counters(device, rows: int) -> torch.Tensor:
     key = torch.device(device).index or 0
     have = _SAMPLE_COUNTERS.get(key)
     if have is None:
-        have = _SAMPLE_COUNTERS[key] = torch.zeros((SAMPLE_SPLIT_MAX_ROWS,), dtype=torch.int32, device=device)
+        have = _SAMPLE_COUNTERS[key] = torch.zeros((SAMPLE_SPLIT_MAX_ROWS * 1025,), dtype=torch.int32, device=device)
     return have
 
 

@@ -560,12 +560,13 @@ def test_small_top_k_on_a_large_vocabulary(case):
     assert set(only_k) <= kept and len(set(only_k)) > len(kept) // 2
 
 
-@pytest.mark.parametrize("B,V", [(1, 151936), (5, 40003), (8, 8200), (64, 20000)])
+@pytest.mark.parametrize("B,V", [(1, 151936), (5, 40003), (8, 36000), (30, 70001)])
 @pytest.mark.parametrize("case", ["spread", "one_binade", "tie_in_the_gathered"])
-def test_few_rows_cut_into_chunks_sample_the_same(B, V, case):
-    """Few rows and a small top-k: every row is cut into chunks for more blocks than rows.  Same ids as one block per row,
-    the same logits after the penalties, and the draw is the walk through the plain implementation's candidates."""
-    k = 29
+@pytest.mark.parametrize("k,p", [(29, 0.97), (0, 0.5), (0, 0.9)])
+def test_few_rows_cut_into_chunks_sample_the_same(B, V, case, k, p):
+    """Few rows and a small top-k, or top-p alone (tried on the 1,024 most likely tokens, and done the general way when
+    it needs more): every row is cut into chunks for more blocks than rows.  Same ids as one block per row, the same
+    logits after the penalties, and the draw is the walk through the plain implementation's candidates."""
     rng = np.random.default_rng(B + len(case))
     if case == "spread":
         rows = (rng.normal(size=(B, V)) * 2.5).astype(np.float32)
@@ -586,13 +587,13 @@ def test_few_rows_cut_into_chunks_sample_the_same(B, V, case):
     for step in range(6):
         a, b = torch.from_numpy(rows).to(DEV), torch.from_numpy(rows).to(DEV)
         u = torch.zeros(B, dtype=torch.float64, device=DEV)
-        ids = ops.sample(a, 0.9, top_k=k, top_p=0.97, seed=3, sequence_index=seq, step=step, recent=rec, out_u=u, **pen)
-        one = ops.sample(b, 0.9, top_k=k, top_p=0.97, seed=3, sequence_index=seq, step=step, recent=rec, split=False, **pen)
+        ids = ops.sample(a, 0.9, top_k=k, top_p=p, seed=3, sequence_index=seq, step=step, recent=rec, out_u=u, **pen)
+        one = ops.sample(b, 0.9, top_k=k, top_p=p, seed=3, sequence_index=seq, step=step, recent=rec, split=False, **pen)
         assert torch.equal(ids, one) and torch.equal(a, b)
         for r in range(B):
             want = pm.penalized_logits(rows[r], [t for t in recent[r] if t >= 0], repeat_penalty=1.2, presence=0.3, frequency=0.1)
             assert np.abs(f64(a[r]) - want).max() < 1e-5
-            probs = pm.candidate_probabilities(f64(a[r]).astype(np.float32), 0.9, top_k=k, top_p=0.97)
+            probs = pm.candidate_probabilities(f64(a[r]).astype(np.float32), 0.9, top_k=k, top_p=p)
             cum = np.cumsum(probs)
             assert int(np.searchsorted(cum, float(u[r]) * cum[-1], side="left")) == int(ids[r])
     # the counters are back at zero: the next call, with other sizes, starts clean

@@ -4,6 +4,7 @@
     python -m questwend_b200.kernels.microbench attn_decode --batch 8 --ctx 1152 [--heads 32 --kv-heads 8 --head-dim 128]
     python -m questwend_b200.kernels.microbench attn_prefill --tokens 2048
     python -m questwend_b200.kernels.microbench rmsnorm --m 8 --k 4096
+    python -m questwend_b200.kernels.microbench sample --batch 8 --vocab 151936 --temp 0.8 --top-k 40 --top-p 0.95
     python -m questwend_b200.kernels.microbench decode_shapes --m 8        (every product of a Qwen3-8B decode step)
 
 Inputs rotate through enough copies to exceed the 126 MB L2, so every timed launch reads from HBM.
@@ -139,9 +140,21 @@ def bench_rmsnorm(M, K, iters) -> dict:
     return {"kernel": "rmsnorm", "M": M, "K": K, "us": us}
 
 
+def bench_sample(B, V, temperature, top_k, top_p, iters, spread=3.0) -> dict:
+    copies = max(2, math.ceil(2 * L2_BYTES / (B * V * 4)))
+    copies = min(copies, 64)
+    rows = [torch.randn(B, V, device="cuda") * spread for _ in range(copies)]
+    seq = torch.arange(B, dtype=torch.int32, device="cuda")
+    out = torch.empty(B, dtype=torch.int32, device="cuda")
+    fn = lambda i: ops.sample(rows[i], temperature, top_k=top_k, top_p=top_p, seed=1, sequence_index=seq, step=i, out=out)
+    us = _time(fn, copies, iters)
+    return {"kernel": "sample", "B": B, "V": V, "temperature": temperature, "top_k": top_k, "top_p": top_p, "us": us,
+            "bytes": B * V * 4, "GBps": B * V * 4 / us / 1e3}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn_decode", "attn_prefill", "rmsnorm", "decode_shapes"])
+    ap.add_argument("what", choices=["gemm", "attn_decode", "attn_prefill", "rmsnorm", "decode_shapes", "sample"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=24576)
     ap.add_argument("--k", type=int, default=4096)
@@ -153,6 +166,10 @@ def main() -> int:
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--vocab", type=int, default=151936)
+    ap.add_argument("--temp", type=float, default=0.8)
+    ap.add_argument("--top-k", type=int, default=40)
+    ap.add_argument("--top-p", type=float, default=0.95)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--tile-n", type=int, default=None)
     ap.add_argument("--split", type=int, default=0, help="keys per run of the decode attention kernel (0: its own choice)")
@@ -172,6 +189,8 @@ def main() -> int:
     elif args.what == "attn_decode":
         print(json.dumps(bench_attn_decode(args.batch, args.ctx, args.heads, args.kv_heads, args.head_dim, args.iters, dtype, args.split,
                                            args.runs_target, args.run_pages_max, args.fused)))
+    elif args.what == "sample":
+        print(json.dumps(bench_sample(args.batch, args.vocab, args.temp, args.top_k, args.top_p, args.iters)))
     elif args.what == "attn_prefill":
         print(json.dumps(bench_attn_prefill(args.tokens, args.heads, args.kv_heads, args.head_dim, args.iters, dtype)))
     else:

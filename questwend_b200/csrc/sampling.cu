@@ -239,7 +239,7 @@ struct Gathered {
     const int* id;          // [B][SAMPLE_CAND_MAX]
     const float* logit;     // [B][SAMPLE_CAND_MAX]
     const double* mass;     // [B][n_chunks] the chunks' sums of exp((l - best) / temperature) over all their tokens, or null
-    int n_chunks;
+    int n_chunks, chunk;    // chunks a row, tokens a chunk
 };
 
 // Penalties over the recent tokens, each distinct token once, for the tokens in [i0, i1) of the row.
@@ -330,7 +330,11 @@ sample_gather_kernel(const float* __restrict__ logits, int V, int chunk, int top
     const int c = blockIdx.x, b = blockIdx.y, n_chunks = gridDim.x, tid = threadIdx.x;
     for (int bin = tid; bin < BINS; bin += blockDim.x) hist_n[bin] = row_hist[(size_t)b * BINS + bin];
     __syncthreads();
-    if (tid < 32) find_count_bin<BINS / 32>(hist_n, 0, top_k, &sh_bin, &sh_above, &sh_at);   // the k-th largest key's bin
+    if (top_k <= 0) {                                                    // temperature alone: only the masses are wanted
+        if (tid == 0) { sh_bin = BINS; sh_above = 0; sh_at = 0; }
+    } else if (tid < 32) {
+        find_count_bin<BINS / 32>(hist_n, 0, top_k, &sh_bin, &sh_above, &sh_at);   // the k-th largest key's bin
+    }
     __syncthreads();
     if (tid == 0) {
         const int bin = sh_bin, run = sh_above;
@@ -757,9 +761,35 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
     // 5. one draw, walking the kept tokens in id order.  Every warp owns a run of ids (a multiple of 128, so that its
     // lanes read 16 bytes each, 4 ids in a row): first each warp adds up its run, then the one warp whose run holds the
     // drawn point walks it again, 128 ids at a time with a scan over its lanes.
+    const double u = philox_uniform(seed, (unsigned int)(sequence_index ? sequence_index[b] : b),
+                                    step + (step_add ? *step_add : 0u));
+    // Temperature alone after the split kernels: the chunks' masses say which chunk holds the drawn point; only that
+    // chunk is walked.
+    int lo = 0, hi = V;
+    double base = 0.0, all = -1.0;
+    if (given && pre.mass && !narrow) {
+        const double* mass = pre.mass + (size_t)b * pre.n_chunks;
+        all = 0.0;
+        for (int c = 0; c < pre.n_chunks; ++c) all += mass[c];
+        const double r0 = u * all;
+        int chosen = -1, last = 0;
+        double run = 0.0, last_base = 0.0;
+        for (int c = 0; c < pre.n_chunks; ++c) {
+            const double m = mass[c];
+            if (m > 0.0) {
+                last = c;
+                last_base = run;
+                if (chosen < 0 && r0 <= run + m) { chosen = c; base = run; }
+            }
+            run += m;
+        }
+        if (chosen < 0) { chosen = last; base = last_base; }            // rounding at the very end
+        lo = min(V, chosen * pre.chunk);
+        hi = min(V, lo + pre.chunk);
+    }
     const int n_warps = (int)(blockDim.x >> 5);
-    const int per_warp = ((V + n_warps - 1) / n_warps + 127) / 128 * 128;
-    const int w0 = min(V, warp * per_warp), w1 = min(V, w0 + per_warp);
+    const int per_warp = ((hi - lo + n_warps - 1) / n_warps + 127) / 128 * 128;
+    const int w0 = min(hi, lo + warp * per_warp), w1 = min(hi, w0 + per_warp);
     const bool vec = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
     auto masses = [&](int i0, double* m) -> double {          // masses of the 4 ids from i0 on (0 where not kept), and their sum
         float l4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -789,13 +819,12 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
     if (lane == 0) red_d[warp] = mine;
     if (tid == 0) sh_pick = -1;
     __syncthreads();
-    double before_warp = 0.0, total = 0.0;
+    double before_warp = base, total = 0.0;
     for (int w = 0; w < n_warps; ++w) {
         if (w < warp) before_warp += red_d[w];
         total += red_d[w];
     }
-    const double u = philox_uniform(seed, (unsigned int)(sequence_index ? sequence_index[b] : b),
-                                    step + (step_add ? *step_add : 0u));
+    if (all >= 0.0) total = all;
     const double r = u * total;
     if (red_d[warp] > 0.0 && r > before_warp && r <= before_warp + red_d[warp]) {    // this warp's run holds the point
         double running = before_warp;
@@ -828,6 +857,7 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
     __syncthreads();
     if (tid == 0) {
         out_ids[b] = sh_pick >= 0 ? sh_pick : best_i;     // rounding at the very end of the walk: the mode
+        if (pre.count) pre.count[b] = 0;
         if (out_u) out_u[b] = u;
     }
 }
@@ -836,7 +866,8 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
 static int split_chunks(int B, int V, float temperature, int top_k, float top_p) {
     const bool small_k = top_k > 0 && top_k < V && top_k <= SAMPLE_THREADS;
     const bool p_try = top_p < 1.f && !(top_k > 0 && top_k < V) && V > SAMPLE_THREADS;      // as in sample_kernel
-    if (!(temperature > 0.f) || !(small_k || p_try)) return 0;
+    const bool t_only = !(top_p < 1.f) && !(top_k > 0 && top_k < V);                         // temperature alone
+    if (!(temperature > 0.f) || !(small_k || p_try || t_only)) return 0;
     static int n_sm = 0;
     if (!n_sm) {
         int dev = 0;
@@ -881,6 +912,7 @@ extern "C" int qwb_sample(float* logits, int B, int V, const int* recent, int wi
     if (chunks) {
         if ((uintptr_t)scratch % 16) return qwb_fail(QWB_ERR_ARG, "sample: the scratch memory must be 16-byte aligned");
         const bool small_k = top_k > 0 && top_k < V && top_k <= SAMPLE_THREADS;
+        const bool p_try = top_p < 1.f && !(top_k > 0 && top_k < V) && V > SAMPLE_THREADS;
         double* part_mass = reinterpret_cast<double*>(scratch);
         float* part_best = reinterpret_cast<float*>(part_mass + (size_t)B * chunks);
         int* row_hist = counters + B;
@@ -894,7 +926,7 @@ extern "C" int qwb_sample(float* logits, int B, int V, const int* recent, int wi
         qwb_launch(sample_scan_kernel, dim3(chunks, B), SPLIT_THREADS, 0, stream, logits, V, chunk, recent, window, repeat_penalty,
                    presence_penalty, frequency_penalty, part_best, part_best_i, row_hist);
         qwb_launch(sample_gather_kernel, dim3(chunks, B), SPLIT_THREADS, 0, stream, (const float*)logits, V, chunk,
-                   small_k ? top_k : SAMPLE_THREADS, (const float*)part_best, (const int*)part_best_i, (const int*)row_hist, best,
+                   small_k ? top_k : (p_try ? SAMPLE_THREADS : 0), (const float*)part_best, (const int*)part_best_i, (const int*)row_hist, best,
                    best_i, info, counters, cand_id, cand_l, small_k ? (double*)nullptr : part_mass, 1.f / temperature);
         pre.best = best;
         pre.best_i = best_i;
@@ -905,6 +937,7 @@ extern "C" int qwb_sample(float* logits, int B, int V, const int* recent, int wi
         pre.logit = cand_l;
         pre.mass = small_k ? nullptr : part_mass;
         pre.n_chunks = chunks;
+        pre.chunk = chunk;
     }
     qwb_launch(sample_kernel, B, SAMPLE_THREADS, smem, stream, logits, V, recent, window, repeat_penalty, presence_penalty,
                                                    frequency_penalty, temperature, top_k, top_p, seed, sequence_index,

@@ -562,10 +562,10 @@ def test_small_top_k_on_a_large_vocabulary(case):
 
 @pytest.mark.parametrize("B,V", [(1, 151936), (5, 40003), (8, 36000), (30, 70001)])
 @pytest.mark.parametrize("case", ["spread", "one_binade", "tie_in_the_gathered"])
-@pytest.mark.parametrize("k,p", [(29, 0.97), (0, 0.5), (0, 0.9)])
+@pytest.mark.parametrize("k,p", [(29, 0.97), (0, 0.5), (0, 0.9), (0, 1.0)])
 def test_few_rows_cut_into_chunks_sample_the_same(B, V, case, k, p):
     """Few rows and a small top-k, or top-p alone (tried on the 1,024 most likely tokens, and done the general way when
-    it needs more): every row is cut into chunks for more blocks than rows.  Same ids as one block per row, the same
+    it needs more), or temperature alone: every row is cut into chunks for more blocks than rows.  Same ids as one block per row, the same
     logits after the penalties, and the draw is the walk through the plain implementation's candidates."""
     rng = np.random.default_rng(B + len(case))
     if case == "spread":

@@ -490,7 +490,8 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int = 0, top_p: floa
            out_u: torch.Tensor | None = None, step_add: torch.Tensor | None = None,
            out: torch.Tensor | None = None, split: bool = True) -> torch.Tensor:
     """One token id per row of float32 ``logits`` [B, V] (changed in place by penalties).
-    ``split`` False: one block per row whatever the sizes (the result is the same)."""
+    ``split`` False: one block per row whatever the sizes (the result is the same).  With few rows the kernels cut
+    every row into chunks and count into one buffer per device: such calls must follow one another on one stream."""
     _need(logits, "logits", torch.float32, 2)
     B, V = logits.shape
     window = 0

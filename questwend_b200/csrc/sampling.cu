@@ -1,21 +1,29 @@
-// Sampling on the device, one block per sequence, in the reference's order
-// (core/sampler.cpp:38-109): penalties over the recent tokens; greedy if the temperature
-// is <= 0 (the lowest id wins a tie); else top-k by logit, softmax with temperature,
-// top-p (the smallest descending prefix whose share reaches top_p), and one draw.
+// Sampling on the device in the reference's order (core/sampler.cpp:38-109): penalties over the
+// recent tokens; greedy if the temperature is <= 0 (the lowest id wins a tie); else top-k by logit,
+// softmax with temperature, top-p (the smallest descending prefix whose share reaches top_p), and
+// one draw.  The draw walks the kept tokens in id order with a uniform number from a counter-based
+// generator (Philox 4x32-10) keyed by the seed, the sequence's own index and the step, so a
+// sequence's tokens do not depend on what else is in the batch.
 //
-// Nothing is sorted.  The k-th largest logit and the top-p cut are found by radix
-// selection over an order-preserving 32-bit key of the logit (four passes of 8 bits
-// with a histogram of counts or of probability mass in shared memory); ties at a cut
-// are broken toward the lower token id.  Every warp fills a histogram of its own, and
-// the lanes of a warp that hit the same bin are added up by one of them first, so no
-// two threads ever write the same word and no atomic operation is needed: with a
-// vocabulary of 150,000 a histogram shared by the block, updated atomically, cost a
-// millisecond a cut.  Rows are read 16 bytes a load.  When top-k leaves at most one token
-// per thread (the usual case: the reference's default is 40), the kept tokens are gathered
-// into shared memory and top-p and the draw are done there.  The draw walks the kept tokens in id order with
-// a uniform number from a counter-based generator (Philox 4x32-10) keyed by the seed,
-// the sequence's own index and the step, so a sequence's tokens do not depend on what
-// else is in the batch.
+// The general way (sample_kernel, one block per row): nothing is sorted.  The k-th largest logit
+// and the top-p cut are found by radix selection over an order-preserving 32-bit key of the logit
+// (four passes of 8 bits with a histogram of counts or of probability mass in shared memory); ties
+// at a cut are broken toward the lower token id.  Every warp fills a histogram of its own, and the
+// lanes of a warp that hit the same bin are added up by one of them first, so no two threads ever
+// write the same word and no atomic operation is needed: with a vocabulary of 150,000 a histogram
+// shared by the block, updated atomically, cost a millisecond a cut.  Rows are read 16 bytes a load.
+//
+// The short way, when few tokens can be left (a top-k of at most 1,024, the reference's default
+// being 40; or top-p alone, tried as a top-k of 1,024 whose share is of the whole row's mass): the
+// pass that finds the maximum also counts the tokens by the top bits of their key; the tokens from
+// the bin of the k-th largest key up (at most 8,192) are gathered into shared memory, and the exact
+// cut, its ties, top-p and the draw are settled there.  If they do not fit, or top-p needs more than
+// the 1,024 tokens, the general way runs.
+//
+// With few rows (at least 16 chunks of a row find an SM) the two passes of the short way are kernels
+// of their own over chunks of a row (sample_scan_kernel, sample_gather_kernel), and sample_kernel
+// starts from what they gathered; temperature alone uses them too: the chunks' masses say which
+// chunk holds the drawn point, and only that chunk is walked.
 #include "common.cuh"
 
 #define SAMPLE_THREADS 1024

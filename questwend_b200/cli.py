@@ -51,6 +51,33 @@ def build_parser() -> argparse.ArgumentParser:
     return ap
 
 
+def model_info(config, dtype: str) -> dict:
+    """The configuration, the tensors it asks for, and what the model takes in memory: the weights as the engine holds
+    them and the cache per token of a live sequence (the reference's ``--info`` prints its summary, cli/main.cpp:236-239)."""
+    import math
+
+    import torch
+
+    from .config.registry import get_architecture
+    from .engine.model import Model
+    from .parts.base import Runtime
+    from .weights.loader import held_dtype
+    plan = get_architecture(config.architecture).plan(config)
+    compute = torch.bfloat16 if dtype == "bfloat16" else torch.float32
+    model = Model(plan, Runtime(torch.device("cpu"), compute))
+    tensors = [t for t in model.tensors() if not (t.optional or t.ignored)]
+    size = lambda dt: torch.empty((), dtype=dt).element_size()
+    weight_bytes = sum(math.prod(t.shape) * size(held_dtype(t, compute, compute)) for t in tensors)
+    cache_bytes = sum(2 * kv.n_kv_heads * kv.head_dim * size(compute)
+                      for kv, _, cache_of in model.cache_units() if kv is not None and cache_of is None)
+    state_bytes = sum(math.prod(st.shape) * size(st.dtype)
+                      for _, st, cache_of in model.cache_units() if st is not None and cache_of is None)
+    return {"config": config.to_dict(), "parameters": sum(math.prod(t.shape) for t in tensors), "layers": len(plan.layers),
+            "tensors": len(plan.manifest()),
+            "memory": {"dtype": dtype, "weight_bytes": weight_bytes, "cache_bytes_per_token": cache_bytes,
+                       "state_bytes_per_sequence": state_bytes}}
+
+
 def main(argv=None) -> int:
     args = build_parser().parse_args(argv)
     from .config.registry import load_config
@@ -60,11 +87,7 @@ def main(argv=None) -> int:
 
     config = load_config(args.model)
     if args.info:
-        from .config.registry import get_architecture
-        plan = get_architecture(config.architecture).plan(config)
-        n = sum(int(__import__("math").prod(t.shape)) for t in plan.manifest() if not (t.optional or t.ignored))
-        print(json.dumps({"config": config.to_dict(), "parameters": n, "layers": len(plan.layers),
-                          "tensors": len(plan.manifest())}, indent=2))
+        print(json.dumps(model_info(config, args.dtype), indent=2))
         return 0
     prompts = [parse_ids(p) for p in args.prompts]
     if args.ids_file:

@@ -104,3 +104,18 @@ def test_plan_is_data():
     shapes = {t.name: t.shape for t in plan.manifest()}
     assert shapes["model.layers.0.self_attn.q_proj.weight"] == (192, 96)
     assert shapes["model.layers.0.mlp.down_proj.weight"] == (96, 200)
+
+
+def test_info_counts_weights_and_cache():
+    from questwend_b200.cli import model_info
+    cfgd = TINY_B
+    info = model_info(config_from_dict(dict(cfgd)), "float32")
+    L, D, F, V = cfgd["num_hidden_layers"], cfgd["hidden_size"], cfgd["intermediate_size"], cfgd["vocab_size"]
+    Hq, Hkv, hd = cfgd["num_attention_heads"], cfgd["num_key_value_heads"], cfgd["head_dim"]
+    per_layer = (Hq + 2 * Hkv) * hd * D + Hq * hd * D + 3 * F * D + 2 * D + 2 * hd
+    params = L * per_layer + V * D * (1 if cfgd.get("tie_word_embeddings") else 2) + D
+    assert info["parameters"] == params
+    assert info["memory"] == {"dtype": "float32", "weight_bytes": 4 * params,
+                              "cache_bytes_per_token": L * 2 * Hkv * hd * 4, "state_bytes_per_sequence": 0}
+    half = model_info(config_from_dict(dict(cfgd)), "bfloat16")["memory"]
+    assert half["weight_bytes"] == 2 * params and half["cache_bytes_per_token"] == L * 2 * Hkv * hd * 2

@@ -886,8 +886,10 @@ static int split_chunks(int B, int V, float temperature, int top_k, float top_p)
     if (chunks > 32) chunks = 32;
     if (chunks > V / 2048) chunks = V / 2048;
     // With fewer than 16 chunks a row (more than 37 rows on 148 SMs, or a small vocabulary) the three kernels cost more
-    // than they save: measured 87 against 64 us at 64 rows of 151,936 logits, 41 against 63 us at 16 rows.
-    return chunks < 16 ? 0 : chunks;
+    // than they save: measured 87 against 64 us at 64 rows of 151,936 logits, 41 against 63 us at 16 rows.  Not so for
+    // top-p alone: a block on its own counts by the key's top byte only, too coarse to gather 1,024 tokens of a wide
+    // distribution, and then takes the general way (135 against 505 us at 64 rows).
+    return chunks < (p_try ? 2 : 16) ? 0 : chunks;
 }
 
 // Bytes of scratch that qwb_sample wants for these arguments (0: none); 16-byte aligned memory, any contents.

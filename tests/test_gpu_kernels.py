@@ -560,7 +560,7 @@ def test_small_top_k_on_a_large_vocabulary(case):
     assert set(only_k) <= kept and len(set(only_k)) > len(kept) // 2
 
 
-@pytest.mark.parametrize("B,V", [(1, 151936), (5, 40003), (8, 36000), (30, 70001)])
+@pytest.mark.parametrize("B,V", [(1, 151936), (5, 40003), (8, 36000), (30, 70001), (64, 20000)])
 @pytest.mark.parametrize("case", ["spread", "one_binade", "tie_in_the_gathered"])
 @pytest.mark.parametrize("k,p", [(29, 0.97), (0, 0.5), (0, 0.9), (0, 1.0)])
 def test_few_rows_cut_into_chunks_sample_the_same(B, V, case, k, p):

@@ -61,12 +61,15 @@ class DecodeRunner:
         self.state_host = torch.zeros((6, B), dtype=torch.int32).pin_memory()
         self.tokens_host = torch.zeros((B,), dtype=torch.int32).pin_memory()
         self.sampled_host = torch.zeros((B,), dtype=torch.int32).pin_memory()
-        self.graphs: dict = {}
+        self._tokens_np = self.tokens_host.numpy()      # the same pinned memory, written and read without a tensor op
+        self._sampled_np = self.sampled_host.numpy()
+        self._sampled_on_host = False                   # the last step copied its ids to the host itself
+        self.graphs: dict = {}                          # (length bound, with host copies) -> graph
         self._pool = None           # the graphs run one at a time: they share one pool of memory
         self.slots: list = []
         self._pages_seen: list = []
         self._room = 0              # steps that need no new page and no other graph (see step)
-        self._graph = None
+        self._graph = {}            # with host copies or not -> the graph for the steps in this room
         self._plain_steps: dict = {}    # length bound -> plain steps run so far
         self.launches_per_step = 0
 
@@ -120,9 +123,11 @@ class DecodeRunner:
                            step_counter=self.step_counter, recent=self.recent,
                            n_seen=self.n_seen if self.window else None)
 
-    def _capture(self, bucket: int):
+    def _capture(self, bucket: int, host_copies: bool):
         # one plain run first: it loads the kernels and sets their attributes; it writes only what
         # the captured run writes again (this step's keys and values, the sampled ids)
+        if host_copies:
+            self.token_ids.copy_(self.tokens_host, non_blocking=True)
         self._forward_and_sample(bucket)
         torch.cuda.current_stream().synchronize()
         g = torch.cuda.CUDAGraph()
@@ -136,18 +141,27 @@ class DecodeRunner:
             if self._pool is None:
                 self._pool = torch.cuda.graph_pool_handle()
             with torch.cuda.graph(g, pool=self._pool):
+                if host_copies:         # the step's tokens come from pinned host memory and its ids go back there:
+                    self.token_ids.copy_(self.tokens_host, non_blocking=True)      # two copy nodes of the graph
                 self._forward_and_sample(bucket)
                 self._advance()
+                if host_copies:
+                    self.sampled_host.copy_(self.sampled, non_blocking=True)
         finally:
             if collect_again:
                 gc.enable()
         self.launches_per_step = ops.LAUNCHES[0] - before
         return g
 
-    def step(self) -> None:
+    def step(self, host_tokens=None) -> None:
         """Run one decode step for the bound sequences; the sampled ids land in ``self.sampled``
-        and become the next inputs."""
+        and become the next inputs.  ``host_tokens``: this step's input tokens as the host knows them; the step
+        then copies them in from pinned memory and copies its ids out to pinned memory (``read_sampled`` only
+        waits), inside the graph when it is replayed.  None: the inputs are on the device already."""
         cache = self.engine.cache
+        host_copies = host_tokens is not None
+        if host_copies:
+            self._tokens_np[:] = host_tokens
         if self._room <= 0:
             # A sequence may need a page, or the longest one leaves the graph's bucket: look, and count the steps
             # until either can happen again.  Nothing else changes between the steps of a bound batch.
@@ -162,29 +176,38 @@ class DecodeRunner:
                 room = min(room, min(c * ops.PAGE_SIZE - n for c, n in zip(counts, lengths)))
             self._bucket = length_bucket(max(lengths) + 1)
             self._room = min(room, self._bucket - max(lengths))
-            self._graph = None
+            self._graph = {}
         self._room -= 1
         with torch.cuda.device(self.engine.device):
-            if self.use_graph and self._graph is None:
-                self._graph = self.graphs.get(self._bucket)
-                if self._graph is None and self._plain_steps.get(self._bucket, 0) >= GRAPH_AFTER:
+            graph = self._graph.get(host_copies)
+            if self.use_graph and graph is None:
+                key = (self._bucket, host_copies)
+                graph = self.graphs.get(key)
+                if graph is None and self._plain_steps.get(self._bucket, 0) >= GRAPH_AFTER:
                     # a capture costs about two steps: it pays only for a batch that stays (a batch whose sequences
                     # end one after the other passes through many sizes for a step or two each)
-                    self._graph = self.graphs[self._bucket] = self._capture(self._bucket)
-            if self._graph is not None:
-                self._graph.replay()
+                    graph = self.graphs[key] = self._capture(self._bucket, host_copies)
+                self._graph[host_copies] = graph
+            if graph is not None:
+                graph.replay()
             else:
+                if host_copies:
+                    self.token_ids.copy_(self.tokens_host, non_blocking=True)
                 before = ops.LAUNCHES[0]
                 self._forward_and_sample(self._bucket)
                 self._advance()
                 self.launches_per_step = ops.LAUNCHES[0] - before
                 self._plain_steps[self._bucket] = self._plain_steps.get(self._bucket, 0) + 1
+                if host_copies:
+                    self.sampled_host.copy_(self.sampled, non_blocking=True)
+        self._sampled_on_host = host_copies
         for s in self.slots:
             cache.advance(s, 1)
         self.engine.steps_run += 1
 
     def read_sampled(self) -> list:
-        """The ids sampled by the last step, on the host (one copy, waits for the step)."""
-        self.sampled_host.copy_(self.sampled, non_blocking=True)
+        """The ids sampled by the last step, on the host (waits for the step; copies first if the step did not)."""
+        if not self._sampled_on_host:
+            self.sampled_host.copy_(self.sampled, non_blocking=True)
         torch.cuda.current_stream().synchronize()
-        return self.sampled_host.tolist()
+        return self._sampled_np.tolist()

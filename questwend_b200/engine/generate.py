@@ -97,8 +97,7 @@ class _GraphStepper:
             self.runner.bind([self.slot_of[i] for i in active], tokens, active, step,
                              [self.windows[i] for i in active])
             self.bound = list(active)
-        self.runner.set_tokens(tokens)
-        self.runner.step()
+        self.runner.step(host_tokens=tokens)
         return self.runner.read_sampled()
 
 

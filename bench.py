@@ -144,7 +144,7 @@ def decode_run(engine, torch, batch, warmup, steps, rng, count_launches=False):
         grp = list(range(i, min(batch, i + 8)))
         lg = engine.step([StepEntry(slots[j], prompts[j], [PROMPT_LEN - 1]) for j in grp])
         first += lg.argmax(-1).tolist()
-    runner = engine.decode_runner(batch, GREEDY, 0)
+    runner = engine.decode_runner(batch, GREEDY)
     runner.bind(slots, first, list(range(batch)), 1)
     for _ in range(warmup):
         runner.step()

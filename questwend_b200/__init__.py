@@ -7,10 +7,10 @@ kishida/questwend computes for its Qwen3 dense architecture.
 """
 from . import models  # noqa: F401  (registers the architectures)
 from .config import ConfigError, load_config, register_architecture
-from .engine import Engine, EngineError, StepEntry, generate, GenerationResult, GenerationStats
+from .engine import Engine, EngineError, StepEntry, generate, GenerationResult, GenerationStats, StepProfile
 from .sampling import SamplingParams, GREEDY
 from .weights import WeightsError, write_model_folder
 
-__all__ = ["Engine", "EngineError", "StepEntry", "generate", "GenerationResult", "GenerationStats",
+__all__ = ["Engine", "EngineError", "StepEntry", "generate", "GenerationResult", "GenerationStats", "StepProfile",
            "SamplingParams", "GREEDY", "ConfigError", "load_config", "register_architecture", "WeightsError",
            "write_model_folder"]

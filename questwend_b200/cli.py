@@ -7,7 +7,11 @@ default), ``--top-p`` (0.95), ``--top-k`` (40), ``--seed`` (0 = random), ``--rep
 ``--repeat-last-n`` (64), ``--log-tokens-per-sec``, ``--info``.  There is no tokenizer here, so a
 prompt is a list of token ids: ``-p "1 2 3"`` (spaces or commas); ``-p`` may be given several times,
 and ``--ids-file`` reads one prompt per line; the prompts then run as batches.  ``-m`` names a
-folder with config.json and model.safetensors.  Generation stops at the model's ``eos_token_id``
+folder with config.json and model.safetensors; instead of it, ``--random <config.json>`` takes a
+configuration alone and draws the weights from ``--seed`` (N(0, 0.02), norms 1 + U(-0.1, 0.1)), on the
+device, or, with ``--save <folder>``, on the CPU into a model folder that is written and then loaded
+(the same numbers on every machine).  ``--profile-step`` prints where every decode step's time went
+(the reference's QWEN_PROF, core/runtime.cpp:1769, 1821-1825).  Generation stops at the model's ``eos_token_id``
 (the reference stops at its vocabulary's EOS and at <|im_end|>, cli/main.cpp:374-376) and at any
 ``--stop-id``; a stop token is not printed.  Output: one line of generated ids per prompt.
 """
@@ -29,7 +33,9 @@ def parse_ids(text: str) -> list[int]:
 
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="qw-cli", description="generate from token ids with a Qwen3 model on one B200")
-    ap.add_argument("-m", dest="model", required=True, help="model folder (config.json + model.safetensors)")
+    ap.add_argument("-m", dest="model", help="model folder (config.json + model.safetensors)")
+    ap.add_argument("--random", metavar="CONFIG_JSON", help="instead of -m: a config.json; the weights are drawn from --seed")
+    ap.add_argument("--save", metavar="DIR", help="with --random: write the model folder there (config.json + model.safetensors)")
     ap.add_argument("-p", dest="prompts", action="append", default=[], help="prompt as token ids, e.g. \"1 2 3\"")
     ap.add_argument("--ids-file", help="file with one prompt (token ids) per line")
     ap.add_argument("-n", dest="max_tokens", type=int, default=128, help="max new tokens (default 128)")
@@ -48,6 +54,7 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--max-batch", type=int, default=64, help="most sequences generated at once")
     ap.add_argument("--log-tokens-per-sec", action="store_true", help="print speed")
     ap.add_argument("--info", action="store_true", help="print model info and exit")
+    ap.add_argument("--profile-step", action="store_true", help="print where every decode step's time went")
     return ap
 
 
@@ -80,12 +87,28 @@ def model_info(config, dtype: str) -> dict:
 
 def main(argv=None) -> int:
     args = build_parser().parse_args(argv)
-    from .config.registry import load_config
+    from .config.registry import config_from_dict, load_config
     from .engine.engine import Engine
     from .engine.generate import GenerationStats, generate
     from .sampling.params import SamplingParams
+    from .weights.random_init import write_model_folder
 
-    config = load_config(args.model)
+    if bool(args.model) == bool(args.random):
+        raise SystemExit("error: give either -m <model folder> or --random <config.json>")
+    if args.save and not args.random:
+        raise SystemExit("error: --save goes with --random")
+    if args.random:
+        import os
+        with open(args.random) as f:
+            config = config_from_dict(json.load(f), args.random)
+        if args.save:
+            write_model_folder(args.save, config, args.seed, args.dtype)
+            args.model = args.save
+            if not (args.prompts or args.ids_file or args.info):
+                print(os.path.abspath(args.save))
+                return 0
+    else:
+        config = load_config(args.model)
     if args.info:
         print(json.dumps(model_info(config, args.dtype), indent=2))
         return 0
@@ -98,8 +121,11 @@ def main(argv=None) -> int:
     n_ctx = args.n_ctx or getattr(config, "max_position_embeddings", None) or 4096
     batch = min(args.max_batch, len(prompts))
     longest = min(n_ctx, max(len(p) for p in prompts) + args.max_tokens)
-    engine = Engine.from_folder(args.model, dtype=args.dtype, max_tokens=batch * (longest + 64),
-                                max_seq_len=n_ctx, max_batch=batch)
+    sizes = dict(max_tokens=batch * (longest + 64), max_seq_len=n_ctx, max_batch=batch)
+    if args.model:
+        engine = Engine.from_folder(args.model, dtype=args.dtype, **sizes)
+    else:
+        engine = Engine.from_config(config, seed=args.seed, dtype=args.dtype, **sizes)
     sampling = SamplingParams(temperature=args.temp, top_p=args.top_p, top_k=args.top_k, seed=args.seed,
                               repeat_penalty=args.repeat_penalty, presence_penalty=args.presence_penalty,
                               frequency_penalty=args.frequency_penalty, repeat_last_n=args.repeat_last_n)
@@ -108,7 +134,7 @@ def main(argv=None) -> int:
     if args.stop_id is not None:
         stop_ids = tuple(args.stop_id) + tuple(engine.plan.stop_token_ids)
     results = generate(engine, prompts, max_new_tokens=args.max_tokens, sampling=sampling, stop_ids=stop_ids,
-                       ignore_eos=args.ignore_eos, stats=stats)
+                       ignore_eos=args.ignore_eos, stats=stats, profile=True if args.profile_step else None)
     for r in results:
         print(" ".join(str(t) for t in r.tokens))
     if args.log_tokens_per_sec:

@@ -14,6 +14,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 
 from .base import ConfigError, ConfigReader, ModelConfig
+from ..kernels.limits import head_dim_refusal
 
 ARCHITECTURE = "Qwen3ForCausalLM"
 
@@ -97,6 +98,10 @@ class Qwen3Config(ModelConfig):
                               f"'num_key_value_heads' ({kv_heads})")
         if head_dim % 2:
             raise ConfigError(f"{w}: key 'head_dim' ({head_dim}) must be even: RoPE rotates pairs")
+        refusal = head_dim_refusal(head_dim)
+        if refusal:
+            which = "key 'head_dim'" if r.has("head_dim") else "'hidden_size' / 'num_attention_heads' (no key 'head_dim')"
+            raise ConfigError(f"{w}: {which} gives a head size of {head_dim}: {refusal}")
         tie = r.boolean("tie_word_embeddings", None)
         max_pos = r.integer("max_position_embeddings", None, minimum=1)
         eos = tuple(r.int_list("eos_token_id", []))

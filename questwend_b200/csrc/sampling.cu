@@ -405,15 +405,18 @@ __device__ void sort_words(unsigned long long* w, int count) {
 
 // logits [B, V] float (changed in place when penalties apply); recent [B, window] token ids
 // seen lately, -1 where empty; sequence_index [B] and step (+ *step_add, if given: a counter on
-// the device, for steps replayed from a CUDA graph) key the random stream; out_ids [B];
+// the device, for steps replayed from a CUDA graph) key the random stream, with the seed (read from *seed_from
+// instead, if that is given: a seed on the device, so that a captured graph serves every seed); out_ids [B];
 // out_u [B] optional: the uniform numbers that were used.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, float repeat_penalty,
               float presence_penalty, float frequency_penalty, float temperature, int top_k, float top_p,
-              unsigned long long seed, const int* __restrict__ sequence_index, unsigned int step,
+              unsigned long long seed, const unsigned long long* __restrict__ seed_from,
+              const int* __restrict__ sequence_index, unsigned int step,
               const unsigned int* __restrict__ step_add, int* __restrict__ out_ids, double* out_u, const Gathered pre) {
     pdl_wait();
     pdl_launch_dependents();
+    if (seed_from) seed = *seed_from;
     extern __shared__ __align__(8) unsigned char sample_smem[];      // a histogram per warp: [warps][256] masses, then counts
     double* whist = reinterpret_cast<double*>(sample_smem);
     int* whist_n = reinterpret_cast<int*>(whist + SAMPLE_WARPS * 256);
@@ -903,9 +906,9 @@ extern "C" int qwb_sample_scratch_bytes(int B, int V, float temperature, int top
 // counters: [B][1 + 1024] int, zero before the first call (the kernels leave them zero), needed with scratch.
 extern "C" int qwb_sample(float* logits, int B, int V, const int* recent, int window, float repeat_penalty,
                           float presence_penalty, float frequency_penalty, float temperature, int top_k, float top_p,
-                          unsigned long long seed, const int* sequence_index, unsigned int step,
-                          const unsigned int* step_add, int* out_ids, double* out_u, void* scratch, int* counters,
-                          cudaStream_t stream) {
+                          unsigned long long seed, const unsigned long long* seed_from, const int* sequence_index,
+                          unsigned int step, const unsigned int* step_add, int* out_ids, double* out_u, void* scratch,
+                          int* counters, cudaStream_t stream) {
     if (B <= 0) return 0;
     if (V <= 0) return qwb_fail(QWB_ERR_ARG, "sample: bad vocabulary size %d", V);
     if (temperature > 0.f && !(top_p > 0.f)) return qwb_fail(QWB_ERR_ARG, "sample: top_p must be > 0, got %g", (double)top_p);
@@ -950,7 +953,7 @@ extern "C" int qwb_sample(float* logits, int B, int V, const int* recent, int wi
         pre.chunk = chunk;
     }
     qwb_launch(sample_kernel, B, SAMPLE_THREADS, smem, stream, logits, V, recent, window, repeat_penalty, presence_penalty,
-                                                   frequency_penalty, temperature, top_k, top_p, seed, sequence_index,
-                                                   step, step_add, out_ids, out_u, pre);
+                                                   frequency_penalty, temperature, top_k, top_p, seed, seed_from,
+                                                   sequence_index, step, step_add, out_ids, out_u, pre);
     return qwb_check_launch("sample");
 }

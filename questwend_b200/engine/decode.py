@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import gc
 
+import numpy as np
 import torch
 
 from ..kernels import ops
@@ -25,6 +26,8 @@ from ..sampling.params import SamplingParams
 
 
 MIN_BUCKET = 256
+N_SCALARS = 4               # int32 words before the rows of the state buffer: seed (two words), step, one unused
+N_ROWS = 7
 GRAPH_AFTER = 2             # plain steps at a batch size and length bound before a graph is captured for them
 
 
@@ -38,32 +41,42 @@ def length_bucket(n_tokens: int) -> int:
 class DecodeRunner:
     """Fixed buffers and graphs for decode steps of ``batch`` sequences with one sampling setup."""
 
-    def __init__(self, engine, batch: int, sampling: SamplingParams, seed: int, use_graph: bool = True):
+    def __init__(self, engine, batch: int, sampling: SamplingParams, use_graph: bool = True):
         self.engine = engine
         self.B = B = batch
         self.sampling = sampling
-        self.seed = seed
         self.use_graph = use_graph
+        if GRAPH_AFTER < 1:
+            raise ValueError("a graph is captured only after a plain step has loaded the kernels")
         dev = engine.device
         cache = engine.cache
-        # int32 state: token_ids, tok_pos, pos0, seq_len, sequence_index, n_seen | constants: tok_seq, cu_seqlens, rows
-        self.state = torch.zeros((6, B), dtype=torch.int32, device=dev)
-        self.token_ids, self.tok_pos, self.pos0, self.seq_len, self.seq_index, self.n_seen = self.state.unbind(0)
+        # One int32 buffer, one copy per bind: [seed low, seed high, step, unused] then seven rows of B:
+        # token_ids, tok_pos, pos0, seq_len, sequence_index, n_seen, slot ids.  The seed, the step counter and the
+        # slot ids live on the device, so a captured graph holds none of them: it serves every batch of this size.
+        self.state_flat = torch.zeros((N_SCALARS + N_ROWS * B,), dtype=torch.int32, device=dev)
+        self.seed_word = self.state_flat[0:2].view(torch.int64)
+        self.step_counter = self.state_flat[2:3]
+        self.state = self.state_flat[N_SCALARS:].view(N_ROWS, B)
+        (self.token_ids, self.tok_pos, self.pos0, self.seq_len, self.seq_index, self.n_seen,
+         self.slot_ids) = self.state.unbind(0)
         self.tok_seq = torch.arange(B, dtype=torch.int32, device=dev)
         self.cu_seqlens = torch.arange(B + 1, dtype=torch.int32, device=dev)
         self.rows = torch.arange(B, dtype=torch.int32, device=dev)
-        self.step_counter = torch.zeros((1,), dtype=torch.int32, device=dev)
         self.sampled = torch.zeros((B,), dtype=torch.int32, device=dev)
         self.window = sampling.repeat_last_n if sampling.penalized else 0
         self.recent = (torch.full((B, self.window), -1, dtype=torch.int32, device=dev) if self.window else None)
         self.tables = {g: torch.zeros((B, cache.table_width), dtype=torch.int32, device=dev)
                        for g in range(cache.n_groups())}
-        self.state_host = torch.zeros((6, B), dtype=torch.int32).pin_memory()
+        self.tables_host = {g: torch.zeros((B, cache.table_width), dtype=torch.int32).pin_memory()
+                            for g in range(cache.n_groups())}
+        self.state_host = torch.zeros((N_SCALARS + N_ROWS * B,), dtype=torch.int32).pin_memory()
+        self._state_np = self.state_host.numpy()
         self.tokens_host = torch.zeros((B,), dtype=torch.int32).pin_memory()
         self.sampled_host = torch.zeros((B,), dtype=torch.int32).pin_memory()
         self._tokens_np = self.tokens_host.numpy()      # the same pinned memory, written and read without a tensor op
         self._sampled_np = self.sampled_host.numpy()
         self._sampled_on_host = False                   # the last step copied its ids to the host itself
+        self._copied = None                             # event: the pinned buffers' last copies to the device are done
         self.graphs: dict = {}                          # (length bound, with host copies) -> graph
         self._pool = None           # the graphs run one at a time: they share one pool of memory
         self.slots: list = []
@@ -72,31 +85,42 @@ class DecodeRunner:
         self._graph = {}            # with host copies or not -> the graph for the steps in this room
         self._plain_steps: dict = {}    # length bound -> plain steps run so far
         self.launches_per_step = 0
+        self.profile = None         # a StepProfile while someone wants to know where a step's time goes
+        self.last_step_how = ""     # "graph" or "plain"
 
     # ------------------------------------------------------------------ binding a batch
-    def bind(self, slots, tokens, sequence_indices, step: int, windows=None) -> None:
-        """Point the buffers at these sequences: ``tokens`` are the next inputs (one each)."""
+    def bind(self, slots, tokens, sequence_indices, step: int, windows=None, seed: int = 0) -> None:
+        """Point the buffers at these sequences: ``tokens`` are the next inputs (one each); ``seed`` and ``step`` key the
+        sampler's random streams.  One copy from pinned memory, no wait: the copy is ordered before the next step on the
+        stream, and the pinned buffer is written again only after the copy has been seen to finish."""
         assert len(slots) == self.B
+        B = self.B
         cache = self.engine.cache
         self.slots = list(slots)
         lens = [cache.length(s) for s in slots]
-        h = self.state_host
-        h[0] = torch.tensor(tokens, dtype=torch.int32)
-        h[1] = torch.tensor(lens, dtype=torch.int32)
-        h[2] = h[1]
-        h[3] = h[1] + 1
-        h[4] = torch.tensor(sequence_indices, dtype=torch.int32)
+        if self._copied is not None:
+            self._copied.synchronize()
+        h = self._state_np
+        seed &= (1 << 64) - 1
+        h[0:2] = np.array([seed & 0xFFFFFFFF, seed >> 32], dtype=np.uint32).view(np.int32)
+        h[2] = step
+        rows = h[N_SCALARS:].reshape(N_ROWS, B)
+        rows[0] = tokens
+        rows[1] = lens
+        rows[2] = lens
+        rows[3] = rows[1] + 1
+        rows[4] = sequence_indices
+        rows[5] = 0
+        rows[6] = slots
         if self.window:
-            rows = [w.row() for w in windows]
-            h[5] = torch.tensor([sum(1 for t in r if t >= 0) for r in rows], dtype=torch.int32)
-            self.recent.copy_(torch.tensor(rows, dtype=torch.int32))
-        else:
-            h[5] = 0
-        self.state.copy_(h, non_blocking=True)
-        self.step_counter.fill_(step)
+            recent = [w.row() for w in windows]
+            rows[5] = [sum(1 for t in r if t >= 0) for r in recent]
+            self.recent.copy_(torch.tensor(recent, dtype=torch.int32))
+        self.state_flat.copy_(self.state_host, non_blocking=True)
+        self._copied = torch.cuda.Event()
+        self._copied.record()
         self._pages_seen = [None] * cache.n_groups()
         self._room = 0
-        torch.cuda.current_stream().synchronize()      # the pinned buffer may be written again
 
     def set_tokens(self, tokens) -> None:
         """This step's input tokens from the host (pinned memory, one copy)."""
@@ -107,13 +131,13 @@ class DecodeRunner:
     def _context(self, max_len_bucket: int) -> StepContext:
         return StepContext(n_tokens=self.B, n_seqs=self.B, token_ids=self.token_ids, tok_seq=self.tok_seq,
                            tok_pos=self.tok_pos, cu_seqlens=self.cu_seqlens, pos0=self.pos0, seq_len=self.seq_len,
-                           slots=self.tok_seq, max_new=1, max_len=max_len_bucket, single_token=True,
-                           page_tables=self.tables, host_slots=self.slots)
+                           slots=self.slot_ids, max_new=1, max_len=max_len_bucket, single_token=True,
+                           page_tables=self.tables, host_slots=None)
 
     def _forward_and_sample(self, max_len_bucket: int) -> None:
         eng, p = self.engine, self.sampling
         logits = eng.model.forward(self._context(max_len_bucket), eng.unit_caches, self.rows)
-        ops.sample(logits, p.temperature, top_k=p.top_k, top_p=p.top_p, seed=self.seed,
+        ops.sample(logits, p.temperature, top_k=p.top_k, top_p=p.top_p, seed=0, seed_from=self.seed_word,
                    sequence_index=self.seq_index, step=0, step_add=self.step_counter, recent=self.recent,
                    repeat_penalty=p.repeat_penalty, presence_penalty=p.presence_penalty,
                    frequency_penalty=p.frequency_penalty, out=self.sampled)
@@ -124,11 +148,9 @@ class DecodeRunner:
                            n_seen=self.n_seen if self.window else None)
 
     def _capture(self, bucket: int, host_copies: bool):
-        # one plain run first: it loads the kernels and sets their attributes; it writes only what
-        # the captured run writes again (this step's keys and values, the sampled ids)
-        if host_copies:
-            self.token_ids.copy_(self.tokens_host, non_blocking=True)
-        self._forward_and_sample(bucket)
+        # Plain steps at this batch size and length bound came before (GRAPH_AFTER): they loaded the kernels, set their
+        # attributes and let the few-rows products settle their choices.  No extra run here: a mixer with state of its
+        # own would count a token twice.
         torch.cuda.current_stream().synchronize()
         g = torch.cuda.CUDAGraph()
         before = ops.LAUNCHES[0]
@@ -172,12 +194,18 @@ class DecodeRunner:
                 counts = [len(cache._groups[g].pages[s]) for s in self.slots]
                 if counts != self._pages_seen[g]:
                     self._pages_seen[g] = counts
-                    self.tables[g].copy_(torch.from_numpy(cache.page_table_host(g, self.slots)))
+                    if self._copied is not None:
+                        self._copied.synchronize()
+                    self.tables_host[g].numpy()[:] = cache.page_table_host(g, self.slots)
+                    self.tables[g].copy_(self.tables_host[g], non_blocking=True)
+                    self._copied = torch.cuda.Event()
+                    self._copied.record()
                 room = min(room, min(c * ops.PAGE_SIZE - n for c, n in zip(counts, lengths)))
             self._bucket = length_bucket(max(lengths) + 1)
             self._room = min(room, self._bucket - max(lengths))
             self._graph = {}
         self._room -= 1
+        prof = self.profile
         with torch.cuda.device(self.engine.device):
             graph = self._graph.get(host_copies)
             if self.use_graph and graph is None:
@@ -188,6 +216,9 @@ class DecodeRunner:
                     # end one after the other passes through many sizes for a step or two each)
                     graph = self.graphs[key] = self._capture(self._bucket, host_copies)
                 self._graph[host_copies] = graph
+            if prof:
+                prof.launching()
+            self.last_step_how = "graph" if graph is not None else "plain"
             if graph is not None:
                 graph.replay()
             else:
@@ -200,6 +231,8 @@ class DecodeRunner:
                 self._plain_steps[self._bucket] = self._plain_steps.get(self._bucket, 0) + 1
                 if host_copies:
                     self.sampled_host.copy_(self.sampled, non_blocking=True)
+            if prof:
+                prof.launched()
         self._sampled_on_host = host_copies
         for s in self.slots:
             cache.advance(s, 1)

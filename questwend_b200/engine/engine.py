@@ -197,15 +197,18 @@ class Engine:
         self.steps_run += 1
         return logits
 
-    def decode_runner(self, batch: int, sampling, seed: int, use_graph: bool = True):
-        """The fixed buffers and CUDA graphs for decode steps of ``batch`` sequences (made once, kept)."""
+    def decode_runner(self, batch: int, sampling, use_graph: bool = True):
+        """The fixed buffers and CUDA graphs for decode steps of ``batch`` sequences (made once, kept).  The sampling
+        options without the seed key it: the seed lives on the device and is given with ``bind``."""
+        import dataclasses
         from .decode import DecodeRunner
-        key = (batch, sampling, seed, use_graph)
+        sampling = dataclasses.replace(sampling, seed=0)
+        key = (batch, sampling, use_graph)
         runner = self._runners.get(key)
         if runner is None:
             if len(self._runners) >= 16:             # graphs hold memory: drop the oldest
                 self._runners.pop(next(iter(self._runners)))
-            runner = self._runners[key] = DecodeRunner(self, batch, sampling, seed, use_graph)
+            runner = self._runners[key] = DecodeRunner(self, batch, sampling, use_graph)
         return runner
 
     # ------------------------------------------------------------------ facts

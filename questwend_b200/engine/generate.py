@@ -14,6 +14,7 @@ device, so they can be followed with any object that has ``open_sequences``,
 """
 from __future__ import annotations
 
+import os
 import time
 from dataclasses import dataclass, field
 
@@ -71,46 +72,121 @@ def plan_batches(prompt_lengths, max_new_tokens: int, max_batch: int, max_tokens
     return batches
 
 
+class StepProfile:
+    """Where a decode step's time goes, one line a step on ``out`` (the reference prints build / input / compute per
+    token under QWEN_PROF, core/runtime.cpp:1769, 1821-1825):
+
+      loop    the generation loop between two steps (stop tests, results, who goes on)
+      host    preparing the step on the host (binding a changed batch, the step's tokens, page bookkeeping)
+      launch  starting the step's work (a graph replay, or every kernel launch of a plain step)
+      wait    waiting for the sampled ids
+      device  the step on the device, between two CUDA events on the stream
+    """
+
+    def __init__(self, out=None, clock=time.perf_counter):
+        import sys
+        self.out = out if out is not None else sys.stderr
+        self.clock = clock
+        self.rows: list = []
+        self._last_end = None
+        self._events = None
+
+    def begin(self):
+        import torch
+        t = self.clock()
+        self._loop = 0.0 if self._last_end is None else t - self._last_end
+        self._t0 = t
+        self._events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+
+    def launching(self):
+        self._t1 = self.clock()
+        self._events[0].record()
+
+    def launched(self):
+        self._events[1].record()
+        self._t2 = self.clock()
+
+    def end(self, step: int, batch: int, how: str):
+        t3 = self.clock()
+        self._events[1].synchronize()
+        row = {"step": step, "batch": batch, "how": how, "loop_ms": self._loop * 1e3, "host_ms": (self._t1 - self._t0) * 1e3,
+               "launch_ms": (self._t2 - self._t1) * 1e3, "wait_ms": (t3 - self._t2) * 1e3,
+               "device_ms": self._events[0].elapsed_time(self._events[1])}
+        self.rows.append(row)
+        print("[prof] step=%d batch=%d %s loop=%.3f host=%.3f launch=%.3f wait=%.3f device=%.3f ms" % (
+            step, batch, how, row["loop_ms"], row["host_ms"], row["launch_ms"], row["wait_ms"], row["device_ms"]),
+            file=self.out)
+        self._last_end = self.clock()
+
+
 class _PlainStepper:
     """Decode steps through ``engine.step`` and a sampler callable."""
 
-    def __init__(self, engine, sampler, slot_of, windows):
+    def __init__(self, engine, sampler, slot_of, windows, profile=None):
         self.engine, self.sampler, self.slot_of, self.windows = engine, sampler, slot_of, windows
+        self.profile = profile
 
     def run(self, active, tokens, step):
-        logits = self.engine.step([StepEntry(self.slot_of[i], [t], [0]) for i, t in zip(active, tokens)])
-        return self.sampler(logits, active, step, [self.windows[i] for i in active])
+        prof = self.profile
+        if prof:
+            prof.begin()
+        entries = [StepEntry(self.slot_of[i], [t], [0]) for i, t in zip(active, tokens)]
+        if prof:
+            prof.launching()
+        logits = self.engine.step(entries)
+        if prof:
+            prof.launched()
+        ids = self.sampler(logits, active, step, [self.windows[i] for i in active])
+        if prof:
+            prof.end(step, len(active), "plain")
+        return ids
 
 
 class _GraphStepper:
     """Decode steps replayed from CUDA graphs (``DecodeRunner``); rebinds when the batch changes."""
 
-    def __init__(self, engine, sampling, seed, slot_of, windows):
+    def __init__(self, engine, sampling, seed, slot_of, windows, profile=None):
         self.engine, self.sampling, self.seed = engine, sampling, seed
         self.slot_of, self.windows = slot_of, windows
         self.bound = None
         self.runner = None
+        self.profile = profile
 
     def run(self, active, tokens, step):
+        prof = self.profile
+        if prof:
+            prof.begin()
         if self.bound != active:
-            self.runner = self.engine.decode_runner(len(active), self.sampling, self.seed)
+            self.runner = self.engine.decode_runner(len(active), self.sampling)
             self.runner.bind([self.slot_of[i] for i in active], tokens, active, step,
-                             [self.windows[i] for i in active])
+                             [self.windows[i] for i in active], seed=self.seed)
             self.bound = list(active)
+        if prof:
+            self.runner.profile = prof
         self.runner.step(host_tokens=tokens)
-        return self.runner.read_sampled()
+        ids = self.runner.read_sampled()
+        if prof:
+            self.runner.profile = None
+            prof.end(step, len(active), self.runner.last_step_how)
+        return ids
 
 
 def generate(engine, prompts, max_new_tokens: int = 128, sampling: SamplingParams = GREEDY,
              stop_ids=None, ignore_eos: bool = False, sampler=None, stats: GenerationStats | None = None,
-             clock=time.perf_counter, use_graph: bool = True) -> list[GenerationResult]:
+             clock=time.perf_counter, use_graph: bool = True, profile=None) -> list[GenerationResult]:
     """Generate for every prompt (a list of token ids each).
 
     stop_ids    tokens that end a sequence; default: the model's own (``eos_token_id``)
     ignore_eos  never stop on a token (benchmarks)
     sampler     ``(logits, sequence_indices, step, windows) -> list of ids``; default: the device sampler
     use_graph   replay decode steps from CUDA graphs (needs the default sampler)
+    profile     a ``StepProfile``, or True for one that prints to stderr: a line per decode step that says where its
+                time went (also switched on by the environment variable QWB200_PROF=1)
     """
+    if profile is None and os.environ.get("QWB200_PROF", "0") not in ("", "0"):
+        profile = True
+    if profile is True:
+        profile = StepProfile()
     prompts = [list(p) for p in prompts]
     for i, p in enumerate(prompts):
         if not p:
@@ -128,7 +204,11 @@ def generate(engine, prompts, max_new_tokens: int = 128, sampling: SamplingParam
     results = [GenerationResult(prompt_tokens=len(p)) for p in prompts]
     max_seq_len = engine.cache.max_seq_len
 
-    for batch in plan_batches([len(p) for p in prompts], max_new_tokens, engine.max_batch,
+    max_batch = engine.max_batch
+    held = getattr(engine.cache, "slots", None)
+    if held is not None:                    # slots that someone else holds meanwhile are not this call's to plan with
+        max_batch = max(1, min(max_batch, held.n_free))
+    for batch in plan_batches([len(p) for p in prompts], max_new_tokens, max_batch,
                               engine.cache.max_tokens, max_seq_len):
         stats.batches += 1
         slots = engine.open_sequences(len(batch))
@@ -136,8 +216,8 @@ def generate(engine, prompts, max_new_tokens: int = 128, sampling: SamplingParam
         windows = {i: PenaltyWindow(sampling, prompts[i]) for i in batch}
         length = {i: len(prompts[i]) for i in batch}
         active = list(batch)
-        stepper = (_GraphStepper(engine, sampling, sampler.seed, slot_of, windows) if graph_path
-                   else _PlainStepper(engine, sampler, slot_of, windows))
+        stepper = (_GraphStepper(engine, sampling, sampler.seed, slot_of, windows, profile) if graph_path
+                   else _PlainStepper(engine, sampler, slot_of, windows, profile))
         try:
             t0 = clock()
             want_last = max_new_tokens > 0

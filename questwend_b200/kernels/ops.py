@@ -488,8 +488,10 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int = 0, top_p: floa
            sequence_index: torch.Tensor | None = None, step: int = 0, recent: torch.Tensor | None = None,
            repeat_penalty: float = 1.0, presence_penalty: float = 0.0, frequency_penalty: float = 0.0,
            out_u: torch.Tensor | None = None, step_add: torch.Tensor | None = None,
-           out: torch.Tensor | None = None, split: bool = True) -> torch.Tensor:
+           out: torch.Tensor | None = None, split: bool = True, seed_from: torch.Tensor | None = None) -> torch.Tensor:
     """One token id per row of float32 ``logits`` [B, V] (changed in place by penalties).
+    ``seed_from``: one int64 on the device that holds the seed (``seed`` is then not used); ``step_add``: one int32 on
+    the device that is added to ``step``.  With both, a captured graph holds neither the seed nor the step.
     ``split`` False: one block per row whatever the sizes (the result is the same).  With few rows the kernels cut
     every row into chunks and count into one buffer per device: such calls must follow one another on one stream."""
     _need(logits, "logits", torch.float32, 2)
@@ -502,6 +504,8 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int = 0, top_p: floa
         _need(sequence_index, "sequence_index", torch.int32, 1)
     if out_u is not None:
         _need(out_u, "out_u", torch.float64, 1)
+    if seed_from is not None:
+        _need(seed_from, "seed_from", torch.int64, 1)
     if out is None:
         out = torch.empty((B,), dtype=torch.int32, device=logits.device)
     # few rows and a small top-k: the kernels cut every row into chunks and want scratch memory for what the chunks find
@@ -513,7 +517,7 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int = 0, top_p: floa
         counters = _sample_counters(logits.device, B)
     _call("sampling", "qwb_sample", _ptr(logits), _i(B), _i(V), _ptr(recent), _i(window), _f(repeat_penalty),
           _f(presence_penalty), _f(frequency_penalty), _f(temperature), _i(top_k), _f(top_p),
-          ctypes.c_ulonglong(seed & (2 ** 64 - 1)), _ptr(sequence_index), ctypes.c_uint(step & 0xFFFFFFFF),
+          ctypes.c_ulonglong(seed & (2 ** 64 - 1)), _ptr(seed_from), _ptr(sequence_index), ctypes.c_uint(step & 0xFFFFFFFF),
           _ptr(step_add), _ptr(out), _ptr(out_u), _ptr(scratch), _ptr(counters), _stream(), kernels=3 if scratch_bytes else 1)
     return out
 

@@ -9,6 +9,7 @@ import math
 import torch
 
 from ..kernels import ops
+from ..kernels.limits import head_dim_refusal
 from ..weights.manifest import MATRIX, NORM_WEIGHT, VECTOR, TensorSpec
 from .base import KVSpec, Mixer
 from .linear import kernel_modules as linear_modules, linear
@@ -45,6 +46,9 @@ class GroupedQueryAttention(Mixer):
         self.rotary_dim = getattr(position, "rotary_dim", 0) if position is not None else 0
         if self.n_heads % self.n_kv_heads:
             raise ValueError(f"{self.n_heads} heads are not a multiple of {self.n_kv_heads} key/value heads")
+        refusal = head_dim_refusal(self.head_dim)           # now, and not at the first step with the weights loaded
+        if refusal:
+            raise ValueError(f"grouped-query attention '{self.prefix}': parameter 'head_dim': {refusal}")
         if self.rotary_dim > self.head_dim:
             raise ValueError(f"rotary size {self.rotary_dim} exceeds the head size {self.head_dim}")
         self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None

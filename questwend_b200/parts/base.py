@@ -67,12 +67,13 @@ class StepContext:
     cu_seqlens: torch.Tensor    # [B + 1] start of each sequence's tokens in the packed order
     pos0: torch.Tensor          # [B] each sequence's length before this step
     seq_len: torch.Tensor       # [B] each sequence's length after this step
-    slots: torch.Tensor         # [B] cache slot of each sequence
+    slots: torch.Tensor         # [B] cache slot of each sequence: the row of its fixed-size state (``UnitCache.state``)
     max_new: int                # most new tokens of any sequence
     max_len: int                # longest sequence after this step
     single_token: bool          # every sequence brings exactly one token
     page_tables: dict           # cache group id -> [B, width] int32 pages of each sequence
-    host_slots: list            # the slots again, as Python ints
+    host_slots: list | None     # the slots again, as Python ints; None in a step that may be replayed from a CUDA graph
+                                # (generation's single-token steps): a part that runs there reads no value on the host
     shared: dict = field(default_factory=dict)   # per-step values shared between layers (rotation tables)
 
 

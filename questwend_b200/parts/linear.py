@@ -48,12 +48,21 @@ def _stream_rows(M: int, weight: torch.Tensor) -> bool:
 # Which few-rows product is fastest depends on the matrix: at 8 rows the own kernel needs 19 us for Qwen3-8B's down
 # projection where the library needs 31, and 62 us for Qwen3-32B's where the library needs 45.  So for matrices large
 # enough to matter, the first step that meets a shape (rows up to 8, or 9 to 16; plain, residual-add or SwiGLU) times
-# the candidates once, each on a cold L2 as inside a step, and the choice is kept for the process.
+# the candidates once, each on a cold L2 as inside a step, and the choice is kept for the process -- if QWB200_TUNE=1 asks
+# for it (``bench.py`` does, for the largest model).  By default the choice follows from the shape alone, so that the same
+# trace gives the same bits in every process; ``tuned_choices()`` tells what a tuned process chose.
 TUNE_MIN_WEIGHT_BYTES = 8 << 20     # smaller matrices stay in L2 anyway and every choice is at its launch floor
-TUNE = os.environ.get("QWB200_TUNE", "1") != "0"
+TUNE = os.environ.get("QWB200_TUNE", "0") == "1"      # off unless asked for: a timed choice can differ from run to run, and
+                                                      # with it the order of a sum and a logit's last bits
 LIBRARY_MUST_WIN_BY = 0.90          # the own kernel starts under the tail of the kernel before it, the library's does not
 CHANGE_MUST_WIN_BY = 0.92           # what the usual choice must lose by before another is taken
 _CHOICES: dict = {}                 # (device, N, K, rows, kind) -> ("stream", (u, w) or None) | ("library", None)
+
+
+def tuned_choices() -> dict:
+    """What the measuring has chosen so far in this process: {(N, K, rows up to, kind): "stream u x w" or "library"}."""
+    return {k[1:]: ("library" if how == "library" else f"stream {cfg[0]}x{cfg[1]}" if cfg else "stream")
+            for k, (how, cfg) in _CHOICES.items()}
 
 
 def _library(x, weight, add_to, kind, interleave):

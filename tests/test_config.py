@@ -73,6 +73,23 @@ def test_rejections_name_the_key(patch, word):
         config_from_dict({**TINY_A, **patch})
 
 
+@pytest.mark.parametrize("head_dim", [24, 320])
+def test_a_head_size_the_kernels_do_not_take_is_refused_before_any_weight_is_read(head_dim, tmp_path):
+    """Not at the first step, with gigabytes of weights on the device: when the configuration is read, with the key's
+    name; and, for an architecture whose configuration does not check, when the attention part is built."""
+    with pytest.raises(ConfigError, match="key 'head_dim'.*multiples of 16"):
+        config_from_dict({**TINY_A, "head_dim": head_dim})
+    with pytest.raises(ConfigError, match="'hidden_size' / 'num_attention_heads'"):
+        config_from_dict({k: v for k, v in {**TINY_A, "hidden_size": 4 * head_dim}.items() if k != "head_dim"})
+    import torch
+    from questwend_b200.parts import PartSpec, Runtime, build_part
+    spec = PartSpec("gqa", {"hidden_size": 64, "n_heads": 4, "n_kv_heads": 2, "head_dim": head_dim}, prefix="layers.0.mix.")
+    with pytest.raises(ValueError, match="layers.0.mix.*'head_dim'.*multiples of 16"):
+        build_part("mixer", spec, Runtime(torch.device("cpu"), torch.float32))
+    build_part("mixer", PartSpec("gqa", {"hidden_size": 64, "n_heads": 4, "n_kv_heads": 2, "head_dim": 48}),
+               Runtime(torch.device("cpu"), torch.float32))
+
+
 def test_unknown_architecture_lists_the_known():
     with pytest.raises(ConfigError, match="Qwen3ForCausalLM"):
         config_from_dict({**TINY_A, "architectures": ["NoSuchModel"]})

@@ -218,3 +218,27 @@ def test_command_line(folders, tmp_path):
     proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "qw-cli"), "-m", folder, "--info"],
                           capture_output=True, text=True, timeout=300)
     assert proc.returncode == 0 and '"parameters"' in proc.stdout
+
+
+def test_command_line_random_weights_and_step_profile(tmp_path):
+    """``--random <config.json> --seed N``: weights drawn from the seed (with ``--save`` into a folder that the plain
+    implementation reads too); ``--profile-step``: a line per decode step."""
+    import json, os, subprocess, sys
+    from helpers import ROOT, TINY_B
+    cfg_path = tmp_path / "b.json"
+    cfg_path.write_text(json.dumps(TINY_B))
+    cli = [sys.executable, os.path.join(ROOT, "bin", "qw-cli")]
+    saved = str(tmp_path / "saved")
+    proc = subprocess.run(cli + ["--random", str(cfg_path), "--seed", "4", "--save", saved, "-p", "3 14 15", "-n", "6",
+                                 "--dtype", "float32", "--ignore-eos", "--profile-step"],
+                          capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr
+    cfg, w = pm.read_model_folder(saved)
+    assert [int(x) for x in proc.stdout.split()] == pm.greedy_continue(cfg, w, [3, 14, 15], 6)
+    prof = [line for line in proc.stderr.splitlines() if line.startswith("[prof] step=")]
+    assert len(prof) == 5 and all("device=" in line and "wait=" in line for line in prof)
+    proc = subprocess.run(cli + ["--random", str(cfg_path), "--seed", "4", "-p", "3 14 15", "-p", "7", "-n", "4", "--ignore-eos"],
+                          capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr
+    lines = proc.stdout.strip().splitlines()
+    assert len(lines) == 2 and all(len(line.split()) == 4 for line in lines)

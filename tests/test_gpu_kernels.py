@@ -426,6 +426,26 @@ def test_gemm_stream(M, N, K):
         ops.gemm_stream(torch.zeros(17, K, dtype=torch.bfloat16, device=DEV), w)
 
 
+@pytest.mark.parametrize("config", ops.STREAM_CONFIGS)
+@pytest.mark.parametrize("M", [2, 8, 13])
+def test_gemm_stream_in_every_form(M, config):
+    """Every (loads in flight, warps) form of the few-rows product, chosen by hand as the measuring in ``parts.linear`` may
+    choose it: plain, residual-add and SwiGLU, at a width and a length that are no multiples of the forms' tiles."""
+    N, K = 1192, 4136
+    g = torch.Generator().manual_seed(M)
+    x = (torch.randn(M, K, generator=g) * 0.3).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(N, K, generator=g) * 0.3).to(torch.bfloat16).to(DEV)
+    ref = f64(x) @ f64(w).T
+    close(ops.gemm_stream(x, w, config=config), ref, torch.float32, scale=np.abs(ref).max() * 4)
+    res = torch.randn(M, N, generator=g).to(DEV)
+    close(ops.gemm_stream(x, w, residual=res.clone(), config=config), f64(res) + ref, torch.float32,
+          scale=np.abs(ref).max() * 4)
+    F = N // 2
+    out = ops.gemm_stream_swiglu(x, ops.interleave_gate_up(w[:F], w[F:]), config=config)
+    close(out, pm.swiglu(ref[:, :F], ref[:, F:]), torch.bfloat16)
+    assert torch.equal(ops.gemm_stream(x[:1], w, config=config)[0], ops.gemm_stream(x, w, config=config)[0])
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 256), (300, 200, 200), (17, 96, 1032), (512, 1024, 4096),
                                    (1, 64, 64), (129, 136, 72)])
 @pytest.mark.parametrize("tile_n", [64, 128, 256])

@@ -182,8 +182,10 @@ def test_few_row_products_choose_by_measuring(monkeypatch):
 
 # ----------------------------------------------------------------------------- a toy architecture, defined here
 class RunningMeanMixer(Mixer):
-    """y_t = mean(x_0..x_t) W.  Keeps, per sequence, the running sum and the count: fixed-size state,
-    no keys or values.  Written with torch operations; it is a test's toy, not a model."""
+    """y_t = mean(x_0..x_t) W.  Keeps, per sequence, the running sum and the count: fixed-size state, no keys or values.
+    The state rows are found with ``ctx.slots`` on the device and nothing is read on the host, so a step can be replayed
+    from a CUDA graph for whichever sequences are bound to it.  Written with torch operations; it is a test's toy, not a
+    model."""
 
     def __init__(self, spec, runtime, position=None):
         super().__init__(spec, runtime)
@@ -199,18 +201,19 @@ class RunningMeanMixer(Mixer):
         return StateSpec((self.hidden + 1,), torch.float32)
 
     def forward(self, x, ctx, cache):
-        out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
-        cu = ctx.cu_seqlens.tolist()
-        for b, slot in enumerate(ctx.host_slots):
-            xs = x[cu[b]:cu[b + 1]].float()
-            state = cache.state[slot]
-            sums = state[:-1] + torch.cumsum(xs, 0)
-            counts = state[-1] + torch.arange(1, xs.shape[0] + 1, device=x.device)
-            out[cu[b]:cu[b + 1]] = (sums / counts[:, None]).to(x.dtype).float() @ self.w.float().T
-            if cache.writable:
-                state[:-1] = sums[-1]
-                state[-1] = counts[-1]
-        return out
+        seq = ctx.tok_seq.long()                                  # [T] batch row of each token
+        slot = ctx.slots.long()                                   # [B] state row of each sequence
+        state = cache.state.index_select(0, slot).double()        # [B, D + 1]
+        running = torch.cumsum(x.double(), 0)                     # over the packed tokens; each sequence subtracts what
+        first = ctx.cu_seqlens[:-1].long()                        # had run up before its own first token
+        before = running.index_select(0, (first - 1).clamp(min=0)) * (first > 0)[:, None]
+        sums = state[:, :-1].index_select(0, seq) + running - before.index_select(0, seq)
+        counts = state[:, -1].index_select(0, seq) + (ctx.tok_pos - ctx.pos0.index_select(0, seq) + 1)
+        if cache.writable:
+            last = ctx.cu_seqlens[1:].long() - 1
+            new = torch.cat([sums.index_select(0, last), counts.index_select(0, last)[:, None]], dim=1)
+            cache.state.index_copy_(0, slot, new.float())
+        return (sums / counts[:, None]).to(x.dtype).float() @ self.w.float().T
 
 
 @dataclass(frozen=True)
@@ -247,11 +250,54 @@ def toy_plan(cfg: ToyConfig) -> ModelPlan:
                                               "tied_to": "emb.weight"}))
 
 
-def test_toy_mixer_with_state_of_its_own():
+def toy_plain_logits(w, tokens):
+    """The toy architecture once more in NumPy float64, whole sequences, no cache and no state: what the engine's
+    schedule, cache and state rows have to reproduce."""
+    T = len(tokens)
+    eps = 1e-5
+
+    def feed_forward(h, px):
+        x = pm.rms_norm(h, w[px + "n2.weight"], eps)
+        a = pm.swiglu(pm.linear(x, w[px + "ff.gate_proj.weight"]), pm.linear(x, w[px + "ff.up_proj.weight"]))
+        return h + pm.linear(a, w[px + "ff.down_proj.weight"])
+
+    def running_mean(h, px):
+        x = pm.rms_norm(h, w[px + "n1.weight"], eps)
+        mean = np.cumsum(x, 0) / np.arange(1, T + 1)[:, None]
+        return feed_forward(h + pm.linear(mean, w[px + "mix.w.weight"]), px)
+
+    def attention(h, px, kv=None):
+        x = pm.rms_norm(h, w[px + "n1.weight"], eps)
+        ang = pm.rope_angles(np.arange(T), 16, 1e4)
+        q = pm.apply_rope_neox(pm.linear(x, w[px + "mix.q_proj.weight"]).reshape(T, 2, 16), ang, 16)
+        if kv is None:
+            k = pm.apply_rope_neox(pm.linear(x, w[px + "mix.k_proj.weight"]).reshape(T, 1, 16), ang, 16)
+            kv = (k, pm.linear(x, w[px + "mix.v_proj.weight"]).reshape(T, 1, 16))
+        att = pm.attention_causal(q, kv[0], kv[1]).reshape(T, 32)
+        return feed_forward(h + pm.linear(att, w[px + "mix.o_proj.weight"]), px), kv
+
+    h = w["emb.weight"][np.asarray(tokens)]
+    h = running_mean(h, "layers.0.")
+    h, kv = attention(h, "layers.1.")
+    h = running_mean(h, "layers.2.")
+    h, _ = attention(h, "layers.1.", kv)              # the same layer again, with the first run's keys and values
+    h = running_mean(h, "layers.0.")                  # and the first layer again, with a state of its own
+    return pm.linear(pm.rms_norm(h, w["norm.weight"], eps), w["emb.weight"])
+
+
+@pytest.fixture(scope="module")
+def toy_model(tmp_path_factory):
+    import questwend_b200 as qw
     register_mixer("toy_running_mean", RunningMeanMixer, replace=True)
     register_architecture("ToyStateForCausalLM", ToyConfig, toy_plan, replace=True)
-    cfg = ToyConfig(32, 40)
-    eng = Engine.from_config(cfg, seed=7, dtype="float32", max_tokens=512)
+    folder = str(tmp_path_factory.mktemp("toy_state"))
+    qw.write_model_folder(folder, ToyConfig(32, 40), seed=7, dtype="float32")
+    return folder, pm.read_safetensors(folder + "/model.safetensors")
+
+
+def test_toy_mixer_with_state_of_its_own(toy_model):
+    folder, w = toy_model
+    eng = Engine.from_folder(folder, dtype="float32", max_tokens=512)
     units = eng.model.cache_units()
     assert [u[0] is not None for u in units] == [False, True, False, True, False]
     assert [u[1] is not None for u in units] == [True, False, True, False, True]
@@ -259,9 +305,14 @@ def test_toy_mixer_with_state_of_its_own():
     assert eng.unit_caches[0].state.data_ptr() != eng.unit_caches[4].state.data_ptr()   # a layer run twice: two states
     rng = np.random.default_rng(0)
     seqs = [rng.integers(0, 40, n).tolist() for n in (23, 5, 70)]
+    refs = [toy_plain_logits(w, t) for t in seqs]
     slots = eng.open_sequences(3)
     whole = eng.step([StepEntry(s, t, list(range(len(t)))) for s, t in zip(slots, seqs)]).cpu().numpy()
     eng.close_sequences(slots)
+    off = 0
+    for t, ref in zip(seqs, refs):
+        assert rel_err(whole[off:off + len(t)], ref) < FP32_TOL
+        off += len(t)
     # the same sequences: a prompt of a few tokens, then token by token, in slots that were used before
     slots = eng.open_sequences(3)
     rows = {i: [] for i in range(3)}
@@ -279,8 +330,39 @@ def test_toy_mixer_with_state_of_its_own():
         done = [i for i in live if pos[i] == len(seqs[i])]
         eng.close_sequences([slots[i] for i in done])
         live = [i for i in live if i not in done]
-    off = 0
-    for i, t in enumerate(seqs):
-        assert rel_err(np.stack(rows[i]), whole[off:off + len(t)]) < FP32_TOL
-        off += len(t)
+    for i, ref in enumerate(refs):
+        assert rel_err(np.stack(rows[i]), ref) < FP32_TOL
+    assert eng.cache.slots.n_free == eng.max_batch
+
+
+@pytest.mark.parametrize("use_graph", [True, False])
+def test_toy_state_through_the_generation_loop(toy_model, use_graph):
+    """Generation's decode steps (replayed from CUDA graphs, or plain) on the model whose mixer keeps state: two batches one
+    after the other, in slots that are not 0..B-1 (another sequence holds slot 0 meanwhile) and that are used again, one
+    sequence ending early at a stop token.  Every token is checked against the NumPy model fed the same tokens."""
+    import questwend_b200 as qw
+    folder, w = toy_model
+    eng = Engine.from_folder(folder, dtype="float32", max_tokens=1024, max_batch=3)
+    rng = np.random.default_rng(5)
+    prompts = [rng.integers(0, 40, n).tolist() for n in (9, 2, 30, 1, 14)]
+    (held,) = eng.open_sequences(1)                          # generation gets slots 1 and 2
+    assert held == 0
+    eng.step([StepEntry(held, [1, 2, 3], [])])
+    n_new = 14
+    free = qw.generate(eng, prompts, max_new_tokens=n_new, ignore_eos=True, use_graph=use_graph)
+    stop = free[2].tokens[5]                                 # ends the third sequence (at least) early
+    stats = qw.GenerationStats()
+    res = qw.generate(eng, prompts, max_new_tokens=n_new, stop_ids=[stop], use_graph=use_graph, stats=stats)
+    assert stats.batches == 3 and res[2].finish_reason == "stop" and len(res[2].tokens) <= 5
+    for run in (free, res):
+        for p, r in zip(prompts, run):
+            ref = toy_plain_logits(w, p + r.tokens)
+            scale = np.abs(ref).max()
+            for j, tok in enumerate(r.tokens):
+                row = ref[len(p) - 1 + j]
+                assert row.max() - row[tok] <= 2 * FP32_TOL * scale, (
+                    f"prompt of {len(p)}, new token {j}: the engine chose {tok}, the NumPy model {int(row.argmax())}")
+            if r.finish_reason == "stop":
+                assert int(ref[len(p) - 1 + len(r.tokens)].argmax()) == stop
+    eng.close_sequences([held])
     assert eng.cache.slots.n_free == eng.max_batch

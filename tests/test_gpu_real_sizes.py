@@ -61,3 +61,71 @@ def test_float32_prompt_then_tokens(model):
     ref = pm.forward_logits(cfg, w, toks)
     eng = qw.Engine.from_folder(folder, dtype="float32", max_tokens=1024)
     assert rel_err(run_cut(eng, toks, [150] + [1] * 50), ref) < FP32_TOL
+
+
+def test_bfloat16_unequal_batch_that_shrinks(model):
+    """24 sequences with unequal prompts start together and end at different steps, so that the decode steps have 24, 17,
+    16, 9, 8 and 1 rows: at these widths each of those counts takes other kernels (the few-rows product's forms, the
+    library), and each sequence must get the logits it gets alone."""
+    folder, cfg, w = model
+    rng = np.random.default_rng(4)
+    decode_steps = [1] * 7 + [2] + [3] * 7 + [4] + [5] * 7 + [7]
+    rng.shuffle(decode_steps)
+    heads = rng.integers(1, 20, 24).tolist()
+    heads[:3] = [1, 64, 70]
+    seqs = [rng.integers(0, cfg["vocab_size"], h + d).tolist() for h, d in zip(heads, decode_steps)]
+    eng = qw.Engine.from_folder(folder, dtype="bfloat16", max_tokens=24 * 64 + 128, max_batch=24)
+    slots = eng.open_sequences(24)
+    got = [[] for _ in seqs]
+    first = eng.step([qw.StepEntry(s, t[:h], list(range(h))) for s, t, h in zip(slots, seqs, heads)]).cpu().numpy()
+    off = 0
+    for i, h in enumerate(heads):
+        got[i] += list(first[off:off + h])
+        off += h
+    pos = list(heads)
+    live = list(range(24))
+    counts = []
+    while live:
+        counts.append(len(live))
+        out = eng.step([qw.StepEntry(slots[i], [seqs[i][pos[i]]], [0]) for i in live]).cpu().numpy()
+        for row, i in zip(out, live):
+            got[i].append(row)
+            pos[i] += 1
+        ended = [i for i in live if pos[i] == len(seqs[i])]
+        eng.close_sequences([slots[i] for i in ended])
+        live = [i for i in live if i not in ended]
+    assert counts == [24, 17, 16, 9, 8, 1, 1]
+    for i, t in enumerate(seqs):
+        ref = pm.forward_logits(cfg, w, t, round16="bf16")
+        err = np.abs(np.stack(got[i]) - ref).max(axis=1) / np.abs(ref).max()
+        assert err.max() < BF16_TOL, f"sequence {i} (prompt of {heads[i]}): position {int(np.argmax(err))} off by {err.max():.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_output_head_at_the_real_vocabulary(dtype):
+    """The head product at 151,936 rows of W (width 1,024 keeps it at 311 MB), for the row counts a step can bring: few
+    (the weight-streaming kernels), 9 to 16, and more (the library), against a float64 product of the same numbers."""
+    import torch
+    from questwend_b200.parts.base import PartSpec, Runtime
+    from questwend_b200.parts.registry import build_part
+    V, D = 151936, 1024
+    dev = torch.device("cuda:0")
+    tdtype = torch.bfloat16 if dtype == "bfloat16" else torch.float32
+    g = torch.Generator(device=dev).manual_seed(7)
+    W = (torch.randn((V, D), generator=g, device=dev) * 0.02).to(tdtype)
+    head = build_part("head", PartSpec("linear", {"vocab_size": V, "hidden_size": D, "tied": False,
+                                                  "name": "lm_head.weight", "tied_to": "embed"}), Runtime(dev, tdtype))
+    head.bind({"lm_head.weight": W})
+    cols = np.concatenate([np.arange(0, 300), np.arange(75000, 75300), np.arange(V - 300, V)])     # both ends and the middle
+    Wd = W[torch.from_numpy(cols).to(dev)].double().cpu().numpy()
+    for M in (1, 8, 13, 16, 24, 64):
+        x = torch.randn((M, D), generator=g, device=dev).to(tdtype)
+        y = head.forward(x)
+        assert tuple(y.shape) == (M, V) and y.dtype == torch.float32
+        ref = x.double().cpu().numpy() @ Wd.T
+        got = y[:, torch.from_numpy(cols).to(dev)].double().cpu().numpy()
+        assert rel_err(got, ref) < (1e-5 if dtype == "float32" else 1e-4), M
+        # every column is a sum of the same kind: the largest of all columns agrees with a float64 product of that row
+        top = y.argmax(dim=1)
+        ref_top = (x.double() @ W[top].double().t()).diagonal()
+        assert torch.allclose(y.gather(1, top[:, None])[:, 0].double(), ref_top, rtol=1e-3, atol=1e-4)

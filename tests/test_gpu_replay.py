@@ -97,3 +97,93 @@ def test_replay_agrees_with_the_plain_implementation(name, dtype, tmp_path):
             got_whole[r] = got
         else:                                                 # the ways of cutting agree with each other
             assert np.abs(got - got_whole[r]).max() / scale < tol
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Many live sequences.  A decode step's kernels change with its number of rows (up to 8, 9 to 16, 17 and more: other
+# forms of the few-rows product, library products, the separate q/k-norm + rotation kernel), so the batches here start
+# with 64 and 24 requests and shrink through 17, 16, 9, 8 and 1 as requests end.  The reference's own check of this kind
+# feeds one prompt whole and token by token (cli/main.cpp:313-337).
+# ---------------------------------------------------------------------------------------------------------------------
+# how many requests decode for how many steps; the live count after the prompts' step is then, step by step,
+# 64 64 44 17 17 16 16 9 9 8 8 4 4 1 1 1  and  24 17 16 9 8 1 1
+DECODE_STEPS_1 = [2] * 20 + [3] * 27 + [5] + [7] * 7 + [9] + [11] * 4 + [13] * 3 + [16]
+DECODE_STEPS_2 = [1] * 7 + [2] + [3] * 7 + [4] + [5] * 7 + [7]
+LIVE_COUNTS_1 = [64, 64, 44, 17, 17, 16, 16, 9, 9, 8, 8, 4, 4, 1, 1, 1]
+LIVE_COUNTS_2 = [24, 17, 16, 9, 8, 1, 1]
+
+
+def many_requests(rng, vocab):
+    """[(batch, prompt length, tokens)]: unequal prompts (some of one token, some across a page's edge), then as many
+    single tokens as the request decodes; which request ends when is shuffled, so that the ended ones lie anywhere in
+    the batch."""
+    out = []
+    for batch, decode_steps in enumerate((DECODE_STEPS_1, DECODE_STEPS_2)):
+        steps = list(decode_steps)
+        rng.shuffle(steps)
+        heads = rng.integers(1, 25, len(steps)).tolist()
+        heads[0], heads[1], heads[2], heads[3] = 1, 64, 63, 130
+        for h, d in zip(heads, steps):
+            out.append((batch, h, rng.integers(0, vocab, h + d).tolist()))
+    return out
+
+
+def build_many_traces(requests):
+    steps, where, live_counts = [], {}, {0: [], 1: []}
+    peak = 0
+    for r, (_, _, t) in enumerate(requests):                       # each request alone and whole
+        steps.append({"step": len(steps), "entries": [{"id": f"w{r}", "tokens": t, "want": list(range(len(t)))}],
+                      "end": [f"w{r}"]})
+        where[("whole", r)] = [(len(steps) - 1, i) for i in range(len(t))]
+    for batch in (0, 1):                                           # the second batch gets the first one's slots and pages
+        members = [r for r, q in enumerate(requests) if q[0] == batch]
+        peak = max(peak, sum(-(-len(requests[r][2]) // 64) * 64 for r in members))
+        pos = {r: requests[r][1] for r in members}
+        rows = {r: [] for r in members}
+        s, row = len(steps), 0
+        for r in members:
+            rows[r] += [(s, row + i) for i in range(pos[r])]
+            row += pos[r]
+        steps.append({"step": s, "entries": [{"id": f"m{r}", "tokens": requests[r][2][:pos[r]],
+                                              "want": list(range(pos[r]))} for r in members], "end": []})
+        live = list(members)
+        while live:
+            s = len(steps)
+            live_counts[batch].append(len(live))
+            entries = []
+            for i, r in enumerate(live):
+                entries.append({"id": f"m{r}", "tokens": [requests[r][2][pos[r]]], "want": [0]})
+                rows[r].append((s, i))
+                pos[r] += 1
+            ended = [r for r in live if pos[r] == len(requests[r][2])]
+            steps.append({"step": s, "entries": entries, "end": [f"m{r}" for r in ended]})
+            live = [r for r in live if r not in ended]
+        for r in members:
+            where[("batch", r)] = rows[r]
+    return steps, where, live_counts, peak
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_with_many_live_sequences(name, dtype, tmp_path):
+    cfgd, seed = TINY[name]
+    folder = make_folder(tmp_path / "model", cfgd, seed, dtype)
+    cfg, w = pm.read_model_folder(folder)
+    requests = many_requests(np.random.default_rng(seed + 40), cfgd["vocab_size"])
+    steps, where, live_counts, peak = build_many_traces(requests)
+    assert live_counts[0] == LIVE_COUNTS_1 and live_counts[1] == LIVE_COUNTS_2
+    out = run_trace(folder, dtype, steps, max_tokens=peak, out_dir=str(tmp_path / "out"))
+    tol = FP32_TOL if dtype == "float32" else BF16_TOL
+    whole = {}
+    for (phase, r), rows in sorted(where.items(), key=lambda kv: kv[0][0] != "whole"):
+        ref = pm.forward_logits(cfg, w, requests[r][2], round16=None if dtype == "float32" else "bf16")
+        got = np.stack([out[s][i] for s, i in rows]).astype(np.float64)
+        scale = np.abs(ref).max()
+        err = np.abs(got - ref).max(axis=1) / scale
+        bad = int(np.argmax(err > tol)) if (err > tol).any() else -1
+        assert bad < 0, (f"{phase}, request {r} (prompt of {requests[r][1]}): position {bad} of {len(ref)} is off by "
+                         f"{err[bad]:.3e} (tolerance {tol:.1e}); step {rows[bad][0]}, row {rows[bad][1]}")
+        if phase == "whole":
+            whole[r] = got
+        else:
+            assert np.abs(got - whole[r]).max() / scale < tol, f"request {r}: in the batch it differs from alone"

@@ -167,3 +167,23 @@ def test_sharded_folder(tmp_path):
     cfg = config_from_dict(TINY_A)
     w = load_tensors(d, get_architecture(cfg.architecture).plan(cfg).manifest(), torch.float32, "cpu")
     assert all(torch.equal(w[n], tensors[n]) for n in names)
+
+
+def test_command_line_writes_a_random_model_folder(tmp_path, capsys):
+    """``qw-cli --random <config.json> --seed N --save <folder>``: a folder from a configuration and a seed, the same numbers
+    as ``write_model_folder`` with that seed, without a GPU."""
+    import json
+    from questwend_b200 import cli
+    cfg_path = tmp_path / "b.json"
+    cfg_path.write_text(json.dumps(TINY_B))
+    out = tmp_path / "from_cli"
+    assert cli.main(["--random", str(cfg_path), "--seed", "3", "--save", str(out), "--dtype", "float32"]) == 0
+    assert capsys.readouterr().out.strip() == str(out)
+    other = make_folder(tmp_path / "direct", TINY_B, 3, "float32")
+    a, b = SafetensorsFile(str(out / "model.safetensors")), SafetensorsFile(other + "/model.safetensors")
+    assert sorted(a.names()) == sorted(b.names()) and all(torch.equal(a.tensor(k), b.tensor(k)) for k in a.names())
+    assert json.loads((out / "config.json").read_text())["num_hidden_layers"] == 3
+    with pytest.raises(SystemExit, match="either -m"):
+        cli.main(["--seed", "3"])
+    with pytest.raises(SystemExit, match="--save goes with --random"):
+        cli.main(["-m", other, "--save", str(out)])

@@ -187,11 +187,14 @@ extern "C" int qwb_attn_prefill(const void* q, const void* k_pool, const void* v
 // ---------------------------------------------------------------------------------
 #define QWB_DECODE_GT 8      // query heads per block
 
-__device__ __forceinline__ void decode_run_range(int len, int window, int split_tokens, int* first, int* end) {
-    // runs [first, end) hold at least one visible key of a sequence of `len` keys
+__device__ __forceinline__ void decode_run_range(int len, int window, int split_tokens, int max_runs, int* first, int* end) {
+    // runs [first, end) hold at least one visible key of a sequence of `len` keys.  The caller sizes the grid and the
+    // scratch for `max_runs` runs; a sequence longer than max_runs * split_tokens keys (a caller's mistake: the lengths
+    // are on the device, the launcher cannot check them) is cut there, so that no block reads or writes beyond the
+    // scratch it was given.
     const int k_first = window > 0 ? max(0, len - window) : 0;
-    *first = k_first / split_tokens;
-    *end = (len + split_tokens - 1) / split_tokens;
+    *first = min(k_first / split_tokens, max_runs);
+    *end = min((len + split_tokens - 1) / split_tokens, max_runs);
 }
 
 template <typename T>
@@ -206,7 +209,7 @@ __global__ void attn_decode_split_kernel(const T* __restrict__ q, const T* __res
     const int b = blockIdx.z, run = blockIdx.x;
     const int len = seq_len[b];
     int run_first, run_end;
-    decode_run_range(len, window, split_tokens, &run_first, &run_end);
+    decode_run_range(len, window, split_tokens, max_runs, &run_first, &run_end);
     if (run < run_first || run >= run_end) return;
 
     const int G = Hq / Hkv, slices = (G + GT - 1) / GT;
@@ -354,7 +357,7 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_acc, c
     pdl_launch_dependents();
     const int h = blockIdx.x, b = blockIdx.y;
     int run_first, run_end;
-    decode_run_range(seq_len[b], window, split_tokens, &run_first, &run_end);
+    decode_run_range(seq_len[b], window, split_tokens, max_runs, &run_first, &run_end);
     if (run_end - run_first <= 1) return;                  // the split kernel wrote the result itself
     const size_t row = ((size_t)b * Hq + h) * max_runs;
     float M = -INFINITY;

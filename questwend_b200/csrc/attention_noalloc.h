@@ -16,15 +16,22 @@
 // exits, whether this entry point is ever called or not.
 //
 // Limits.  B * Hq * max_runs * (hd + 2) must not exceed QWB_NOALLOC_SCRATCH_FLOATS; a larger
-// problem is refused with an error message (qwb_last_error), nothing is launched.  At the
-// default run length of 256 keys that is, for 32 heads of 128: 8 sequences of up to 32,768
-// keys, or 32 sequences of up to 8,192.
+// problem is refused with an error message (qwb_last_error), nothing is launched.  With 32
+// heads of 128 a run takes 32 * 130 = 4,160 floats, so B * max_runs can be 1,008 at most: at
+// the default run length of 256 keys that is 8 sequences of up to 126 runs = 32,256 keys, or
+// 31 sequences of up to 32 runs = 8,192 keys (8 x 32,768 and 32 x 8,192 are just too many).
+// max_runs must cover the longest sequence, max_runs >= ceil(longest / split_tokens): the
+// lengths are on the device, so the launcher cannot check this; the kernels cut a longer
+// sequence at max_runs runs rather than touch memory beyond the scratch.
 //
 // First call.  The first call on each device looks the array's device address up
 // (cudaGetSymbolAddress, with that device current) and keeps it; that lookup is a
 // synchronising runtime call, so make the first call on a device before any stream capture
 // begins on it.  Later calls only launch kernels.  The function calls no cudaMalloc, no
-// cudaFree and no library routine that allocates.
+// cudaFree and no library routine that allocates.  The kept address is not guarded by a
+// lock: make a device's first call from one host thread, and let other threads call once it
+// has returned.  The device that is current when the function is called decides which
+// array is used, so `stream` must be a stream of the current device.
 //
 // Sharing.  All calls on a device use the same array.  Nothing in it has to start at zero
 // (every value that is read was written earlier in the same call), so stale contents of an

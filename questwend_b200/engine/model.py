@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import torch
 
-from ..parts.base import Runtime, StepContext, UnitCache
+from ..parts.base import BoundWeights, Runtime, StepContext, UnitCache
 from ..parts.registry import build_part
 from ..weights.manifest import TensorSpec
 from .plan import ModelPlan
@@ -47,9 +47,16 @@ class Model:
                     out.append(t)
         return out
 
-    def bind(self, weights) -> None:
+    def bind(self, weights: dict) -> None:
+        """Hand every part its tensors.  Tensors that a part only copies from (into a fused matrix) are taken out of
+        ``weights`` as the binding goes, unless another part names them too."""
+        uses: dict = {}
         for part in self.parts():
-            part.bind(weights)
+            for t in part.tensors():
+                uses[t.name] = uses.get(t.name, 0) + 1
+        bound = BoundWeights(weights, uses)
+        for part in self.parts():
+            part.bind(bound)
 
     def kernel_modules(self) -> list[str]:
         mods = []

@@ -11,7 +11,7 @@ import torch
 from ..kernels import ops
 from ..kernels.limits import head_dim_refusal
 from ..weights.manifest import MATRIX, NORM_WEIGHT, VECTOR, TensorSpec
-from .base import KVSpec, Mixer
+from .base import KVSpec, Mixer, take_weight
 from .linear import kernel_modules as linear_modules, linear
 from .registry import register_mixer
 
@@ -65,8 +65,10 @@ class GroupedQueryAttention(Mixer):
 
     def bind(self, weights):
         n, px = self.names, self.prefix
-        # one fused projection: rows of q, then k, then v (a row concat, no change to the math)
-        self.w_qkv = torch.cat([weights[px + n["q"]], weights[px + n["k"]], weights[px + n["v"]]], dim=0).contiguous()
+        # one fused projection: rows of q, then k, then v (a row concat, no change to the math).  The three sources are
+        # taken out of ``weights`` (see ``take_weight``), so that a large model does not hold them twice until every layer
+        # is bound.
+        self.w_qkv = torch.cat([take_weight(weights, px + n[x]) for x in "qkv"], dim=0).contiguous()
         self.w_o = weights[px + n["o"]]
         if self.qk_norm:
             self.q_norm_w = weights[px + n["q_norm"]].to(torch.float32).contiguous()

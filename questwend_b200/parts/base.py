@@ -89,6 +89,33 @@ class UnitCache:
         self.writable = writable
 
 
+def take_weight(weights, name: str) -> torch.Tensor:
+    """A tensor that the caller copies into a layout of its own (a fused matrix) and does not keep as it is.  When a
+    whole model is bound, ``weights`` lets go of such a tensor unless another part asks for it too, so that a large model
+    is not held twice until every layer is bound; a plain dict just hands it out."""
+    take = getattr(weights, "take", None)
+    return take(name) if take is not None else weights[name]
+
+
+class BoundWeights:
+    """The tensors of a model while its parts bind them: ``weights[name]`` to keep a tensor as it is, ``take(name)`` for
+    one that is only copied from.  ``uses`` counts how many parts name each tensor."""
+
+    def __init__(self, tensors: dict, uses: Mapping[str, int]):
+        self._tensors = tensors
+        self._uses = dict(uses)
+
+    def __getitem__(self, name):
+        return self._tensors[name]
+
+    def __contains__(self, name):
+        return name in self._tensors
+
+    def take(self, name):
+        self._uses[name] = self._uses.get(name, 1) - 1
+        return self._tensors.pop(name) if self._uses[name] <= 0 else self._tensors[name]
+
+
 class Part:
     """Common to all parts: the tensors it wants and how it takes them."""
 

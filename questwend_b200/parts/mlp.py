@@ -5,7 +5,7 @@ import torch
 
 from ..kernels import ops
 from ..weights.manifest import MATRIX, TensorSpec
-from .base import FeedForward
+from .base import FeedForward, take_weight
 from .linear import kernel_modules as linear_modules, linear, linear_swiglu
 from .registry import register_feed_forward
 
@@ -31,7 +31,7 @@ class GatedMLP(FeedForward):
 
     def bind(self, weights):
         n, px = self.names, self.prefix
-        gate, up = weights[px + n["gate"]], weights[px + n["up"]]
+        gate, up = take_weight(weights, px + n["gate"]), take_weight(weights, px + n["up"])      # only copied from
         # one fused projection.  Where the sizes allow, gate and up rows are interleaved in groups of 8 features, so that the
         # products with a fused SwiGLU epilogue find both in one thread (a reordering of rows: the same numbers).
         self.interleave = ops.GATE_UP_GROUP if self.inter % ops.GATE_UP_GROUP == 0 else 0
@@ -39,6 +39,7 @@ class GatedMLP(FeedForward):
             self.w_gate_up = ops.interleave_gate_up(gate, up, self.interleave)
         else:
             self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
+        del gate, up
         self.w_down = weights[px + n["down"]]
 
     def kernel_modules(self):

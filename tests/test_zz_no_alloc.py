@@ -75,3 +75,18 @@ def test_a_problem_beyond_the_array_is_refused():
     assert rc != 0
     msg = lib.qwb_last_error().decode()
     assert "built-in array holds" in msg and "scratch of your own" in msg
+
+
+def test_too_few_runs_cut_the_sequence_and_touch_nothing_beyond_the_scratch():
+    """``max_runs`` must cover the longest sequence; the lengths are on the device, so the launcher cannot check that.  A
+    caller that gives too few gets the attention over the first ``max_runs`` runs of keys, not a read or write beyond
+    the scratch that it sized by ``max_runs``."""
+    lib = load_module("attention")
+    q, k_pool, v_pool, table, seq_len = _inputs(4, torch.float32, [300, 40])
+    scale = 1 / math.sqrt(q.shape[-1])
+    rc, got = _noalloc(lib, q, k_pool, v_pool, table, seq_len, scale, 256, 128)          # 2 runs where 300 keys need 3
+    torch.cuda.synchronize()
+    assert rc == 0, lib.qwb_last_error().decode()
+    cut = torch.tensor([256, 40], dtype=torch.int32, device=DEV)
+    want = ops.attn_decode(q, k_pool, v_pool, table, cut, scale, 256, split_tokens=128)
+    assert (got - want).abs().max().item() <= 5e-6 * want.abs().max().item()

@@ -12,7 +12,6 @@ but travels to the GPU box.  ``bench.py --impl reference`` runs that program.  N
 """
 import argparse
 import os
-import shutil
 import subprocess
 import sys
 import tempfile
@@ -38,14 +37,16 @@ def main() -> int:
     out_dir = os.path.join(HERE, "_ref", "bin")
     os.makedirs(out_dir, exist_ok=True)
     out = os.path.join(out_dir, "qw_ref_bench")
-    # the CUDA runtime and cuBLAS are linked as shared libraries: the GPU box has the same toolkit image
+    # the CUDA runtime and cuBLAS are linked as shared libraries: the GPU box has the same toolkit image.  ggml's CUDA
+    # backend links NCCL when CMake finds it (for its two-GPU split, which the reference never uses): link what it found.
+    nccl = []
+    with open(os.path.join(bd, "build.ninja")) as f:
+        if "libnccl" in f.read():
+            nccl = ["-lnccl"]
     subprocess.check_call(["g++", "-O2", "-std=c++17", os.path.join(HERE, "ref_bench.cpp"), "-I", os.path.join(ref, "core"),
                            "-I", os.path.join(ref, "third_party/ggml/include"), "-o", out, "-Wl,--start-group"] + libs +
                           ["-Wl,--end-group", f"-L{cuda}/lib64", f"-L{cuda}/lib64/stubs", "-lcudart", "-lcublas", "-lcublasLt",
-                           "-lcuda", f"-Wl,-rpath,{cuda}/lib64", "-lpthread", "-ldl", "-lm"])
-    cli = os.path.join(bd, "qw-cli")
-    if os.path.exists(cli):
-        shutil.copy2(cli, os.path.join(out_dir, "qw-cli"))
+                           "-lcuda", *nccl, f"-Wl,-rpath,{cuda}/lib64", "-lpthread", "-ldl", "-lm"])
     print(out)
     return 0
 

@@ -172,6 +172,7 @@ def decode_run(engine, torch, batch, warmup, steps, rng, count_launches=False):
     end.record()
     torch.cuda.synchronize()
     ms = start.elapsed_time(end)
+    engine.check_kernels()                             # no bounded wait inside a kernel gave up
     ctx1 = engine.cache.length(slots[0])
     per_step = runner.launches_per_step
     engine.close_sequences(slots)

@@ -400,7 +400,10 @@ attn_mma_decode_kernel(const FusedQKV fused, const bf16* __restrict__ q, const b
                        float* __restrict__ part_m, float* __restrict__ part_l, bf16* __restrict__ out, int Hq, int Hkv,
                        int table_width, float scale, int window, int runs_target, int run_pages_max, int max_runs, int Gc,
                        int chunks) {
-    pdl_wait();
+    // Launched with programmatic stream serialization, the block may start while the kernel before it (the q/k/v projection)
+    // still runs.  What it needs first does not come from that kernel: the sequences' lengths and page tables were set
+    // before the step, and the keys and values of earlier tokens in earlier steps.  So the run's first page is on its way
+    // before the wait; q, and the new token's key and value, are read after it.
     pdl_launch_dependents();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     // blocks start in the order of x, then y, then z: the run is z, so that the runs that only longer sequences have
@@ -434,6 +437,7 @@ attn_mma_decode_kernel(const FusedQKV fused, const bf16* __restrict__ q, const b
         cp_async_commit();
     }
 
+    pdl_wait();
     int row_pos[2];
     uint32_t qf[HD / 16][4];
     {
@@ -654,7 +658,8 @@ static int launch_decode(const FusedQKV& fused, const void* q, const void* k_poo
     float* part_m = scratch + (size_t)B * Hq * max_runs * HD;
     float* part_l = part_m + (size_t)B * Hq * max_runs;
     dim3 grid(Hkv * chunks, B, max_runs);
-    qwb_launch(attn_mma_decode_kernel<HD, FUSED>, grid, 32, smem, stream, fused, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
+    // early: see the kernel's first lines
+    qwb_launch_early(attn_mma_decode_kernel<HD, FUSED>, grid, 32, smem, stream, fused, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
         page_table, seq_len, part_acc, part_m, part_l, (bf16*)out, Hq, Hkv, table_width, scale, window, runs_target, run_pages_max,
         max_runs, Gc, chunks);
     if (int rc = qwb_check_launch("attn_mma_decode")) return rc;

@@ -190,12 +190,18 @@ class Engine:
         with torch.cuda.device(self.device):
             ctx, want_rows = self.build_context(entries)
             logits = self.model.forward(ctx, self.unit_caches, want_rows)
-            if self.dtype == torch.bfloat16 and not ctx.single_token:
-                ops.gemm_tc_check(self.device)       # a tcgen05 product that gave up a wait must not pass unseen
+            self.check_kernels()
         for e in entries:
             self.cache.advance(e.slot, len(e.tokens))
         self.steps_run += 1
         return logits
+
+    def check_kernels(self) -> None:
+        """Raise if a kernel with bounded waits (the TMA-fed products, the tcgen05 attention) gave one up since the last
+        check: its result is then not valid.  Reads one int from the device, so it waits for the work queued so far."""
+        if self.dtype == torch.bfloat16:
+            with torch.cuda.device(self.device):
+                ops.gemm_tc_check(self.device)
 
     def decode_runner(self, batch: int, sampling, use_graph: bool = True):
         """The fixed buffers and CUDA graphs for decode steps of ``batch`` sequences (made once, kept).  The sampling

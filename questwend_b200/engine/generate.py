@@ -258,6 +258,8 @@ def generate(engine, prompts, max_new_tokens: int = 128, sampling: SamplingParam
                     length[i] += 1
                 step += 1
                 stats.steps += 1
+            if graph_path:
+                engine.check_kernels()            # the steps replayed from graphs are checked once a batch (plain steps each)
         finally:
             if slot_of:
                 engine.close_sequences(list(slot_of.values()))

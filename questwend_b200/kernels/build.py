@@ -24,7 +24,7 @@ CSRC = os.path.join(os.path.dirname(_HERE), "csrc")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "--shared", "-Xcompiler", "-fPIC"]
 EXTRA_FLAGS: dict[str, list[str]] = {}
-MODULES = ("elementwise", "rope_kv", "attention", "attention_mma", "attention_tc", "gemm_small", "gemm_stream", "gemm_tc", "sampling")
+MODULES = ("elementwise", "rope_kv", "attention", "attention_mma", "attention_tc", "gemm_small", "gemm_stream", "gemm_ring", "gemm_tc", "sampling")
 
 _lock = threading.Lock()
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -56,6 +56,10 @@ def bench_gemm(M: int, N: int, K: int, impl: str, iters: int, dtype=torch.bfloat
     x = torch.randn(M, K, device="cuda").to(dtype)
     if impl == "stream":
         fn = lambda i: ops.gemm_stream(x, ws[i])
+    elif impl == "ring":
+        fn = lambda i: ops.gemm_ring(x, ws[i])
+    elif impl == "ring_swiglu":
+        fn = lambda i: ops.gemm_ring_swiglu(x, ws[i])
     elif impl == "stream_swiglu":
         fn = lambda i: ops.gemm_stream_swiglu(x, ws[i])
     elif impl == "small":
@@ -158,7 +162,7 @@ def main() -> int:
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=24576)
     ap.add_argument("--k", type=int, default=4096)
-    ap.add_argument("--impl", default="stream", choices=["stream", "stream_swiglu", "small", "library", "tc", "tc_add", "tc_swiglu"])
+    ap.add_argument("--impl", default="stream", choices=["stream", "stream_swiglu", "ring", "ring_swiglu", "small", "library", "tc", "tc_add", "tc_swiglu"])
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=1152)

@@ -422,6 +422,40 @@ def gemm_stream_swiglu(x: torch.Tensor, weight: torch.Tensor, config: tuple | No
     return out
 
 
+def gemm_ring(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor | None = None,
+              out: torch.Tensor | None = None) -> torch.Tensor:
+    """As ``gemm_stream``, by the kernel that streams W through a ring in shared memory filled by bulk copies and is built
+    to overlap with the kernels before and after it.  A wait that gave up shows in ``gemm_tc_check``."""
+    _need(x, "x", torch.bfloat16, 2)
+    _need(weight, "weight", torch.bfloat16, 2)
+    M, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K:
+        raise KernelError(f"gemm_ring: x has {K} columns, the weight {weight.shape[1]}")
+    if out is None:
+        out = residual if residual is not None else torch.empty((M, N), dtype=torch.float32, device=x.device)
+    _need(out, "out", torch.float32, 2)
+    if residual is not None:
+        _need(residual, "residual", torch.float32, 2)
+    _call("gemm_ring", "qwb_gemm_ring", _ptr(x), _ptr(weight), _ptr(residual), _ptr(out), _i(M), _i(N), _i(K),
+          _ptr(gemm_tc_error_word(x.device)), _stream())
+    return out
+
+
+def gemm_ring_swiglu(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """As ``gemm_stream_swiglu``, by the ring kernel (see ``gemm_ring``)."""
+    _need(x, "x", torch.bfloat16, 2)
+    _need(weight, "weight", torch.bfloat16, 2)
+    M, K = x.shape
+    if weight.shape[1] != K or weight.shape[0] % 2:
+        raise KernelError(f"gemm_ring_swiglu: x is {tuple(x.shape)}, the weight {tuple(weight.shape)}")
+    F = weight.shape[0] // 2
+    out = torch.empty((M, F), dtype=torch.bfloat16, device=x.device)
+    _call("gemm_ring", "qwb_gemm_ring_swiglu", _ptr(x), _ptr(weight), _ptr(out), _i(M), _i(F), _i(K),
+          _ptr(gemm_tc_error_word(x.device)), _stream())
+    return out
+
+
 _TC_ERROR: dict = {}    # device -> one int32 that a gemm_tc kernel sets when one of its waits gives up
 TC_EPILOGUES = {"store": 0, "add": 1, "swiglu": 2}
 

@@ -26,7 +26,7 @@ from ..kernels import ops
 
 def kernel_modules(dtype: torch.dtype) -> tuple:
     """The kernel modules that ``linear`` may launch for this engine dtype."""
-    return ("gemm_small", "gemm_stream", "gemm_tc") if dtype == torch.bfloat16 else ("gemm_small",)
+    return ("gemm_small", "gemm_stream", "gemm_ring", "gemm_tc") if dtype == torch.bfloat16 else ("gemm_small",)
 
 
 def require_true_fp32() -> None:
@@ -73,7 +73,14 @@ def _library(x, weight, add_to, kind, interleave):
     return torch.mm(x, weight.t(), out_dtype=torch.float32)
 
 
+FEW_ROWS_KERNEL = os.environ.get("QWB200_FEW_ROWS", "ring")     # "ring" or "stream": which few-rows kernel the engine uses
+
+
 def _stream(x, weight, add_to, kind, config):
+    if config is None and FEW_ROWS_KERNEL == "ring":
+        if kind == "swiglu":
+            return ops.gemm_ring_swiglu(x, weight)
+        return ops.gemm_ring(x, weight, residual=add_to)
     if kind == "swiglu":
         return ops.gemm_stream_swiglu(x, weight, config=config)
     return ops.gemm_stream(x, weight, residual=add_to, config=config)
@@ -141,7 +148,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, add_to: torch.Tensor | None = 
     if bf16 and M <= ops.STREAM_M and K % 8 == 0:
         how, config = _few_rows_choice(M, weight, "plain" if add_to is None else "add")
         if how == "stream":
-            return ops.gemm_stream(x, weight, residual=add_to, config=config)
+            return _stream(x, weight, add_to, "add" if add_to is not None else "plain", config)
     elif M <= (STREAM_MAX_ROWS if bf16 else ops.SMALL_M):     # float32; bfloat16 rows whose length is no multiple of 8
         return ops.gemm_small(x, weight, residual=add_to)
     if bf16:
@@ -162,7 +169,7 @@ def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor, out_dtype: torc
         if x.shape[0] <= ops.STREAM_M and x.shape[1] % 8 == 0:
             how, config = _few_rows_choice(x.shape[0], weight_gate_up, "swiglu")
             if how == "stream":
-                return ops.gemm_stream_swiglu(x, weight_gate_up, config=config)
+                return _stream(x, weight_gate_up, None, "swiglu", config)
         if x.shape[0] >= TC_SWIGLU_MIN_ROWS and x.shape[1] >= TC_SWIGLU_MIN_INNER and x.shape[1] % 8 == 0:
             return ops.gemm_tc(x, weight_gate_up, epilogue="swiglu", tile_n=256)
     return ops.silu_mul(linear(x, weight_gate_up), out_dtype, interleave)

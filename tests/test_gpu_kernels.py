@@ -426,6 +426,37 @@ def test_gemm_stream(M, N, K):
         ops.gemm_stream(torch.zeros(17, K, dtype=torch.bfloat16, device=DEV), w)
 
 
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(37, 96), (200, 200), (16, 4104), (129, 1024), (5000, 8200), (2400, 512), (4096, 520)])
+def test_gemm_ring(M, N, K):
+    """The few-rows product that streams W through a ring of bulk copies: tiles of 16 rows and stages of 512 k that the
+    sizes do not fill, more tiles than blocks (5000 rows), one stage and many; plain, residual-add and SwiGLU."""
+    g = torch.Generator().manual_seed(M * 1000 + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(N, K, generator=g).to(torch.bfloat16).to(DEV)
+    ref = f64(x) @ f64(w).T
+    out = ops.gemm_ring(x, w)
+    ops.gemm_tc_check(DEV)
+    close(out, ref, torch.float32, scale=np.abs(ref).max() * 4)          # 32-bit sums of exact products
+    res = torch.randn(M, N, generator=g).to(DEV)
+    want = f64(res) + ref
+    close(ops.gemm_ring(x, w, residual=res.clone()), want, torch.float32, scale=np.abs(want).max() * 4)
+    assert torch.equal(ops.gemm_ring(x[:1], w)[0], out[0])               # a row does not depend on the others
+    assert torch.equal(ops.gemm_ring(x, w), out)                         # nor on timing
+    if N % 16 == 0:
+        F = N // 2
+        xs, ws = (x.float() * 0.3).to(torch.bfloat16), (w.float() * 0.3).to(torch.bfloat16)
+        gu = f64(xs) @ f64(ws).T
+        act = ops.gemm_ring_swiglu(xs, ops.interleave_gate_up(ws[:F], ws[F:]))
+        close(act, pm.swiglu(gu[:, :F], gu[:, F:]), torch.bfloat16)
+        assert torch.equal(act, ops.silu_mul(ops.gemm_ring(xs, ws), torch.bfloat16))
+    ops.gemm_tc_check(DEV)
+    with pytest.raises(KernelError, match="multiple of 8"):
+        ops.gemm_ring(x[:, :K - 4].contiguous(), w[:, :K - 4].contiguous())
+    with pytest.raises(KernelError, match="at most 16"):
+        ops.gemm_ring(torch.zeros(17, K, dtype=torch.bfloat16, device=DEV), w)
+
+
 @pytest.mark.parametrize("config", ops.STREAM_CONFIGS)
 @pytest.mark.parametrize("M", [2, 8, 13])
 def test_gemm_stream_in_every_form(M, config):

@@ -265,12 +265,8 @@ def small_model_workload(torch, np, peaks) -> dict:
 
 
 def large_model_workload(torch, np, peaks) -> dict:
-    """Qwen3-32B sizes, all 64 layers: a 2,048-token prefill, and decode at batch 1, 8 and 16 from 1,024-token prompts.
-    The few-rows products choose their form by measuring here (QWB200_TUNE): at these matrix sizes it pays."""
-    from questwend_b200.parts import linear as L
-    tune_before = L.TUNE
-    L.TUNE = True
-    try:
+    """Qwen3-32B sizes, all 64 layers: a 2,048-token prefill, and decode at batch 1, 8 and 16 from 1,024-token prompts."""
+    if True:
         engine, d = make_engine(QWEN3_32B, QWEN3_32B["num_hidden_layers"], 16, PROMPT_LEN + 256)
         rng = np.random.default_rng(32)
         out = {"m32b_weights_gb": weight_bytes(engine) / 1e9}
@@ -286,8 +282,6 @@ def large_model_workload(torch, np, peaks) -> dict:
                                     / (peaks["bf16_tflops"] * 1e12))
         out["m32b_peak_memory_gb"] = torch.cuda.max_memory_allocated() / 1e9
         release(engine, torch)
-    finally:
-        L.TUNE = tune_before
     return out
 
 

@@ -9,6 +9,7 @@ import torch
 import plain_model as pm
 from helpers import BF16_TOL, FP32_TOL, rel_err
 from questwend_b200.cache import CacheManager
+from questwend_b200.kernels import ops
 from questwend_b200.config import ConfigReader, ModelConfig, register_architecture
 from questwend_b200.engine.engine import Engine, StepEntry, build_step_context
 from questwend_b200.engine.plan import LayerSpec, ModelPlan, Run
@@ -155,29 +156,31 @@ def test_block_part(dtype):
     assert rel_err(f64(h_dev) + (0 if delta is None else f64(delta)), ref) < tol(dtype)
 
 
-def test_few_row_products_choose_by_measuring(monkeypatch):
-    """For large matrices the first call times the candidates and keeps the choice; whatever is chosen, the numbers are
-    those of the product (a 20 MB matrix here, with the limit lowered so that it counts as large)."""
+def test_few_row_products_by_either_kernel(monkeypatch):
+    """``linear`` with few rows: the ring-fed kernel (the default) and the kernel before it give the product's numbers, and
+    from 9 rows on a large matrix goes to the library."""
     from questwend_b200.parts import linear as L
-    monkeypatch.setattr(L, "TUNE", True)
-    monkeypatch.setattr(L, "TUNE_MIN_WEIGHT_BYTES", 1 << 20)
-    monkeypatch.setattr(L, "_CHOICES", {})
     g = torch.Generator().manual_seed(0)
     w = (torch.randn(2560, 4096, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
-    for rows in (3, 8, 12):
-        x = torch.randn(rows, 4096, generator=g).to(torch.bfloat16).to(DEV)
-        ref = f64(x) @ f64(w).T
-        out = L.linear(x, w)
-        assert rel_err(f64(out), ref) < FP32_TOL * 4                      # 32-bit sums of exact products
-        base = torch.randn(rows, 2560, generator=g).to(DEV)
-        added = L.linear(x, w, add_to=base.clone())
-        assert rel_err(f64(added), f64(base) + ref) < FP32_TOL * 4
-    keys = sorted(k[1:] for k in L._CHOICES)
-    assert keys == [(2560, 4096, 8, "add"), (2560, 4096, 8, "plain"), (2560, 4096, 16, "add"), (2560, 4096, 16, "plain")]
-    assert all(v[0] in ("stream", "library") for v in L._CHOICES.values())
-    gu = L.linear_swiglu(x, w, torch.bfloat16, interleave=8)             # 1280 features, gate and up interleaved in eights
-    y = ref.reshape(rows, 160, 2, 8)
-    assert rel_err(f64(gu), pm.swiglu(y[:, :, 0], y[:, :, 1]).reshape(rows, 1280)) < BF16_TOL
+    for kernel in ("ring", "stream"):
+        monkeypatch.setattr(L, "FEW_ROWS_KERNEL", kernel)
+        for rows in (3, 8, 12):
+            x = torch.randn(rows, 4096, generator=g).to(torch.bfloat16).to(DEV)
+            ref = f64(x) @ f64(w).T
+            before = ops.LAUNCHES[0]
+            out = L.linear(x, w)
+            assert ops.LAUNCHES[0] == before + 1                           # an own kernel ran, not the library
+            assert rel_err(f64(out), ref) < FP32_TOL * 4                      # 32-bit sums of exact products
+            base = torch.randn(rows, 2560, generator=g).to(DEV)
+            added = L.linear(x, w, add_to=base.clone())
+            assert rel_err(f64(added), f64(base) + ref) < FP32_TOL * 4
+        gu = L.linear_swiglu(x, w, torch.bfloat16, interleave=8)             # 1280 features, gate and up interleaved in eights
+        y = ref.reshape(rows, 160, 2, 8)
+        assert rel_err(f64(gu), pm.swiglu(y[:, :, 0], y[:, :, 1]).reshape(rows, 1280)) < BF16_TOL
+    ops.gemm_tc_check(DEV)
+    monkeypatch.setattr(L, "STREAM_WIDE_MAX_WEIGHT", 1 << 20)                  # now 10 M weights count as large
+    before = ops.LAUNCHES[0]
+    assert rel_err(f64(L.linear(x, w)), ref) < FP32_TOL * 4 and ops.LAUNCHES[0] == before     # 12 rows: the library
 
 
 # ----------------------------------------------------------------------------- a toy architecture, defined here

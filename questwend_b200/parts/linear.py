@@ -26,7 +26,8 @@ from ..kernels import ops
 
 def kernel_modules(dtype: torch.dtype) -> tuple:
     """The kernel modules that ``linear`` may launch for this engine dtype."""
-    return ("gemm_small", "gemm_stream", "gemm_ring", "gemm_tc") if dtype == torch.bfloat16 else ("gemm_small",)
+    few_rows = "gemm_ring" if FEW_ROWS_KERNEL == "ring" else "gemm_stream"
+    return ("gemm_small", few_rows, "gemm_tc") if dtype == torch.bfloat16 else ("gemm_small",)
 
 
 def require_true_fp32() -> None:

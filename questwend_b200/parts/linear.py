@@ -38,8 +38,10 @@ def require_true_fp32() -> None:
 
 STREAM_MAX_ROWS = 8         # up to here the own weight-streaming product is always the fastest.  With 9 to 16 rows (its
 STREAM_WIDE_MAX_WEIGHT = 1 << 24   # two-tile form) it still is for matrices of up to 16 M weights (the 0.6B model's, an
-                            # 8B model's o projection); beyond, the library is: at 16 rows the gate/up projection of
-                            # Qwen3-8B (100 M weights) takes 42.4 us against 34.7 us
+STREAM_WIDE_MIN_INNER = 8192       # 8B model's o projection) and for long rows (the down projection: 20.9 us against the
+                            # library's 21.8 at 16 rows, 19.9 against 21.8 at 12); else the library is: at 16 rows the
+                            # gate/up projection of Qwen3-8B takes 42.4 us against 34.7 us (16 rows of x of 4,096 no
+                            # longer fit into the L1 that the ring leaves)
 
 FEW_ROWS_KERNEL = os.environ.get("QWB200_FEW_ROWS", "ring")     # "ring" (gemm_ring, the default) or "stream" (gemm_stream, the
                                                                 # kernel before it, kept for comparison)
@@ -48,7 +50,8 @@ FEW_ROWS_KERNEL = os.environ.get("QWB200_FEW_ROWS", "ring")     # "ring" (gemm_r
 def _few_rows(M: int, weight: torch.Tensor) -> bool:
     """Whether M rows of this bfloat16 weight go to the own few-rows product (else to the library).  The choice follows
     from the shape alone, so the same trace gives the same bits in every process."""
-    return M <= STREAM_MAX_ROWS or (M <= ops.STREAM_M and weight.numel() <= STREAM_WIDE_MAX_WEIGHT)
+    return M <= STREAM_MAX_ROWS or (M <= ops.STREAM_M and (weight.numel() <= STREAM_WIDE_MAX_WEIGHT or
+                                                           weight.shape[1] >= STREAM_WIDE_MIN_INNER))
 
 
 def _stream(x, weight, add_to, kind):

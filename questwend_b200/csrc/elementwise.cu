@@ -21,6 +21,18 @@ __global__ void embed_gather_kernel(const int* __restrict__ ids, const T* __rest
         return;
     }
     const T* row = table + (size_t)id * D;
+    constexpr int VEC = Vec16<T>::N;
+    if (D % VEC == 0 && (uintptr_t)table % 16 == 0 && (uintptr_t)out % 16 == 0) {      // 16 bytes of the row a load
+        const Vec16<T>* src = reinterpret_cast<const Vec16<T>*>(row);
+        for (int i = threadIdx.x; i < D / VEC; i += blockDim.x) {
+            float v[VEC];
+            src[i].get(v);
+#pragma unroll
+            for (int e = 0; e < VEC; e += 4)
+                *reinterpret_cast<float4*>(o + (size_t)i * VEC + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = to_f32(row[i]);
 }
 

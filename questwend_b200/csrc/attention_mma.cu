@@ -319,8 +319,8 @@ __device__ __forceinline__ void fused_q_frags(uint32_t (*qf)[4], const FusedQKV&
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
             const int d = 16 * ks + 2 * t;
-            const float2 a = rows[h] ? *reinterpret_cast<const float2*>(rows[h] + d) : make_float2(0.f, 0.f);
-            const float2 c = rows[h] ? *reinterpret_cast<const float2*>(rows[h] + d + 8) : make_float2(0.f, 0.f);
+            const float2 a = rows[h] ? __ldcg(reinterpret_cast<const float2*>(rows[h] + d)) : make_float2(0.f, 0.f);
+            const float2 c = rows[h] ? __ldcg(reinterpret_cast<const float2*>(rows[h] + d + 8)) : make_float2(0.f, 0.f);
             v[h][ks][0] = a.x; v[h][ks][1] = a.y; v[h][ks][2] = c.x; v[h][ks][3] = c.y;
             ss += a.x * a.x + a.y * a.y + c.x * c.x + c.y * c.y;
         }
@@ -371,7 +371,7 @@ __device__ __forceinline__ void fused_new_row(const FusedQKV& f, const float* sr
     constexpr int PER = HD / 32, HALF = HD / 2;
     const int d0 = lane * PER;
 #pragma unroll
-    for (int e = 0; e < PER; ++e) y[e] = src[d0 + e];
+    for (int e = 0; e < PER; ++e) y[e] = __ldcg(src + d0 + e);        // written by the kernel before: past the read-only cache
     if (!is_k) return;
     if (f.k_w) {
         float ss = 0.f;
@@ -395,15 +395,19 @@ __device__ __forceinline__ void fused_new_row(const FusedQKV& f, const float* sr
 
 template <int HD, bool FUSED>
 __global__ void __launch_bounds__(32)
-attn_mma_decode_kernel(const FusedQKV fused, const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+attn_mma_decode_kernel(const FusedQKV fused, const bf16* q, const bf16* k_pool, const bf16* v_pool,
                        const int* __restrict__ page_table, const int* __restrict__ seq_len, float* __restrict__ part_acc,
                        float* __restrict__ part_m, float* __restrict__ part_l, bf16* __restrict__ out, int Hq, int Hkv,
                        int table_width, float scale, int window, int runs_target, int run_pages_max, int max_runs, int Gc,
                        int chunks) {
-    // Launched with programmatic stream serialization, the block may start while the kernel before it (the q/k/v projection)
-    // still runs.  What it needs first does not come from that kernel: the sequences' lengths and page tables were set
-    // before the step, and the keys and values of earlier tokens in earlier steps.  So the run's first page is on its way
-    // before the wait; q, and the new token's key and value, are read after it.
+    // Launched with programmatic stream serialization, the block may start while the kernel before it still runs.
+    // FUSED, that kernel is the q/k/v projection, and what the block needs first does not come from it: the sequences'
+    // lengths and page tables were set before the step, and the keys and values of earlier tokens in earlier steps.  So
+    // the run's first page is on its way before the wait; q, and the new token's key and value, are read after it, with
+    // loads that do not go through the read-only cache (q, k_pool and v_pool are not __restrict__ for that reason: what
+    // the kernel before wrote while this one was resident must not be read as constant data).  Not FUSED, the kernel
+    // before it wrote the new key and value into the cache, so the wait comes first.
+    if (!FUSED) pdl_wait();
     pdl_launch_dependents();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     // blocks start in the order of x, then y, then z: the run is z, so that the runs that only longer sequences have
@@ -437,7 +441,7 @@ attn_mma_decode_kernel(const FusedQKV fused, const bf16* __restrict__ q, const b
         cp_async_commit();
     }
 
-    pdl_wait();
+    if (FUSED) pdl_wait();
     int row_pos[2];
     uint32_t qf[HD / 16][4];
     {

@@ -48,6 +48,10 @@ typedef __nv_bfloat16 bf16;
 // slower, 4.77 ms against 4.49 ms: the early blocks of the next kernel take room on the SMs from the
 // running one.  So only kernels that gain from an early start get it (qwb_launch_early).  (The
 // reference's CUDA back end has the same hooks, ggml-cuda/common.cuh:123-129.)
+// A kernel that is launched early reads what its predecessor wrote with loads that are coherent at
+// L2 (__ldcg, or plain loads through a pointer that is not __restrict__), never through the read-only
+// path (__ldg, ld.global.nc): a block that was resident while the predecessor wrote has been seen to
+// get the buffer's earlier contents from there after the wait.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -90,10 +90,10 @@ struct GrSmem {
 };
 
 // NT = number of 8-row tiles of x handled at once (M <= 8 * NT); GR_KC = k per stage; GR_STAGES = stages of the ring;
-// GR_WARPS = warps (GR_STAGES is a multiple of it).
-template <int NT, int EPI, int GR_KC, int GR_STAGES, int GR_WARPS>
+// GR_WARPS = warps (GR_STAGES is a multiple of it); SPW: see below (0: the general form).
+template <int NT, int EPI, int GR_KC, int GR_STAGES, int GR_WARPS, int SPW>
 __global__ void __launch_bounds__(GR_WARPS * 32)
-gemm_ring_kernel(const bf16* __restrict__ x, const __grid_constant__ CUtensorMap map_w, const float* residual, float* y,
+gemm_ring_kernel(const bf16* x, const __grid_constant__ CUtensorMap map_w, const float* residual, float* y,
                  bf16* __restrict__ act, int M, int N, int K, int* error) {
     using Smem = GrSmem<NT, GR_KC, GR_STAGES, GR_WARPS>;
     constexpr int GR_STAGE_BYTES = Smem::STAGE_BYTES;
@@ -148,26 +148,30 @@ gemm_ring_kernel(const bf16* __restrict__ x, const __grid_constant__ CUtensorMap
         x_ok[j] = m < M;
         xr[j] = reinterpret_cast<const uint4*>(x + (size_t)min(m, M - 1) * K);
     }
+    // SPW > 0: a tile has exactly SPW * GR_WARPS stages, so a warp meets the same k in every tile (stages warp, warp + 8, ...)
+    // and keeps its pieces of x in registers for the whole product instead of asking L1 for them at every stage.
+    uint4 xkeep[SPW > 0 ? SPW : 1][KB][NT];
+    if (SPW > 0) {
+#pragma unroll
+        for (int q = 0; q < (SPW > 0 ? SPW : 1); ++q)
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    const int c = (warp + q * GR_WARPS) * (GR_KC / 8) + kb * 4 + t;
+                    xkeep[q][kb][j] = (c < chunks && x_ok[j]) ? __ldcg(xr[j] + c) : zero;
+                }
+    }
     int base = 0, buf = 0;                                   // base: the ring's count of stages before this tile
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, buf ^= 1, base += n_stages) {
         const int n0 = tile * GR_ROWS;
         float acc[NT][4];
 #pragma unroll
         for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-        for (int s = (warp - base % GR_WARPS + GR_WARPS) % GR_WARPS; s < n_stages; s += GR_WARPS) {
+        // one stage: wait for its bytes, multiply, ask for the stage that comes into the slot next
+        auto stage = [&](int s, const uint4 (&xv)[KB][NT]) {
             const int i = base + s, slot = i % GR_STAGES, use = i / GR_STAGES;
             const int c0 = s * (GR_KC / 8);                  // the stage's first 16-byte chunk of a row
-            // a thread's 16 bytes are eight consecutive k of one row; W and x use the same renumbering of k inside a
-            // block of 32, so no shuffle is needed (the sum over k does not care about the order).  The rows of x are
-            // asked for before the wait for W: they do not depend on it.
-            uint4 xv[KB][NT];
-#pragma unroll
-            for (int kb = 0; kb < KB; ++kb)
-#pragma unroll
-                for (int j = 0; j < NT; ++j) {
-                    const int c = c0 + kb * 4 + t;
-                    xv[kb][j] = (c < chunks && x_ok[j]) ? __ldg(xr[j] + c) : zero;
-                }
             gr_wait(full_bar + slot, use & 1, failed, error, 2);
             const unsigned char* st = stages + (size_t)slot * GR_STAGE_BYTES;
 #pragma unroll
@@ -188,6 +192,25 @@ gemm_ring_kernel(const bf16* __restrict__ x, const __grid_constant__ CUtensorMap
             if (lane == 0 && i + GR_STAGES < total && !*failed) {
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 request(i + GR_STAGES);
+            }
+        };
+        if (SPW > 0) {
+#pragma unroll
+            for (int q = 0; q < (SPW > 0 ? SPW : 1); ++q) stage(warp + q * GR_WARPS, xkeep[q]);
+        } else {
+            for (int s = (warp - base % GR_WARPS + GR_WARPS) % GR_WARPS; s < n_stages; s += GR_WARPS) {
+                // a thread's 16 bytes are eight consecutive k of one row; W and x use the same renumbering of k inside a
+                // block of 32, so no shuffle is needed (the sum over k does not care about the order).  The rows of x are
+                // asked for before the wait for W: they do not depend on it.
+                uint4 xv[KB][NT];
+#pragma unroll
+                for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+                    for (int j = 0; j < NT; ++j) {
+                        const int c = s * (GR_KC / 8) + kb * 4 + t;
+                        xv[kb][j] = (c < chunks && x_ok[j]) ? __ldcg(xr[j] + c) : zero;
+                    }
+                stage(s, xv);
             }
         }
         float* mine = part + (size_t)buf * GR_WARPS * NT * 128;
@@ -262,7 +285,7 @@ static int gr_make_map(CUtensorMap* map, const void* W, int rows, int K) {
     return 0;
 }
 
-template <int NT, int EPI, int KC, int STAGES, int WARPS>
+template <int NT, int EPI, int KC, int STAGES, int WARPS, int SPW>
 static int launch_ring_as(const bf16* x, const bf16* W, const float* residual, float* y, bf16* act, int M, int N, int K,
                           int* error, cudaStream_t stream) {
     static_assert(STAGES % WARPS == 0, "a slot of the ring must always go to the same warp");
@@ -271,13 +294,13 @@ static int launch_ring_as(const bf16* x, const bf16* W, const float* residual, f
     const size_t smem = GrSmem<NT, KC, STAGES, WARPS>::BYTES;
     static bool sized = false;
     if (!sized) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_ring_kernel<NT, EPI, KC, STAGES, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_ring_kernel<NT, EPI, KC, STAGES, WARPS, SPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "gemm_ring: %s", cudaGetErrorString(e));
         sized = true;
     }
     const int n_tiles = (N + GR_ROWS - 1) / GR_ROWS;
     const int grid = n_tiles < gr_sm_count() ? n_tiles : gr_sm_count();        // one block per SM, each walks over its tiles
-    qwb_launch_early(gemm_ring_kernel<NT, EPI, KC, STAGES, WARPS>, grid, WARPS * 32, smem, stream, x, map_w, residual, y, act, M, N, K, error);
+    qwb_launch_early(gemm_ring_kernel<NT, EPI, KC, STAGES, WARPS, SPW>, grid, WARPS * 32, smem, stream, x, map_w, residual, y, act, M, N, K, error);
     return qwb_check_launch("gemm_ring");
 }
 
@@ -285,11 +308,16 @@ static int launch_ring_as(const bf16* x, const bf16* W, const float* residual, f
 // rings on the products of a Qwen3-8B decode step (8 rows; us for q/k/v, o, gate/up, down, head): 8 stages 12.4, 8.7, 39.2,
 // 21.4, 215; 16 stages 10.3, 7.5, 32.1, 18.2, 178; 24 stages 11.4, 8.0, 36.2, 18.8, 194 (the L1 that is left no longer
 // holds the rows of x); 8 stages of 512 k 11.0, 7.8, 33.5, 18.8, 178; 12 stages with 6 or 12 warps 12.3-13.7, 8.6-9.4,
-// 39.5-43.2, 19.5, 213-226.
+// 39.5-43.2, 19.5, 213-226.  With x kept in registers (rows of 4,096): 9.2, 6.7, 30.8 at 8 rows; at 16 rows 12.1, 9.2, 36.0
+// and the head 197 against 13.3, 9.5, 42.0 and 233 without.
 template <int NT, int EPI>
 static int launch_ring(const bf16* x, const bf16* W, const float* residual, float* y, bf16* act, int M, int N, int K,
                        int* error, cudaStream_t stream) {
-    return launch_ring_as<NT, EPI, 256, 16, 8>(x, W, residual, y, act, M, N, K, error, stream);
+    // rows of up to 2,048 or 4,096 values: a warp meets the same one or two stages of k in every tile and keeps its x
+    const int n_stages = (K + 255) / 256;
+    if (n_stages == 8) return launch_ring_as<NT, EPI, 256, 16, 8, 1>(x, W, residual, y, act, M, N, K, error, stream);
+    if (n_stages == 16) return launch_ring_as<NT, EPI, 256, 16, 8, 2>(x, W, residual, y, act, M, N, K, error, stream);
+    return launch_ring_as<NT, EPI, 256, 16, 8, 0>(x, W, residual, y, act, M, N, K, error, stream);
 }
 
 static int check_ring(const void* x, const void* W, int M, int K) {

@@ -36,7 +36,7 @@ __device__ __forceinline__ void mma_bf16_16816(float* c, uint32_t a0, uint32_t a
 // NT = number of 8-row tiles of x handled at once (M <= 8 * NT).
 template <int NT, int U, int GS_WARPS, bool SWIGLU>
 __global__ void __launch_bounds__(GS_WARPS * 32)
-gemm_stream_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const float* residual, float* y,
+gemm_stream_kernel(const bf16* x, const bf16* __restrict__ W, const float* residual, float* y,
                    bf16* __restrict__ act, int M, int N, int K) {
     __shared__ float part[GS_WARPS][NT][4][32];          // [warp][tile][c register][lane]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -91,7 +91,7 @@ gemm_stream_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const
             const bool in = kb + u < kb1 && c < chunks;
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
-                const uint4 xv = (in && x_ok[j]) ? __ldg(xr[j] + c) : zero;
+                const uint4 xv = (in && x_ok[j]) ? __ldcg(xr[j] + c) : zero;
                 mma_bf16_16816(acc[j], lo[u].x, hi[u].x, lo[u].y, hi[u].y, xv.x, xv.y);
                 mma_bf16_16816(acc[j], lo[u].z, hi[u].z, lo[u].w, hi[u].w, xv.z, xv.w);
             }

@@ -37,11 +37,12 @@ def require_true_fp32() -> None:
 
 
 STREAM_MAX_ROWS = 8         # up to here the own weight-streaming product is always the fastest.  With 9 to 16 rows (its
-STREAM_WIDE_MAX_WEIGHT = 1 << 24   # two-tile form) it still is for matrices of up to 16 M weights (the 0.6B model's, an
-STREAM_WIDE_MIN_INNER = 8192       # 8B model's o projection) and for long rows (the down projection: 20.9 us against the
-                            # library's 21.8 at 16 rows, 19.9 against 21.8 at 12); else the library is: at 16 rows the
-                            # gate/up projection of Qwen3-8B takes 42.4 us against 34.7 us (16 rows of x of 4,096 no
-                            # longer fit into the L1 that the ring leaves)
+                            # two-tile form) it is where the rows of x cost it nothing or little: rows of up to 2,048 or 4,096
+                            # values (the ring product then keeps its pieces of x in registers: at 16 rows q/k/v 12.1 us
+                            # against the library's 12.1, o 9.2 against 9.3, gate/up with the SiLU 36.0 against 34.7 + 3 for
+                            # the separate SiLU kernel, the head 197 against 208) and matrices of up to 16 M weights (the
+STREAM_WIDE_MAX_WEIGHT = 1 << 24   # 0.6B model's); else the library is faster or as fast (x no longer fits into the L1 that the
+                            # ring leaves: at the 32B sizes a step of 16 rows loses 7 % with the ring on the long rows)
 
 FEW_ROWS_KERNEL = os.environ.get("QWB200_FEW_ROWS", "ring")     # "ring" (gemm_ring, the default) or "stream" (gemm_stream, the
                                                                 # kernel before it, kept for comparison)
@@ -50,8 +51,11 @@ FEW_ROWS_KERNEL = os.environ.get("QWB200_FEW_ROWS", "ring")     # "ring" (gemm_r
 def _few_rows(M: int, weight: torch.Tensor) -> bool:
     """Whether M rows of this bfloat16 weight go to the own few-rows product (else to the library).  The choice follows
     from the shape alone, so the same trace gives the same bits in every process."""
-    return M <= STREAM_MAX_ROWS or (M <= ops.STREAM_M and (weight.numel() <= STREAM_WIDE_MAX_WEIGHT or
-                                                           weight.shape[1] >= STREAM_WIDE_MIN_INNER))
+    if M <= STREAM_MAX_ROWS:
+        return True
+    K = weight.shape[1]
+    keeps_x = FEW_ROWS_KERNEL == "ring" and -(-K // ops.RING_STAGE_K) in ops.RING_KEEPS_X_STAGES
+    return M <= ops.STREAM_M and (keeps_x or weight.numel() <= STREAM_WIDE_MAX_WEIGHT)
 
 
 def _stream(x, weight, add_to, kind):

@@ -427,10 +427,12 @@ def test_gemm_stream(M, N, K):
 
 
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
-@pytest.mark.parametrize("N,K", [(37, 96), (200, 200), (16, 4104), (129, 1024), (5000, 8200), (2400, 512), (4096, 520)])
+@pytest.mark.parametrize("N,K", [(37, 96), (200, 200), (16, 4104), (129, 1024), (5000, 8200), (2400, 512), (4096, 520),
+                                 (304, 4096), (2400, 2048), (5008, 3848)])
 def test_gemm_ring(M, N, K):
-    """The few-rows product that streams W through a ring of bulk copies: tiles of 16 rows and stages of 512 k that the
-    sizes do not fill, more tiles than blocks (5000 rows), one stage and many; plain, residual-add and SwiGLU."""
+    """The few-rows product that streams W through a ring of TMA boxes: tiles of 16 rows and stages of 256 k that the
+    sizes do not fill, more tiles than blocks (5000 rows), one stage and many; rows of 8 or 16 stages, where the warps keep
+    their pieces of x in registers (K 2,048, 4,096 and 3,848: the last stage is not full); plain, residual-add and SwiGLU."""
     g = torch.Generator().manual_seed(M * 1000 + K)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
     w = torch.randn(N, K, generator=g).to(torch.bfloat16).to(DEV)

@@ -409,7 +409,7 @@ def main() -> int:
         return 0
     layers = args.layers or QWEN3_8B["num_hidden_layers"]
     max_batch = max(args.batch, 1 if args.skip_points else 64)
-    engine, cfgd = make_engine(QWEN3_8B, layers, max_batch, PROMPT_LEN + 512)
+    engine, cfgd = make_engine(QWEN3_8B, layers, max_batch, max(PROMPT_LEN + 512, -(-(PREFILL_TOKENS + 64) // max_batch)))
     rng = np.random.default_rng(0)
     wbytes = weight_bytes(engine)
     kv_tok = kv_bytes_per_token(cfgd, layers)

@@ -407,7 +407,8 @@ attn_mma_decode_kernel(const FusedQKV fused, const bf16* q, const bf16* k_pool, 
     // loads that do not go through the read-only cache (q, k_pool and v_pool are not __restrict__ for that reason: what
     // the kernel before wrote while this one was resident must not be read as constant data).  Not FUSED, the kernel
     // before it wrote the new key and value into the cache, so the wait comes first.
-    if (!FUSED) pdl_wait();
+    const bool page_first = FUSED && fused.store_kv;     // a cache that another layer's kernel fills in this step: wait first
+    if (!page_first) pdl_wait();
     pdl_launch_dependents();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     // blocks start in the order of x, then y, then z: the run is z, so that the runs that only longer sequences have
@@ -441,7 +442,7 @@ attn_mma_decode_kernel(const FusedQKV fused, const bf16* q, const bf16* k_pool, 
         cp_async_commit();
     }
 
-    if (FUSED) pdl_wait();
+    if (page_first) pdl_wait();
     int row_pos[2];
     uint32_t qf[HD / 16][4];
     {
@@ -553,11 +554,10 @@ attn_mma_decode_kernel(const FusedQKV fused, const bf16* q, const bf16* k_pool, 
 #define AM_COMBINE_THREADS 128
 #define AM_COMBINE_FAST 16         // up to this many runs are merged without shared memory
 __global__ void __launch_bounds__(AM_COMBINE_THREADS)
-attn_mma_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_m,
-                        const float* __restrict__ part_l, const int* __restrict__ seq_len, bf16* __restrict__ out, int Hq,
-                        int hd, int window, int runs_target, int run_pages_max, int max_runs) {
+attn_mma_combine_kernel(const float* part_acc, const float* part_m, const float* part_l, const int* __restrict__ seq_len,
+                        bf16* __restrict__ out, int Hq, int hd, int window, int runs_target, int run_pages_max, int max_runs) {
+    pdl_launch_dependents();            // the trigger first: the kernel after this one may start while attention still runs
     pdl_wait();
-    pdl_launch_dependents();
     extern __shared__ float weight[];                     // [max_runs]
     __shared__ float red[AM_COMBINE_THREADS / 32];
     const int h = blockIdx.x, b = blockIdx.y;
@@ -576,9 +576,9 @@ attn_mma_combine_kernel(const float* __restrict__ part_acc, const float* __restr
 #pragma unroll
         for (int i = 0; i < AM_COMBINE_FAST; ++i) {
             const bool in = i < n_runs;
-            mr[i] = in ? part_m[row + run_first + i] : -INFINITY;
-            lr[i] = in ? part_l[row + run_first + i] : 0.f;
-            ar[i] = in && d < hd ? part_acc[(row + run_first + i) * hd + d] : 0.f;
+            mr[i] = in ? __ldcg(part_m + row + run_first + i) : -INFINITY;       // written by the kernel before: coherent loads
+            lr[i] = in ? __ldcg(part_l + row + run_first + i) : 0.f;
+            ar[i] = in && d < hd ? __ldcg(part_acc + (row + run_first + i) * hd + d) : 0.f;
         }
         float M = -INFINITY;
 #pragma unroll
@@ -668,7 +668,7 @@ static int launch_decode(const FusedQKV& fused, const void* q, const void* k_poo
         max_runs, Gc, chunks);
     if (int rc = qwb_check_launch("attn_mma_decode")) return rc;
     if (max_runs > 1) {
-        qwb_launch(attn_mma_combine_kernel, dim3(Hq, B), AM_COMBINE_THREADS, (size_t)max_runs * sizeof(float), stream, part_acc, part_m,
+        qwb_launch_link(B, attn_mma_combine_kernel, dim3(Hq, B), AM_COMBINE_THREADS, (size_t)max_runs * sizeof(float), stream, part_acc, part_m,
                    part_l, seq_len, (bf16*)out, Hq, HD, window, runs_target, run_pages_max, max_runs);
         return qwb_check_launch("attn_mma_combine");
     }

@@ -104,6 +104,22 @@ static cudaError_t qwb_launch_early(void (*kernel)(KArgs...), dim3 grid, dim3 bl
     return qwb_launch_attr(qwb_pdl_mode() >= 1, kernel, grid, block, smem, stream, args...);
 }
 
+// For the small kernels between two early-launched ones (a norm, the merge of attention's runs): launched early as well,
+// with their trigger before their wait, they let the kernel after them start (and fill its ring) while the kernel before
+// them still runs.  Measured on decode steps: 4 % faster with one row, 2 % with 2 to 4 rows, nothing at 8 rows at the
+// Qwen3-8B sizes (attention's blocks and a ring do not fit into one SM's shared memory together), 5 % slower with 8 rows
+// at the 32B sizes: so only steps of up to QWB_LINK_MAX_ROWS rows.  QWB200_CHAIN=<rows> sets another bound, for experiments.
+#define QWB_LINK_MAX_ROWS 4
+static int qwb_link_max_rows() {
+    static int rows = -1;
+    if (rows < 0) { const char* e = getenv("QWB200_CHAIN"); rows = (e && e[0]) ? atoi(e) : QWB_LINK_MAX_ROWS; }
+    return rows;
+}
+template <typename... KArgs, typename... Args>
+static cudaError_t qwb_launch_link(int rows, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    return qwb_launch_attr(qwb_pdl_mode() == 2 || (qwb_pdl_mode() == 1 && rows <= qwb_link_max_rows()), kernel, grid, block, smem, stream, args...);
+}
+
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(bf16 x) { return __bfloat162float(x); }
 template <typename T> __device__ __forceinline__ T from_f32(float x);

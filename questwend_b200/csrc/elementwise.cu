@@ -55,6 +55,9 @@ extern "C" int qwb_embed_gather(const int* ids, const void* table, int table_dty
 // (the reference: core/runtime.cpp:1018-1019, ggml-cuda/norm.cu:76-155.)
 //   x      [rows_in, D] float   the residual stream
 //   delta  [rows_in, D] float   optional: the sum x + delta is formed in 32-bit first
+//   planes [P, rows_in, D] float optional, instead of delta: a product that its kernel left as sums over pieces of k
+//                                (gemm_ring's split form); columns 16 t .. 16 t + 15 have plane_count[t] <= 4 planes, which
+//                                are added onto x in the order of the planes
 //   sum_out[rows_in, D] float   optional: where x + delta is written (may be x itself)
 //   rows   [n_rows] int         optional: row r of the output is made from row rows[r]
 //   out    [n_rows, D]  float or bfloat16
@@ -77,12 +80,15 @@ template <> struct Pack4<bf16> {
 };
 
 // VEC: rows are a multiple of 4 wide and 16-byte aligned, so everything moves four values at a time.
+#define RMS_MAX_PLANES 4
+#define RMS_PLANE_COLS 16
 template <typename TOut, bool VEC>
-__global__ void rmsnorm_kernel(const float* x, const float* __restrict__ delta,
+__global__ void rmsnorm_kernel(const float* x, const float* delta, const float* planes,
+                               const unsigned char* __restrict__ plane_count, size_t plane_stride,
                                float* sum_out, const float* __restrict__ w, TOut* __restrict__ out,
                                const int* __restrict__ rows, int D, float eps) {
+    pdl_launch_dependents();            // the trigger first: the kernel after this one may start before the one before it ends
     pdl_wait();
-    pdl_launch_dependents();
     extern __shared__ __align__(16) float row_cache[];
     __shared__ float red[32];
     const int r = blockIdx.x;
@@ -94,8 +100,21 @@ __global__ void rmsnorm_kernel(const float* x, const float* __restrict__ delta,
         float4* s4 = sum_out ? reinterpret_cast<float4*>(sum_out + src) : nullptr;
         float4* c4 = reinterpret_cast<float4*>(row_cache);
         for (int i = threadIdx.x; i < D / 4; i += blockDim.x) {
+            // plain loads (x and delta are not __restrict__: never the read-only path, see pdl_wait); with __ldcg a norm
+            // of 8 rows of 4,096 took 1.4 us longer under the ring fill of the product that follows
             float4 v = x4[i];
             if (d4) { const float4 d = d4[i]; v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w; }
+            if (planes) {
+                const int n_planes = plane_count[4 * i / RMS_PLANE_COLS];
+                const float4* p4 = reinterpret_cast<const float4*>(planes + src) + i;
+                float4 d[RMS_MAX_PLANES];
+#pragma unroll
+                for (int p = 0; p < RMS_MAX_PLANES; ++p)
+                    if (p < n_planes) d[p] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p4) + p * plane_stride);
+#pragma unroll
+                for (int p = 0; p < RMS_MAX_PLANES; ++p)
+                    if (p < n_planes) { v.x += d[p].x; v.y += d[p].y; v.z += d[p].z; v.w += d[p].w; }
+            }
             if (s4) s4[i] = v;
             c4[i] = v;
             ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
@@ -104,6 +123,8 @@ __global__ void rmsnorm_kernel(const float* x, const float* __restrict__ delta,
         for (int i = threadIdx.x; i < D; i += blockDim.x) {
             float v = x[src + i];
             if (delta) v += delta[src + i];
+            if (planes)
+                for (int p = 0, n_planes = plane_count[i / RMS_PLANE_COLS]; p < n_planes; ++p) v += planes[p * plane_stride + src + i];
             if (sum_out) sum_out[src + i] = v;
             row_cache[i] = v;
             ss += v * v;
@@ -125,35 +146,74 @@ __global__ void rmsnorm_kernel(const float* x, const float* __restrict__ delta,
 }
 
 template <typename TOut>
-static int launch_rmsnorm(const float* x, const float* delta, float* sum_out, const float* w, TOut* out, const int* rows,
+static int launch_rmsnorm(const float* x, const float* delta, const float* planes, const unsigned char* plane_count,
+                          size_t plane_stride, float* sum_out, const float* w, TOut* out, const int* rows,
                           int n_rows, int D, float eps, size_t smem, cudaStream_t stream) {
     const bool vec = D % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0 &&
-                     (!delta || (uintptr_t)delta % 16 == 0) && (!sum_out || (uintptr_t)sum_out % 16 == 0);
+                     (!delta || (uintptr_t)delta % 16 == 0) && (!sum_out || (uintptr_t)sum_out % 16 == 0) &&
+                     (!planes || ((uintptr_t)planes % 16 == 0 && plane_stride % 4 == 0));
     const int work = vec ? D / 4 : D;
     const int block = work >= 1024 ? 256 : (work >= 256 ? 128 : 64);
     cudaError_t e = cudaSuccess;
     if (vec) {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_kernel<TOut, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "rmsnorm: %s", cudaGetErrorString(e));
-        qwb_launch(rmsnorm_kernel<TOut, true>, n_rows, block, smem, stream, x, delta, sum_out, w, out, rows, D, eps);
+        qwb_launch_link(n_rows, rmsnorm_kernel<TOut, true>, n_rows, block, smem, stream, x, delta, planes, plane_count, plane_stride, sum_out, w, out, rows, D, eps);
     } else {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_kernel<TOut, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "rmsnorm: %s", cudaGetErrorString(e));
-        qwb_launch(rmsnorm_kernel<TOut, false>, n_rows, block, smem, stream, x, delta, sum_out, w, out, rows, D, eps);
+        qwb_launch(rmsnorm_kernel<TOut, false>, n_rows, block, smem, stream, x, delta, planes, plane_count, plane_stride, sum_out, w, out, rows, D, eps);
     }
     return qwb_check_launch("rmsnorm");
+}
+
+static int rmsnorm_any(const float* x, const float* delta, const float* planes, const unsigned char* plane_count,
+                       size_t plane_stride, float* sum_out, const float* w, void* out, int out_dtype, const int* rows,
+                       int n_rows, int D, float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (D <= 0) return qwb_fail(QWB_ERR_ARG, "rmsnorm: bad width %d", D);
+    const size_t smem = (size_t)D * sizeof(float);
+    if (smem > 200 * 1024) return qwb_fail(QWB_ERR_ARG, "rmsnorm: width %d does not fit in shared memory (max %d)", D, 200 * 1024 / 4);
+    if (out_dtype == QWB_DT_F32)
+        return launch_rmsnorm<float>(x, delta, planes, plane_count, plane_stride, sum_out, w, (float*)out, rows, n_rows, D, eps, smem, stream);
+    if (out_dtype == QWB_DT_BF16)
+        return launch_rmsnorm<bf16>(x, delta, planes, plane_count, plane_stride, sum_out, w, (bf16*)out, rows, n_rows, D, eps, smem, stream);
+    return qwb_fail(QWB_ERR_ARG, "rmsnorm: unknown dtype %d", out_dtype);
 }
 
 extern "C" int qwb_rmsnorm(const float* x, const float* delta, float* sum_out, const float* w,
                            void* out, int out_dtype, const int* rows, int n_rows, int D, float eps,
                            cudaStream_t stream) {
-    if (n_rows <= 0) return 0;
-    if (D <= 0) return qwb_fail(QWB_ERR_ARG, "rmsnorm: bad width %d", D);
-    const size_t smem = (size_t)D * sizeof(float);
-    if (smem > 200 * 1024) return qwb_fail(QWB_ERR_ARG, "rmsnorm: width %d does not fit in shared memory (max %d)", D, 200 * 1024 / 4);
-    if (out_dtype == QWB_DT_F32) return launch_rmsnorm<float>(x, delta, sum_out, w, (float*)out, rows, n_rows, D, eps, smem, stream);
-    if (out_dtype == QWB_DT_BF16) return launch_rmsnorm<bf16>(x, delta, sum_out, w, (bf16*)out, rows, n_rows, D, eps, smem, stream);
-    return qwb_fail(QWB_ERR_ARG, "rmsnorm: unknown dtype %d", out_dtype);
+    return rmsnorm_any(x, delta, nullptr, nullptr, 0, sum_out, w, out, out_dtype, rows, n_rows, D, eps, stream);
+}
+
+// The same with a product in planes instead of delta: planes [n_planes, rows_in, D], plane_count [ceil(D / 16)] bytes.
+extern "C" int qwb_rmsnorm_planes(const float* x, const float* planes, const unsigned char* plane_count, int n_planes,
+                                  int rows_in, float* sum_out, const float* w, void* out, int out_dtype, const int* rows,
+                                  int n_rows, int D, float eps, cudaStream_t stream) {
+    if (n_planes < 1 || n_planes > RMS_MAX_PLANES)
+        return qwb_fail(QWB_ERR_ARG, "rmsnorm: %d planes; this kernel adds up to %d", n_planes, RMS_MAX_PLANES);
+    return rmsnorm_any(x, nullptr, planes, plane_count, (size_t)rows_in * D, sum_out, w, out, out_dtype, rows, n_rows, D, eps, stream);
+}
+
+// x[t, :] += the planes of a product (as above), for a consumer that is not this norm.
+__global__ void add_planes_kernel(float* x, const float* planes, const unsigned char* __restrict__ plane_count,
+                                  size_t plane_stride, size_t n, int D) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float v = x[i];
+        for (int p = 0, n_planes = plane_count[(i % D) / RMS_PLANE_COLS]; p < n_planes; ++p) v += planes[p * plane_stride + i];
+        x[i] = v;
+    }
+}
+
+extern "C" int qwb_add_planes(float* x, const float* planes, const unsigned char* plane_count, int T, int D, cudaStream_t stream) {
+    if (T <= 0 || D <= 0) return 0;
+    const size_t n = (size_t)T * D;
+    const int block = 256, grid = (int)((n + block - 1) / block < 1184 ? (n + block - 1) / block : 1184);
+    qwb_launch(add_planes_kernel, grid, block, 0, stream, x, planes, plane_count, n, n, D);
+    return qwb_check_launch("add_planes");
 }
 
 // ---------------------------------------------------------------------------------

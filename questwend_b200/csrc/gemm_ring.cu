@@ -23,6 +23,14 @@
 // timing.  Every mbarrier wait is bounded: after a second the block raises *error, stops waiting and asking, and runs
 // to its end.  (The reference's counterpart for few rows: ggml-cuda/mmvf.cu and mmf.cuh; it has no counterpart of the
 // ring.)
+//
+// The split form (GR_EPI_SPLIT).  With whole tiles a matrix of 256 tiles keeps 148 SMs busy for two rounds of which the
+// second is three quarters empty (4,096 rows: 86 % of the stream; 5,120 rows: 72 %).  In the split form every block takes
+// an equal, contiguous share of all (tile, k) stages instead, so a tile may be cut between two or three blocks that
+// follow one another.  Nobody waits for anybody: each block writes the sum over its piece of the tile into the piece's
+// own plane of `y` ([pieces][M][N]; the piece of lowest k is plane 0), and the kernel that consumes the product - the
+// norm that adds it onto the residual stream - adds a tile's planes in that order.  How many planes a tile has follows
+// from N, K and the number of blocks alone (the host hands the consumer a table), so the result does not depend on timing.
 #include "common.cuh"
 
 #include <cuda.h>
@@ -32,6 +40,7 @@
 
 #define GR_EPI_PLAIN 0                // y = product (+ residual)
 #define GR_EPI_SWIGLU 1               // rows of W: for every 8 features their 8 gate rows, then their 8 up rows
+#define GR_EPI_SPLIT 2                // equal shares of stages per block; y = [pieces][M][N], see above
 
 __device__ __forceinline__ uint32_t gr_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void gr_mbar_init(uint64_t* bar, uint32_t count) {
@@ -107,8 +116,13 @@ gemm_ring_kernel(const bf16* x, const __grid_constant__ CUtensorMap map_w, const
     const int n_tiles = (N + GR_ROWS - 1) / GR_ROWS;
     const int n_stages = (K + GR_KC - 1) / GR_KC;           // stages per tile
     const int chunks = K >> 3;                               // 16-byte chunks per row of W and of x
-    const int my_tiles = (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    const int total = my_tiles * n_stages;                   // stages that pass through this block's ring
+    // the stages that pass through this block's ring: those of its tiles (tile b, b + blocks, ...), or, in the split form,
+    // stages [begin, begin + total) of all the matrix's stages, counted tile by tile
+    constexpr bool SPLIT = EPI == GR_EPI_SPLIT;
+    const long long all_stages = (long long)n_tiles * n_stages;
+    const int begin = SPLIT ? (int)(all_stages * blockIdx.x / gridDim.x) : 0;
+    const int total = SPLIT ? (int)(all_stages * (blockIdx.x + 1) / gridDim.x) - begin
+                            : (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x * n_stages;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < GR_STAGES; ++s) gr_mbar_init(full_bar + s, 1);      // the arrival that announces the stage's bytes
@@ -125,7 +139,9 @@ gemm_ring_kernel(const bf16* x, const __grid_constant__ CUtensorMap map_w, const
     // before is pending, and be told "done").  And a thread can start TMA copies only so fast (about 0.15 us and 0.02 us a
     // KB, measured), so one producer cannot feed an SM; here every warp asks for its own stages.
     auto request = [&](int i) {                              // lane 0: ask for stage i into its slot
-        const int slot = i % GR_STAGES, tile = blockIdx.x + (i / n_stages) * gridDim.x, k0 = (i % n_stages) * GR_KC;
+        const int slot = i % GR_STAGES;
+        const int tile = SPLIT ? (begin + i) / n_stages : blockIdx.x + (i / n_stages) * gridDim.x;
+        const int k0 = (SPLIT ? (begin + i) % n_stages : i % n_stages) * GR_KC;
         const int boxes = min(GR_KC / GR_BOX_K, (K - k0 + GR_BOX_K - 1) / GR_BOX_K);          // none wholly beyond K
         gr_mbar_expect_tx(full_bar + slot, (uint32_t)boxes * GR_BOX_BYTES);
         for (int b = 0; b < boxes; ++b)
@@ -148,8 +164,10 @@ gemm_ring_kernel(const bf16* x, const __grid_constant__ CUtensorMap map_w, const
         x_ok[j] = m < M;
         xr[j] = reinterpret_cast<const uint4*>(x + (size_t)min(m, M - 1) * K);
     }
-    // SPW > 0: a tile has exactly SPW * GR_WARPS stages, so a warp meets the same k in every tile (stages warp, warp + 8, ...)
-    // and keeps its pieces of x in registers for the whole product instead of asking L1 for them at every stage.
+    // SPW > 0: a tile has exactly SPW * GR_WARPS stages, so a warp meets the same k in every tile (stages kfix, kfix + 8, ...
+    // of a tile, kfix = warp unless the block's share begins in the middle of a tile) and keeps its pieces of x in
+    // registers for the whole product instead of asking L1 for them at every stage.
+    const int kfix = (begin + warp) % GR_WARPS;
     uint4 xkeep[SPW > 0 ? SPW : 1][KB][NT];
     if (SPW > 0) {
 #pragma unroll
@@ -158,20 +176,25 @@ gemm_ring_kernel(const bf16* x, const __grid_constant__ CUtensorMap map_w, const
             for (int kb = 0; kb < KB; ++kb)
 #pragma unroll
                 for (int j = 0; j < NT; ++j) {
-                    const int c = (warp + q * GR_WARPS) * (GR_KC / 8) + kb * 4 + t;
+                    const int c = (kfix + q * GR_WARPS) * (GR_KC / 8) + kb * 4 + t;
                     xkeep[q][kb][j] = (c < chunks && x_ok[j]) ? __ldcg(xr[j] + c) : zero;
                 }
     }
-    int base = 0, buf = 0;                                   // base: the ring's count of stages before this tile
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, buf ^= 1, base += n_stages) {
+    // The block's pieces: stages [i_lo, i_lo + n_here) of its ring are stages [ks_lo, ks_lo + n_here) of one tile (a whole
+    // tile unless the split form cuts it).
+    int buf = 0;
+    for (int i_lo = 0; i_lo < total; buf ^= 1) {
+        const int tile = SPLIT ? (begin + i_lo) / n_stages : blockIdx.x + (i_lo / n_stages) * gridDim.x;
+        const int ks_lo = SPLIT ? (begin + i_lo) % n_stages : 0;
+        const int n_here = min(n_stages - ks_lo, total - i_lo);
         const int n0 = tile * GR_ROWS;
         float acc[NT][4];
 #pragma unroll
         for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-        // one stage: wait for its bytes, multiply, ask for the stage that comes into the slot next
-        auto stage = [&](int s, const uint4 (&xv)[KB][NT]) {
-            const int i = base + s, slot = i % GR_STAGES, use = i / GR_STAGES;
-            const int c0 = s * (GR_KC / 8);                  // the stage's first 16-byte chunk of a row
+        // one stage (i of the ring, ks of the tile): wait for its bytes, multiply, ask for the stage that comes into the slot next
+        auto stage = [&](int i, int ks, const uint4 (&xv)[KB][NT]) {
+            const int slot = i % GR_STAGES, use = i / GR_STAGES;
+            const int c0 = ks * (GR_KC / 8);                 // the stage's first 16-byte chunk of a row
             gr_wait(full_bar + slot, use & 1, failed, error, 2);
             const unsigned char* st = stages + (size_t)slot * GR_STAGE_BYTES;
 #pragma unroll
@@ -196,23 +219,28 @@ gemm_ring_kernel(const bf16* x, const __grid_constant__ CUtensorMap map_w, const
         };
         if (SPW > 0) {
 #pragma unroll
-            for (int q = 0; q < (SPW > 0 ? SPW : 1); ++q) stage(warp + q * GR_WARPS, xkeep[q]);
+            for (int q = 0; q < (SPW > 0 ? SPW : 1); ++q) {
+                const int ks = kfix + q * GR_WARPS;          // stage ks of the tile is stage i_lo + ks - ks_lo of the ring
+                if (!SPLIT || (ks >= ks_lo && ks < ks_lo + n_here)) stage(i_lo + ks - ks_lo, ks, xkeep[q]);
+            }
         } else {
-            for (int s = (warp - base % GR_WARPS + GR_WARPS) % GR_WARPS; s < n_stages; s += GR_WARPS) {
+            for (int i = i_lo + (warp - i_lo % GR_WARPS + GR_WARPS) % GR_WARPS; i < i_lo + n_here; i += GR_WARPS) {
                 // a thread's 16 bytes are eight consecutive k of one row; W and x use the same renumbering of k inside a
                 // block of 32, so no shuffle is needed (the sum over k does not care about the order).  The rows of x are
                 // asked for before the wait for W: they do not depend on it.
+                const int ks = ks_lo + i - i_lo;
                 uint4 xv[KB][NT];
 #pragma unroll
                 for (int kb = 0; kb < KB; ++kb)
 #pragma unroll
                     for (int j = 0; j < NT; ++j) {
-                        const int c = s * (GR_KC / 8) + kb * 4 + t;
+                        const int c = ks * (GR_KC / 8) + kb * 4 + t;
                         xv[kb][j] = (c < chunks && x_ok[j]) ? __ldcg(xr[j] + c) : zero;
                     }
-                stage(s, xv);
+                stage(i, ks, xv);
             }
         }
+        i_lo += n_here;
         float* mine = part + (size_t)buf * GR_WARPS * NT * 128;
 #pragma unroll
         for (int j = 0; j < NT; ++j)
@@ -221,7 +249,12 @@ gemm_ring_kernel(const bf16* x, const __grid_constant__ CUtensorMap map_w, const
         __syncthreads();
         // c0: (row g, col 2t), c1: (row g, col 2t+1), c2: (row g+8, col 2t), c3: (row g+8, col 2t+1);
         // rows are rows of W (outputs n), columns are rows of x (m).
-        if (EPI == GR_EPI_PLAIN) {
+        if (EPI == GR_EPI_PLAIN || SPLIT) {
+            // split form: the plane of this piece = how many blocks before this one hold earlier pieces of the tile
+            // (the tile's first stage lies in block ((first + 1) * blocks - 1) / all_stages)
+            size_t plane = 0;
+            if (SPLIT && ks_lo > 0)
+                plane = (size_t)(blockIdx.x - (int)((((long long)tile * n_stages + 1) * gridDim.x - 1) / all_stages)) * M * N;
             for (int idx = threadIdx.x; idx < NT * 4 * 32; idx += GR_WARPS * 32) {
                 const int j = idx >> 7, r = (idx >> 5) & 3, ln = idx & 31;
                 float sum = 0.f;
@@ -230,7 +263,8 @@ gemm_ring_kernel(const bf16* x, const __grid_constant__ CUtensorMap map_w, const
                 const int n = n0 + (ln >> 2) + ((r & 2) ? 8 : 0), m = 8 * j + 2 * (ln & 3) + (r & 1);
                 if (n < N && m < M) {
                     const size_t at = (size_t)m * N + n;
-                    y[at] = residual ? residual[at] + sum : sum;
+                    if (SPLIT) y[plane + at] = sum;
+                    else y[at] = residual ? residual[at] + sum : sum;
                 }
             }
         } else {                                             // rows g are gates, rows g + 8 the ups of the same features
@@ -287,7 +321,7 @@ static int gr_make_map(CUtensorMap* map, const void* W, int rows, int K) {
 
 template <int NT, int EPI, int KC, int STAGES, int WARPS, int SPW>
 static int launch_ring_as(const bf16* x, const bf16* W, const float* residual, float* y, bf16* act, int M, int N, int K,
-                          int* error, cudaStream_t stream) {
+                          int* error, cudaStream_t stream, int split_blocks) {
     static_assert(STAGES % WARPS == 0, "a slot of the ring must always go to the same warp");
     CUtensorMap map_w;
     if (int rc = gr_make_map(&map_w, W, N, K)) return rc;
@@ -299,7 +333,8 @@ static int launch_ring_as(const bf16* x, const bf16* W, const float* residual, f
         sized = true;
     }
     const int n_tiles = (N + GR_ROWS - 1) / GR_ROWS;
-    const int grid = n_tiles < gr_sm_count() ? n_tiles : gr_sm_count();        // one block per SM, each walks over its tiles
+    int grid = n_tiles < gr_sm_count() ? n_tiles : gr_sm_count();              // one block per SM, each walks over its tiles
+    if (EPI == GR_EPI_SPLIT) grid = split_blocks;                              // the caller's: the planes' table follows from it
     qwb_launch_early(gemm_ring_kernel<NT, EPI, KC, STAGES, WARPS, SPW>, grid, WARPS * 32, smem, stream, x, map_w, residual, y, act, M, N, K, error);
     return qwb_check_launch("gemm_ring");
 }
@@ -312,12 +347,12 @@ static int launch_ring_as(const bf16* x, const bf16* W, const float* residual, f
 // and the head 197 against 13.3, 9.5, 42.0 and 233 without.
 template <int NT, int EPI>
 static int launch_ring(const bf16* x, const bf16* W, const float* residual, float* y, bf16* act, int M, int N, int K,
-                       int* error, cudaStream_t stream) {
+                       int* error, cudaStream_t stream, int split_blocks = 0) {
     // rows of up to 2,048 or 4,096 values: a warp meets the same one or two stages of k in every tile and keeps its x
     const int n_stages = (K + 255) / 256;
-    if (n_stages == 8) return launch_ring_as<NT, EPI, 256, 16, 8, 1>(x, W, residual, y, act, M, N, K, error, stream);
-    if (n_stages == 16) return launch_ring_as<NT, EPI, 256, 16, 8, 2>(x, W, residual, y, act, M, N, K, error, stream);
-    return launch_ring_as<NT, EPI, 256, 16, 8, 0>(x, W, residual, y, act, M, N, K, error, stream);
+    if (n_stages == 8) return launch_ring_as<NT, EPI, 256, 16, 8, 1>(x, W, residual, y, act, M, N, K, error, stream, split_blocks);
+    if (n_stages == 16) return launch_ring_as<NT, EPI, 256, 16, 8, 2>(x, W, residual, y, act, M, N, K, error, stream, split_blocks);
+    return launch_ring_as<NT, EPI, 256, 16, 8, 0>(x, W, residual, y, act, M, N, K, error, stream, split_blocks);
 }
 
 static int check_ring(const void* x, const void* W, int M, int K) {
@@ -335,6 +370,20 @@ extern "C" int qwb_gemm_ring(const void* x, const void* W, const float* residual
     if (int rc = check_ring(x, W, M, K)) return rc;
     if (M <= 8) return launch_ring<1, GR_EPI_PLAIN>((const bf16*)x, (const bf16*)W, residual, y, nullptr, M, N, K, error, stream);
     return launch_ring<2, GR_EPI_PLAIN>((const bf16*)x, (const bf16*)W, residual, y, nullptr, M, N, K, error, stream);
+}
+
+// The split form: `planes` float [pieces][M][N], pieces = the most blocks that share a tile when `blocks` blocks take equal
+// shares of the ceil(N / 16) * ceil(K / 256) stages (block b: stages [b * all / blocks, (b + 1) * all / blocks), counted
+// tile by tile).  Plane p of a tile's columns holds the sum over the tile's p-th piece; planes that a tile does not have
+// are not written.
+extern "C" int qwb_gemm_ring_split(const void* x, const void* W, float* planes, int M, int N, int K, int blocks, int* error,
+                                   cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (int rc = check_ring(x, W, M, K)) return rc;
+    const long long all_stages = (long long)((N + GR_ROWS - 1) / GR_ROWS) * ((K + 255) / 256);
+    if (blocks <= 0 || blocks > all_stages) return qwb_fail(QWB_ERR_ARG, "gemm_ring: %d blocks for %lld stages", blocks, all_stages);
+    if (M <= 8) return launch_ring<1, GR_EPI_SPLIT>((const bf16*)x, (const bf16*)W, nullptr, planes, nullptr, M, N, K, error, stream, blocks);
+    return launch_ring<2, GR_EPI_SPLIT>((const bf16*)x, (const bf16*)W, nullptr, planes, nullptr, M, N, K, error, stream, blocks);
 }
 
 // W [2 F, K]: for every 8 features their 8 gate rows, then their 8 up rows (F a multiple of 8).

@@ -24,6 +24,7 @@ CSRC = os.path.join(os.path.dirname(_HERE), "csrc")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "--shared", "-Xcompiler", "-fPIC"]
 EXTRA_FLAGS: dict[str, list[str]] = {}
+NVCC_FLAGS += os.environ.get("QWB200_NVCC_FLAGS", "").split()      # more flags (-D switches) for experiments; part of the stamp
 MODULES = ("elementwise", "rope_kv", "attention", "attention_mma", "attention_tc", "gemm_small", "gemm_stream", "gemm_ring", "gemm_tc", "sampling")
 
 _lock = threading.Lock()

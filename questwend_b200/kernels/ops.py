@@ -99,22 +99,30 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     """RMS norm of the rows of float32 ``x`` [T, D] (plus ``delta``), times ``weight``.
 
     With ``write_sum`` the sum x + delta replaces x.  With ``rows`` (int32) only
-    those rows are normed and the output has one row per entry.
+    those rows are normed and the output has one row per entry.  ``delta`` may be a ``SplitSum``
+    (a product left as sums over pieces of k): its planes are added in their order.
     """
     _need(x, "x", torch.float32, 2)
     _need(weight, "weight", torch.float32, 1)
     T, D = x.shape
     if weight.numel() != D:
         raise KernelError(f"rmsnorm: weight has {weight.numel()} entries for rows of {D}")
-    if delta is not None:
-        _need(delta, "delta", torch.float32, 2)
-        if delta.shape != x.shape:
-            raise KernelError(f"rmsnorm: delta {tuple(delta.shape)} does not match x {tuple(x.shape)}")
     n_rows = T
     if rows is not None:
         _need(rows, "rows", torch.int32, 1)
         n_rows = rows.numel()
     out = torch.empty((n_rows, D), dtype=out_dtype, device=x.device)
+    if isinstance(delta, SplitSum):
+        if tuple(delta.planes.shape[1:]) != (T, D):
+            raise KernelError(f"rmsnorm: planes {tuple(delta.planes.shape)} do not match x {tuple(x.shape)}")
+        _call("elementwise", "qwb_rmsnorm_planes", _ptr(x), _ptr(delta.planes), _ptr(delta.plane_count),
+              _i(delta.planes.shape[0]), _i(T), _ptr(x if write_sum else None), _ptr(weight), _ptr(out), _i(_dt(out_dtype)),
+              _ptr(rows), _i(n_rows), _i(D), _f(eps), _stream())
+        return out
+    if delta is not None:
+        _need(delta, "delta", torch.float32, 2)
+        if delta.shape != x.shape:
+            raise KernelError(f"rmsnorm: delta {tuple(delta.shape)} does not match x {tuple(x.shape)}")
     _call("elementwise", "qwb_rmsnorm", _ptr(x), _ptr(delta), _ptr(x if (write_sum and delta is not None) else None),
           _ptr(weight), _ptr(out), _i(_dt(out_dtype)), _ptr(rows), _i(n_rows), _i(D), _f(eps), _stream())
     return out
@@ -444,6 +452,91 @@ def gemm_ring(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor | No
     _call("gemm_ring", "qwb_gemm_ring", _ptr(x), _ptr(weight), _ptr(residual), _ptr(out), _i(M), _i(N), _i(K),
           _ptr(gemm_tc_error_word(x.device)), _stream())
     return out
+
+
+class SplitSum:
+    """A product [T, D] that its kernel left as sums over pieces of k: ``planes`` float32 [P, T, D], of which columns
+    16 t .. 16 t + 15 have ``plane_count[t]`` (uint8); the product is the sum of a column's planes in their order.
+    The kernel that consumes it adds them (``rmsnorm`` does; ``add_onto`` for any other consumer)."""
+    __slots__ = ("planes", "plane_count")
+
+    def __init__(self, planes: torch.Tensor, plane_count: torch.Tensor):
+        self.planes, self.plane_count = planes, plane_count
+
+    def add_onto(self, x: torch.Tensor) -> torch.Tensor:
+        """x += the product, in place."""
+        _need(x, "x", torch.float32, 2)
+        if tuple(self.planes.shape[1:]) != tuple(x.shape):
+            raise KernelError(f"SplitSum: planes {tuple(self.planes.shape)} do not match x {tuple(x.shape)}")
+        _call("elementwise", "qwb_add_planes", _ptr(x), _ptr(self.planes), _ptr(self.plane_count), _i(x.shape[0]),
+              _i(x.shape[1]), _stream())
+        return x
+
+    def total(self) -> torch.Tensor:
+        """The product as one tensor (a new one)."""
+        return self.add_onto(torch.zeros(self.planes.shape[1:], dtype=torch.float32, device=self.planes.device))
+
+
+RING_TILE_ROWS = 16             # rows of W per tile of gemm_ring
+RING_SPLIT_MAX_PLANES = 4       # the most planes that the consumers of a SplitSum add
+RING_SPLIT_BELOW = 0.93         # the split form is used when whole tiles would keep the SMs busy for less than this share
+_RING_PLANS: dict = {}
+
+
+def ring_split_plan(N: int, K: int, device):
+    """How gemm_ring's split form cuts an [N, K] matrix on this device: ``(blocks, n_planes, plane_count)``, or None when
+    whole tiles are as good (they fill the SMs' rounds to RING_SPLIT_BELOW or more, or a tile would be cut into more
+    than RING_SPLIT_MAX_PLANES pieces).  Block b takes stages [b * all / blocks, (b + 1) * all / blocks) of the
+    ceil(N / 16) * ceil(K / 256) stages, counted tile by tile; a tile's planes are the blocks that hold a part of it."""
+    dev = torch.device(device)
+    key = (N, K, dev.index or 0)
+    if key not in _RING_PLANS:
+        n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
+        _RING_PLANS[key] = _ring_split_plan(N, K, n_sm, dev)
+    return _RING_PLANS[key]
+
+
+def ring_split_counts(N: int, K: int, blocks: int):
+    """plane_count of every tile (a list), for ``blocks`` blocks: pure arithmetic, the same as the kernel's."""
+    n_tiles, n_stages = -(-N // RING_TILE_ROWS), -(-K // RING_STAGE_K)
+    all_stages = n_tiles * n_stages
+    counts = []
+    for t in range(n_tiles):
+        first = ((t * n_stages + 1) * blocks - 1) // all_stages            # the block that holds the tile's first stage
+        last = (((t + 1) * n_stages - 1 + 1) * blocks - 1) // all_stages   # ... and its last
+        counts.append(last - first + 1)
+    return counts
+
+
+def _ring_split_plan(N: int, K: int, n_sm: int, device):
+    n_tiles, n_stages = -(-N // RING_TILE_ROWS), -(-K // RING_STAGE_K)
+    rounds = -(-n_tiles // n_sm)
+    if n_tiles <= n_sm or n_tiles / (rounds * n_sm) >= RING_SPLIT_BELOW:
+        return None
+    counts = ring_split_counts(N, K, n_sm)
+    if max(counts) > RING_SPLIT_MAX_PLANES:
+        return None
+    return n_sm, max(counts), torch.tensor(counts, dtype=torch.uint8, device=device)
+
+
+def gemm_ring_split(x: torch.Tensor, weight: torch.Tensor, plan=None) -> SplitSum:
+    """x W^T by the ring kernel's split form: every block streams an equal share of W and leaves its sums over pieces of
+    tiles as planes (see ``SplitSum``).  ``plan``: from ``ring_split_plan`` (default: for this weight, which must have one)."""
+    _need(x, "x", torch.bfloat16, 2)
+    _need(weight, "weight", torch.bfloat16, 2)
+    M, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K:
+        raise KernelError(f"gemm_ring_split: x has {K} columns, the weight {weight.shape[1]}")
+    if plan is None:
+        plan = ring_split_plan(N, K, x.device)
+        if plan is None:
+            raise KernelError(f"gemm_ring_split: no split plan for a weight of {N} x {K}")
+    blocks, n_planes, plane_count = plan
+    planes = torch.empty((n_planes, M, N), dtype=torch.float32, device=x.device)
+    _call("gemm_ring", "qwb_gemm_ring_split", _ptr(x), _ptr(weight), _ptr(planes), _i(M), _i(N), _i(K), _i(blocks),
+          _ptr(gemm_tc_error_word(x.device)), _stream())
+    return SplitSum(planes, plane_count)
 
 
 def gemm_ring_swiglu(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:

@@ -12,7 +12,7 @@ from ..kernels import ops
 from ..kernels.limits import head_dim_refusal
 from ..weights.manifest import MATRIX, NORM_WEIGHT, VECTOR, TensorSpec
 from .base import KVSpec, Mixer, take_weight
-from .linear import kernel_modules as linear_modules, linear
+from .linear import kernel_modules as linear_modules, linear, linear_onto
 from .registry import register_mixer
 
 FUSED_DECODE_MAX_BATCH = 16     # up to here a kernel less per layer pays (3-4 % of a small model's step); with more sequences
@@ -113,8 +113,7 @@ class GroupedQueryAttention(Mixer):
                 att = ops.attn_prefill(q, cache.k_pool, cache.v_pool, table, ctx.cu_seqlens, ctx.pos0, ctx.max_new,
                                        self.scale, window=self.window)
         if residual is not None:
-            linear(att, self.w_o, add_to=residual)      # the residual sum, in the product's epilogue
-            return None
+            return linear_onto(att, self.w_o, residual)     # None: the residual sum was made in the product's epilogue
         return linear(att, self.w_o)
 
 

@@ -161,7 +161,8 @@ class Mixer(Part):
     def state_spec(self) -> StateSpec | None:
         return None
 
-    adds_to_residual = False    # True: forward(..., residual=h) adds its output onto h in place and returns None
+    adds_to_residual = False    # True: forward(..., residual=h) adds its output onto h in place and returns None, or
+                                # returns what is still to be added (a tensor, or a SplitSum that the next norm adds)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: UnitCache) -> torch.Tensor:
         raise NotImplementedError

@@ -98,6 +98,29 @@ def linear(x: torch.Tensor, weight: torch.Tensor, add_to: torch.Tensor | None = 
     return torch.mm(x, weight.t())
 
 
+def linear_onto(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor):
+    """The product x W^T that is to be added onto ``residual`` (float32 [M, N]).  Returns None when it was added in place
+    (in the product's epilogue), or the product still to be added, as a ``SplitSum``: few bfloat16 rows times a matrix
+    whose whole tiles would leave the SMs' last round mostly empty go to the ring product's split form, and the norm that
+    follows adds its planes (``settle`` for any other consumer)."""
+    M, K = x.shape
+    if (FEW_ROWS_KERNEL == "ring" and weight.dtype == torch.bfloat16 and M <= ops.STREAM_M and K % 8 == 0
+            and _few_rows(M, weight)):
+        plan = ops.ring_split_plan(weight.shape[0], K, x.device)
+        if plan is not None:
+            return ops.gemm_ring_split(x, weight, plan)
+    linear(x, weight, add_to=residual)
+    return None
+
+
+def settle(h: torch.Tensor, delta, norm=None):
+    """What a block hands its norm: ``delta`` as it is if the norm can add it, else added onto ``h`` (returns None)."""
+    if isinstance(delta, ops.SplitSum) and not getattr(norm, "adds_split_sums", False):
+        delta.add_onto(h)
+        return None
+    return delta
+
+
 def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor, out_dtype: torch.dtype, interleave: int = 0) -> torch.Tensor:
     """silu(x Wg^T) * (x Wu^T) for the stacked weight [2F, K] -> [M, F] in ``out_dtype``.  ``interleave`` 0: gate rows
     first; ``ops.GATE_UP_GROUP``: gate and up rows interleaved in groups of that many features, which lets the products

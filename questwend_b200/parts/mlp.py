@@ -6,7 +6,7 @@ import torch
 from ..kernels import ops
 from ..weights.manifest import MATRIX, TensorSpec
 from .base import FeedForward, take_weight
-from .linear import kernel_modules as linear_modules, linear, linear_swiglu
+from .linear import kernel_modules as linear_modules, linear, linear_onto, linear_swiglu
 from .registry import register_feed_forward
 
 
@@ -50,8 +50,7 @@ class GatedMLP(FeedForward):
     def forward(self, x, ctx, residual=None):
         act = linear_swiglu(x, self.w_gate_up, self.runtime.dtype, self.interleave)
         if residual is not None:
-            linear(act, self.w_down, add_to=residual)
-            return None
+            return linear_onto(act, self.w_down, residual)  # None: the residual sum was made in the product's epilogue
         return linear(act, self.w_down)
 
 

@@ -9,6 +9,7 @@ from __future__ import annotations
 import torch
 
 from ..parts.base import BoundWeights, Runtime, StepContext, UnitCache
+from ..parts.linear import settle
 from ..parts.registry import build_part
 from ..weights.manifest import TensorSpec
 from .plan import ModelPlan
@@ -83,5 +84,5 @@ class Model:
             h, delta = self.blocks[run.layer].forward(h, delta, ctx, unit_caches[i])
         if want_rows.numel() == 0:
             return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=h.device)
-        x = self.final_norm.forward(h, delta, rows=want_rows)
+        x = self.final_norm.forward(h, settle(h, delta, self.final_norm), rows=want_rows)
         return self.head.forward(x)

@@ -139,6 +139,8 @@ class Part:
 class Norm(Part):
     """y = norm(x + delta) over rows; x float32 [T, D]."""
 
+    adds_split_sums = False     # True: ``delta`` may also be a SplitSum (a product left as sums over pieces of k)
+
     def forward(self, x, delta=None, write_sum=False, rows=None, out_dtype=None) -> torch.Tensor:
         raise NotImplementedError
 

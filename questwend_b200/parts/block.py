@@ -2,12 +2,15 @@
 (the reference: core/runtime.cpp:1015-1081; for this arrangement the second norm reads the
 same tensor that the second residual sum starts from, :1066-1067).  The sums are folded into
 the norms (each norm takes (h, delta), writes h + delta back and norms it) or, for parts that say
-``adds_to_residual``, into the epilogue of the part's last matrix product (delta is then None)."""
+``adds_to_residual``, into the epilogue of the part's last matrix product (delta is then None) - or that product
+comes back as a ``SplitSum``, sums over pieces of k that the next norm adds (``settle`` adds them for a norm that
+does not say ``adds_split_sums``)."""
 from __future__ import annotations
 
 from dataclasses import replace
 
 from .base import Block
+from .linear import settle
 from .registry import build_part, register_block
 
 
@@ -38,12 +41,12 @@ class PreNormBlock(Block):
         return tuple(m for part in self.parts() for m in part.kernel_modules())
 
     def forward(self, h, delta, ctx, cache):
-        x = self.norm1.forward(h, delta, write_sum=True)
+        x = self.norm1.forward(h, settle(h, delta, self.norm1), write_sum=True)
         if self.mixer.adds_to_residual:
             delta = self.mixer.forward(x, ctx, cache, residual=h)
         else:
             delta = self.mixer.forward(x, ctx, cache)
-        x = self.norm2.forward(h, delta, write_sum=True)
+        x = self.norm2.forward(h, settle(h, delta, self.norm2), write_sum=True)
         if self.ffn.adds_to_residual:
             delta = self.ffn.forward(x, ctx, residual=h)
         else:

@@ -28,6 +28,8 @@ class RMSNorm(Norm):
     def kernel_modules(self):
         return ("elementwise",)
 
+    adds_split_sums = True      # ``delta`` may be a SplitSum: the kernel adds its planes
+
     def forward(self, x, delta=None, write_sum=False, rows=None, out_dtype=None):
         return ops.rmsnorm(x, self.weight, self.eps, out_dtype or self.runtime.dtype, delta=delta,
                            write_sum=write_sum, rows=rows)

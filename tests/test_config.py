@@ -136,3 +136,25 @@ def test_info_counts_weights_and_cache():
                               "cache_bytes_per_token": L * 2 * Hkv * hd * 4, "state_bytes_per_sequence": 0}
     half = model_info(config_from_dict(dict(cfgd)), "bfloat16")["memory"]
     assert half["weight_bytes"] == 2 * params and half["cache_bytes_per_token"] == L * 2 * Hkv * hd * 2
+
+
+def test_ring_split_counts_match_a_walk_over_the_blocks():
+    """The table that says into how many planes the ring product's split form cuts a tile is closed-form arithmetic; the
+    kernel's blocks walk their shares stage by stage.  Both must agree, also on which plane a block's piece is."""
+    from questwend_b200.kernels import ops
+    for N, K, blocks in [(4096, 4096, 148), (4096, 12288, 148), (5120, 25600, 148), (2400, 2048, 148), (200, 1000, 7),
+                         (37, 4096, 5), (64, 520, 11), (1000, 96, 13), (16, 256, 1), (48, 768, 9)]:
+        n_tiles, n_stages = -(-N // 16), -(-K // 256)
+        all_stages = n_tiles * n_stages
+        holders = [[] for _ in range(n_tiles)]           # per tile: the blocks that hold a piece, in order
+        for b in range(blocks):
+            begin, end = all_stages * b // blocks, all_stages * (b + 1) // blocks
+            for stage in range(begin, end):
+                t = stage // n_stages
+                if not holders[t] or holders[t][-1] != b:
+                    holders[t].append(b)
+        counts = ops.ring_split_counts(N, K, blocks)
+        assert counts == [len(h) for h in holders], (N, K, blocks)
+        for t, hs in enumerate(holders):                 # the kernel's plane of a later piece: block - the tile's first block
+            first = ((t * n_stages + 1) * blocks - 1) // all_stages
+            assert hs == list(range(first, first + len(hs))), (N, K, blocks, t)

@@ -242,3 +242,47 @@ def test_command_line_random_weights_and_step_profile(tmp_path):
     assert proc.returncode == 0, proc.stderr
     lines = proc.stdout.strip().splitlines()
     assert len(lines) == 2 and all(len(line.split()) == 4 for line in lines)
+
+
+@pytest.mark.parametrize("name", ["A", "B", "D"])
+def test_products_left_in_pieces_for_the_next_norm(folders, name, monkeypatch):
+    """The ring product's split form leaves the o and down products as sums over pieces of k, which the norm that follows
+    adds onto the residual stream.  It is chosen for matrices with more tiles than SMs; here it is forced onto the tiny
+    models' matrices (up to 7 blocks; model D's tiles are cut in two), and the engine must give the plain implementation's logits:
+    whole prompts, single tokens, a batch, and generation from graphs."""
+    from questwend_b200.kernels import ops
+
+    used = []
+
+    def forced(N, K, n_sm, device):
+        blocks = min(7, -(-N // 16) * -(-K // 256))
+        counts = ops.ring_split_counts(N, K, blocks)
+        if max(counts) > ops.RING_SPLIT_MAX_PLANES:
+            return None
+        used.append((N, K, max(counts)))
+        return blocks, max(counts), torch.tensor(counts, dtype=torch.uint8, device=device)
+
+    monkeypatch.setattr(ops, "_ring_split_plan", forced)
+    monkeypatch.setattr(ops, "_RING_PLANS", {})
+    folder = folders[name, "bfloat16"]
+    cfg, w = pm.read_model_folder(folder)
+    eng = qw.Engine.from_folder(folder, dtype="bfloat16", max_tokens=1024)
+    rng = np.random.default_rng(11)
+    toks = rng.integers(0, cfg["vocab_size"], 90).tolist()
+    ref = pm.forward_logits(cfg, w, toks, round16="bf16")
+    a, b = eng.open_sequences(2)
+    rows = list(eng.step([StepEntry(a, toks[:7], list(range(7))), StepEntry(b, toks[:3], [])])[:7].cpu().numpy())
+    both = eng.step([StepEntry(a, [toks[7]], [0]), StepEntry(b, [toks[3]], [0])]).cpu().numpy()
+    rows.append(both[0])
+    assert rel_err(both[1], ref[3]) < BF16_TOL
+    eng.close_sequences([b])
+    for t in toks[8:]:
+        rows.append(eng.step([StepEntry(a, [t], [0])]).cpu().numpy()[0])
+    eng.close_sequences([a])
+    assert used, "no matrix of this model took the split form"
+    assert name != "D" or max(u[2] for u in used) >= 2
+    err = np.abs(np.stack(rows) - ref).max(axis=1) / np.abs(ref).max()
+    assert err.max() < BF16_TOL, f"first position off: {int(np.argmax(err > BF16_TOL))}"
+    prompts = [[3, 14, 15, 92, 65], [35, 89, 79], [32, 38, 46, 26, 43, 38, 32, 79, 50]]
+    want = [pm.greedy_continue(cfg, w, p, 12, round16="bf16") for p in prompts]
+    assert [r.tokens for r in qw.generate(eng, prompts, max_new_tokens=12, ignore_eos=True)] == want

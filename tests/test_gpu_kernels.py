@@ -459,6 +459,60 @@ def test_gemm_ring(M, N, K):
         ops.gemm_ring(torch.zeros(17, K, dtype=torch.bfloat16, device=DEV), w)
 
 
+@pytest.mark.parametrize("M", [1, 8, 13])
+@pytest.mark.parametrize("N,K,blocks", [(4096, 4096, 148), (4096, 12288, 148), (2400, 2048, 148), (5008, 3848, 148),
+                                        (5120, 8200, 148), (200, 1000, 7), (37, 4096, 5), (64, 520, 11), (1000, 96, 13)])
+def test_gemm_ring_split(M, N, K, blocks):
+    """The ring product's split form: every block an equal share of all stages, tiles cut between blocks, their pieces
+    left as planes.  The planes add up to the product (by ``SplitSum.total``, and inside the norm), a tile has as many
+    planes as the host's table says and the others are never written, and the same call gives the same bits.  With rows
+    of 8 or 16 stages (x kept in registers) and others, shares that begin in the middle of a tile, more blocks than
+    tiles (a tile in up to 4 pieces) and fewer."""
+    g = torch.Generator().manual_seed(M * 1000 + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(N, K, generator=g).to(torch.bfloat16).to(DEV)
+    ref = f64(x) @ f64(w).T
+    counts = ops.ring_split_counts(N, K, blocks)
+    assert max(counts) <= ops.RING_SPLIT_MAX_PLANES
+    plan = (blocks, max(counts), torch.tensor(counts, dtype=torch.uint8, device=DEV))
+    split = ops.gemm_ring_split(x, w, plan)
+    ops.gemm_tc_check(DEV)
+    close(split.total(), ref, torch.float32, scale=np.abs(ref).max() * 4)
+    assert torch.equal(ops.gemm_ring_split(x, w, plan).total(), split.total())          # the same bits at every call
+    # planes beyond a tile's count stay as they were: fill them with a mark and look
+    marked = ops.SplitSum(torch.full_like(split.planes, 777.0), split.plane_count)
+    ops._call("gemm_ring", "qwb_gemm_ring_split", ops._ptr(x), ops._ptr(w), ops._ptr(marked.planes), ops._i(M), ops._i(N),
+              ops._i(K), ops._i(blocks), ops._ptr(ops.gemm_tc_error_word(DEV)), ops._stream())
+    per_column = torch.tensor(counts, device=DEV).repeat_interleave(16)[:N]
+    for p in range(marked.planes.shape[0]):
+        untouched = (marked.planes[p] == 777.0).all(dim=0)
+        assert torch.equal(untouched, per_column <= p), f"plane {p}"
+    # inside the norm: h + planes, written back and normed
+    h = torch.randn(M, N, generator=g).to(DEV)
+    wn = (torch.rand(N, generator=g) + 0.5).to(DEV)
+    want_sum = f64(h) + ref
+    h2 = h.clone()
+    out = ops.rmsnorm(h2, wn, 1e-6, torch.float32, delta=split, write_sum=True)
+    close(h2, want_sum, torch.float32, scale=np.abs(want_sum).max() * 4)
+    close(out, pm.rms_norm(f64(h2), f64(wn), 1e-6), torch.float32)
+    rows = torch.tensor([M - 1, 0], dtype=torch.int32, device=DEV)
+    some = ops.rmsnorm(h.clone(), wn, 1e-6, torch.bfloat16, delta=split, rows=rows)
+    close(some, pm.rms_norm(f64(h2), f64(wn), 1e-6)[[M - 1, 0]], torch.bfloat16)
+    h3 = h.clone()
+    split.add_onto(h3)
+    assert torch.equal(h3, h2)                                            # the same sums in the same order
+
+
+def test_ring_split_plan_on_this_device():
+    """Which matrices the split form is chosen for: those whose whole tiles leave the SMs' last round mostly empty."""
+    n_sm = torch.cuda.get_device_properties(DEV).multi_processor_count
+    assert ops.ring_split_plan(16 * n_sm, 4096, DEV) is None             # one full round
+    assert ops.ring_split_plan(16 * n_sm * 20, 4096, DEV) is None        # twenty
+    plan = ops.ring_split_plan(16 * (n_sm + n_sm // 2), 4096, DEV)      # a round and a half
+    assert plan is not None and plan[0] == n_sm and plan[1] == 2 and plan[2].numel() == n_sm + n_sm // 2
+    assert ops.ring_split_plan(16 * (n_sm + 1), 256 * 600, DEV) is None or ops.ring_split_plan(16 * (n_sm + 1), 256 * 600, DEV)[1] <= 4
+
+
 @pytest.mark.parametrize("config", ops.STREAM_CONFIGS)
 @pytest.mark.parametrize("M", [2, 8, 13])
 def test_gemm_stream_in_every_form(M, config):

@@ -8,8 +8,10 @@ sequences with 1,024-token random prompts in a 4,096-token context, W untimed th
 CUDA graphs and timed with CUDA events.  One JSON line is printed:
 
   value      decoded tokens a second, timed on the device (tokens stay on the device)
-  e2e        the same through ``generate`` (host token lists in, host token lists out;
-             every step copies its input ids from pinned host memory and reads the sampled ids back)
+  e2e        the same through ``generate`` (host token lists in, host token lists out; every step copies its input
+             ids from pinned host memory and reads the sampled ids back): one call that runs the prompts, W untimed
+             decode steps and the K timed ones, by the loop's own clock around each step (``value_all_steps``: over
+             all W + K; the first dozen steps after a prompt step run at the clocks the prompt left)
   prefill    one prompt of 2,048 tokens: tokens a second, and flops / time / peak
   roofline   decode: (every weight once + the live sequences' cache) / step time, against the HBM peak
   points     decode tokens a second at batch 1 and 64 with their roofline fractions, prefill of 4,096 and 8,192 tokens,
@@ -439,9 +441,14 @@ def main() -> int:
         prompts = [rng.integers(0, engine.vocab_size, PROMPT_LEN).tolist() for _ in range(args.batch)]
         stats = qw.GenerationStats()
         qw.generate(engine, prompts, max_new_tokens=warmup + 1, ignore_eos=True)          # warm the graphs
-        qw.generate(engine, prompts, max_new_tokens=steps + 1, ignore_eos=True, stats=stats)
-        e2e = {"value": args.batch * stats.steps / stats.decode_seconds, "unit": "tokens/s",
-               "h2d_bytes_per_step": 4 * args.batch, "d2h_bytes_per_step": 4 * args.batch}
+        # one call: the prompts, `warmup` untimed decode steps, then the `steps` timed ones (the loop's own clock around
+        # each step: tokens from pinned host memory in, the step, its ids back on the host)
+        qw.generate(engine, prompts, max_new_tokens=warmup + steps + 1, ignore_eos=True, stats=stats)
+        timed = stats.step_seconds[-steps:]
+        e2e = {"value": args.batch * len(timed) / sum(timed), "unit": "tokens/s",
+               "h2d_bytes_per_step": 4 * args.batch, "d2h_bytes_per_step": 4 * args.batch,
+               "steps": len(timed), "warmup_steps": len(stats.step_seconds) - len(timed),
+               "value_all_steps": args.batch * stats.steps / stats.decode_seconds}
         for n in (4096,):
             ms = time_prefill(engine, torch, rng, n, reps=3)
             points[f"prefill_{n}"] = n / (ms / 1e3)

@@ -43,6 +43,7 @@ class GenerationStats:
     decode_seconds: float = 0.0
     batches: int = 0
     steps: int = 0
+    step_seconds: list = field(default_factory=list)    # every decode step's wall time, in order (its sum: decode_seconds)
 
     def line(self) -> str:
         """The reference's speed line (cli/main.cpp:427-432)."""
@@ -253,7 +254,9 @@ def generate(engine, prompts, max_new_tokens: int = 128, sampling: SamplingParam
                     break
                 t0 = clock()
                 ids = stepper.run(active, [results[i].tokens[-1] for i in active], step)
-                stats.decode_seconds += clock() - t0
+                took = clock() - t0
+                stats.decode_seconds += took
+                stats.step_seconds.append(took)
                 for i in active:
                     length[i] += 1
                 step += 1

@@ -668,7 +668,7 @@ static int launch_decode(const FusedQKV& fused, const void* q, const void* k_poo
         max_runs, Gc, chunks);
     if (int rc = qwb_check_launch("attn_mma_decode")) return rc;
     if (max_runs > 1) {
-        qwb_launch_link(B, attn_mma_combine_kernel, dim3(Hq, B), AM_COMBINE_THREADS, (size_t)max_runs * sizeof(float), stream, part_acc, part_m,
+        qwb_launch_link(B, QWB_LINK_ROWS_MERGE, attn_mma_combine_kernel, dim3(Hq, B), AM_COMBINE_THREADS, (size_t)max_runs * sizeof(float), stream, part_acc, part_m,
                    part_l, seq_len, (bf16*)out, Hq, HD, window, runs_target, run_pages_max, max_runs);
         return qwb_check_launch("attn_mma_combine");
     }

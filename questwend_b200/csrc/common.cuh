@@ -106,18 +106,27 @@ static cudaError_t qwb_launch_early(void (*kernel)(KArgs...), dim3 grid, dim3 bl
 
 // For the small kernels between two early-launched ones (a norm, the merge of attention's runs): launched early as well,
 // with their trigger before their wait, they let the kernel after them start (and fill its ring) while the kernel before
-// them still runs.  Measured on decode steps: 4 % faster with one row, 2 % with 2 to 4 rows, nothing at 8 rows at the
-// Qwen3-8B sizes (attention's blocks and a ring do not fit into one SM's shared memory together), 5 % slower with 8 rows
-// at the 32B sizes: so only steps of up to QWB_LINK_MAX_ROWS rows.  QWB200_CHAIN=<rows> sets another bound, for experiments.
-#define QWB_LINK_MAX_ROWS 4
-static int qwb_link_max_rows() {
-    static int rows = -1;
-    if (rows < 0) { const char* e = getenv("QWB200_CHAIN"); rows = (e && e[0]) ? atoi(e) : QWB_LINK_MAX_ROWS; }
-    return rows;
+// them still runs.  Measured on decode steps.  The norms: 4 % faster with one row, 1-2 % with 2 to 8 rows at the Qwen3-8B
+// sizes, 0.7 % at 8 rows of the 32B sizes, nothing at 16: in steps of up to 16 rows.  The merge: nothing on its own at 8
+// rows (attention's blocks and a ring do not fit into one SM's shared memory together), and with the norms 0.5 % slower
+// there (5 % at the 32B sizes): in steps of up to 4 rows.  QWB200_CHAIN=<rows> sets another bound for both,
+// QWB200_CHAIN_<module>=<rows> for one module's kernels, for experiments.
+#define QWB_LINK_ROWS_NORM 16
+#define QWB_LINK_ROWS_MERGE 4
+static int qwb_link_max_rows(int by_default) {
+    static int rows = -2;
+    if (rows == -2) {
+        char name[96];
+        snprintf(name, sizeof(name), "QWB200_CHAIN_%s", QWB_MODULE_NAME);
+        const char* e = getenv(name);
+        if (!e || !e[0]) e = getenv("QWB200_CHAIN");
+        rows = (e && e[0]) ? atoi(e) : -1;
+    }
+    return rows >= 0 ? rows : by_default;
 }
 template <typename... KArgs, typename... Args>
-static cudaError_t qwb_launch_link(int rows, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
-    return qwb_launch_attr(qwb_pdl_mode() == 2 || (qwb_pdl_mode() == 1 && rows <= qwb_link_max_rows()), kernel, grid, block, smem, stream, args...);
+static cudaError_t qwb_launch_link(int rows, int max_rows, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    return qwb_launch_attr(qwb_pdl_mode() == 2 || (qwb_pdl_mode() == 1 && rows <= qwb_link_max_rows(max_rows)), kernel, grid, block, smem, stream, args...);
 }
 
 __device__ __forceinline__ float to_f32(float x) { return x; }

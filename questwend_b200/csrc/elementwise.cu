@@ -158,7 +158,7 @@ static int launch_rmsnorm(const float* x, const float* delta, const float* plane
     if (vec) {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_kernel<TOut, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "rmsnorm: %s", cudaGetErrorString(e));
-        qwb_launch_link(n_rows, rmsnorm_kernel<TOut, true>, n_rows, block, smem, stream, x, delta, planes, plane_count, plane_stride, sum_out, w, out, rows, D, eps);
+        qwb_launch_link(n_rows, QWB_LINK_ROWS_NORM, rmsnorm_kernel<TOut, true>, n_rows, block, smem, stream, x, delta, planes, plane_count, plane_stride, sum_out, w, out, rows, D, eps);
     } else {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_kernel<TOut, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "rmsnorm: %s", cudaGetErrorString(e));

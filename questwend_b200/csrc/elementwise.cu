@@ -81,6 +81,7 @@ template <> struct Pack4<bf16> {
 
 // VEC: rows are a multiple of 4 wide and 16-byte aligned, so everything moves four values at a time.
 #define RMS_MAX_PLANES 4
+#define RMS_W_FIRST 4             // pieces of the weight a thread asks for before the wait (rows of up to 4,096: all of it)
 #define RMS_PLANE_COLS 16
 template <typename TOut, bool VEC>
 __global__ void rmsnorm_kernel(const float* x, const float* delta, const float* planes,
@@ -88,6 +89,15 @@ __global__ void rmsnorm_kernel(const float* x, const float* delta, const float* 
                                float* sum_out, const float* __restrict__ w, TOut* __restrict__ out,
                                const int* __restrict__ rows, int D, float eps) {
     pdl_launch_dependents();            // the trigger first: the kernel after this one may start before the one before it ends
+    // the norm's weight is nobody's output: a thread's first pieces of it are on their way before the wait
+    float4 w_first[RMS_W_FIRST];
+    if (VEC) {
+#pragma unroll
+        for (int k = 0; k < RMS_W_FIRST; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            w_first[k] = i < D / 4 ? reinterpret_cast<const float4*>(w)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
     pdl_wait();
     extern __shared__ __align__(16) float row_cache[];
     __shared__ float red[32];
@@ -101,7 +111,8 @@ __global__ void rmsnorm_kernel(const float* x, const float* delta, const float* 
         float4* c4 = reinterpret_cast<float4*>(row_cache);
         for (int i = threadIdx.x; i < D / 4; i += blockDim.x) {
             // plain loads (x and delta are not __restrict__: never the read-only path, see pdl_wait); with __ldcg a norm
-            // of 8 rows of 4,096 took 1.4 us longer under the ring fill of the product that follows
+            // of 8 rows of 4,096 took 1.4 us longer under the ring fill of the product that follows (and with a thread's four
+            // loads issued together, before the first store, a step took 0.5 % longer)
             float4 v = x4[i];
             if (d4) { const float4 d = d4[i]; v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w; }
             if (planes) {
@@ -136,7 +147,15 @@ __global__ void rmsnorm_kernel(const float* x, const float* delta, const float* 
     if (VEC) {
         const float4* c4 = reinterpret_cast<const float4*>(row_cache);
         const float4* w4 = reinterpret_cast<const float4*>(w);
-        for (int i = threadIdx.x; i < D / 4; i += blockDim.x) {
+#pragma unroll
+        for (int k = 0; k < RMS_W_FIRST; ++k) {
+            const int i = threadIdx.x + k * blockDim.x;
+            if (i < D / 4) {
+                const float4 v = c4[i], g = w_first[k];
+                Pack4<TOut>::store(o + 4 * i, v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z, v.w * scale * g.w);
+            }
+        }
+        for (int i = threadIdx.x + RMS_W_FIRST * blockDim.x; i < D / 4; i += blockDim.x) {
             const float4 v = c4[i], g = w4[i];
             Pack4<TOut>::store(o + 4 * i, v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z, v.w * scale * g.w);
         }

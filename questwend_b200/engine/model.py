@@ -78,6 +78,8 @@ class Model:
 
     # ---- one step
     def forward(self, ctx: StepContext, unit_caches: list[UnitCache], want_rows: torch.Tensor) -> torch.Tensor:
+        for position in self._positions.values():       # the step's tables first: no layer's kernels find them half made
+            position.prepare(ctx)
         h = self.embedding.forward(ctx.token_ids)
         delta = None
         for i, run in enumerate(self.schedule):

@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Builds the benchmark's reference arm: kishida/questwend itself, unmodified, with its CUDA backend.
 
-    python baseline/build_reference.py [--reference /root/reference] [--build-dir DIR] [--arch 100]
+    python baseline/build_reference.py --reference DIR [--build-dir DIR] [--arch 100]
 
 The reference is a CMake C++ project (no Python package: ``pip install`` of it fails with "Neither 'setup.py' nor
 'pyproject.toml' found"), so it is built the way its README builds it, with its own switch for CUDA
@@ -21,7 +21,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("QW_REFERENCE_DIR"), required="QW_REFERENCE_DIR" not in os.environ,
+                    help="the checkout of kishida/questwend (read only; or the environment variable QW_REFERENCE_DIR)")
     ap.add_argument("--build-dir", default=os.path.join(tempfile.gettempdir(), "qw_ref_cuda_build"))
     ap.add_argument("--arch", default="100", help="CMAKE_CUDA_ARCHITECTURES (100: sm_100 machine code and compute_100 PTX)")
     ap.add_argument("--jobs", type=int, default=os.cpu_count() or 4)

@@ -482,7 +482,8 @@ RING_SPLIT_MAX_PLANES = 4       # the most planes that the consumers of a SplitS
 RING_SPLIT_BELOW = 0.8          # the split form is used when whole tiles would keep the SMs busy for less than this share of
                                 # their rounds (5,120 rows on 148 SMs: 0.72, where it takes 16.0 and 42.4 us for the o and down
                                 # projections of the Qwen3-32B sizes against 19.5 and 54.4 us; 4,096 rows: 0.86, where the
-                                # pieces' extra epilogues cost what the even shares save: 7.8 and 18.2 against 6.9 and 18.8 us)
+                                # pieces' extra epilogues cost what the even shares save: 7.8 and 18.2 against 6.9 and 18.8 us,
+                                # and a step with the down projection alone split 2,457 against 2,485 tokens/s)
 _RING_PLANS: dict = {}
 
 

@@ -191,6 +191,15 @@ gemm_ring_kernel(const bf16* x, const __grid_constant__ CUtensorMap map_w, const
         float acc[NT][4];
 #pragma unroll
         for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+        // the value that this thread's output of the tile is added onto: asked for now, used in the epilogue (asked for
+        // there, every tile ended with a round trip to L2 during which the thread's warp asked for no new stage)
+        static_assert(NT * 4 * 32 <= GR_WARPS * 32, "a thread has at most one output of a tile");
+        float onto = 0.f;
+        if (EPI == GR_EPI_PLAIN && !SPLIT && residual && threadIdx.x < NT * 4 * 32) {
+            const int j = threadIdx.x >> 7, r = (threadIdx.x >> 5) & 3;
+            const int n = n0 + (lane >> 2) + ((r & 2) ? 8 : 0), m = 8 * j + 2 * (lane & 3) + (r & 1);
+            if (n < N && m < M) onto = __ldcg(residual + (size_t)m * N + n);
+        }
         // one stage (i of the ring, ks of the tile): wait for its bytes, multiply, ask for the stage that comes into the slot next
         auto stage = [&](int i, int ks, const uint4 (&xv)[KB][NT]) {
             const int slot = i % GR_STAGES, use = i / GR_STAGES;
@@ -264,7 +273,7 @@ gemm_ring_kernel(const bf16* x, const __grid_constant__ CUtensorMap map_w, const
                 if (n < N && m < M) {
                     const size_t at = (size_t)m * N + n;
                     if (SPLIT) y[plane + at] = sum;
-                    else y[at] = residual ? residual[at] + sum : sum;
+                    else y[at] = onto + sum;
                 }
             }
         } else {                                             // rows g are gates, rows g + 8 the ups of the same features

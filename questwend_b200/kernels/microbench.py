@@ -60,6 +60,9 @@ def bench_gemm(M: int, N: int, K: int, impl: str, iters: int, dtype=torch.bfloat
         fn = lambda i: ops.gemm_ring(x, ws[i])
     elif impl == "ring_swiglu":
         fn = lambda i: ops.gemm_ring_swiglu(x, ws[i])
+    elif impl == "ring_add":                # added onto a 32-bit matrix (the residual stream) in the epilogue
+        acc = torch.zeros(M, N, device="cuda")
+        fn = lambda i: ops.gemm_ring(x, ws[i], residual=acc)
     elif impl == "ring_split":              # equal shares per block, the pieces left as planes (where whole tiles are as
         plan = ops.ring_split_plan(N, K, x.device)          # good there is no split form: the plain one is timed)
         fn = (lambda i: ops.gemm_ring_split(x, ws[i], plan)) if plan else (lambda i: ops.gemm_ring(x, ws[i]))
@@ -165,7 +168,7 @@ def main() -> int:
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=24576)
     ap.add_argument("--k", type=int, default=4096)
-    ap.add_argument("--impl", default="stream", choices=["stream", "stream_swiglu", "ring", "ring_swiglu", "ring_split", "small", "library", "tc", "tc_add", "tc_swiglu"])
+    ap.add_argument("--impl", default="stream", choices=["stream", "stream_swiglu", "ring", "ring_swiglu", "ring_add", "ring_split", "small", "library", "tc", "tc_add", "tc_swiglu"])
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=1152)

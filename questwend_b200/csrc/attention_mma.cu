@@ -576,8 +576,9 @@ attn_mma_combine_warp_kernel(const float* part_acc, const float* part_m, const f
 #pragma unroll
     for (int v = 0; v < VEC; ++v) a[v] = 0.f;
     float L = 0.f, M = -INFINITY;
-    // the maximum over all runs first (32 at a time), then the weighted sums in run order
-    for (int r0 = 0; r0 < n_runs; r0 += 32) {
+    // the maximum over all runs first (32 at a time), then the weighted sums in run order; with up to 16 runs (the
+    // usual case) the one round's own loads give the maximum, so that nothing is asked for twice or one after the other
+    for (int r0 = 0; n_runs > 16 && r0 < n_runs; r0 += 32) {
         float m = r0 + lane < n_runs ? __ldcg(part_m + row + r0 + lane) : -INFINITY;
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
@@ -600,6 +601,11 @@ attn_mma_combine_warp_kernel(const float* part_acc, const float* part_m, const f
                     acc[i][0] = t.x; acc[i][1] = t.y;
                 }
             }
+        }
+        if (n_runs <= 16) {
+            M = my_m;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
         }
         const float my_w = lane < n_here ? expf(my_m - M) : 0.f;
 #pragma unroll
@@ -671,6 +677,7 @@ static int launch_decode(const FusedQKV& fused, const void* q, const void* k_poo
         max_runs, Gc, chunks);
     if (int rc = qwb_check_launch("attn_mma_decode")) return rc;
     if (max_runs > 1) {
+        // (launched early with more sequences, even with its trigger after its wait, a step of 8 got 1 % slower)
         qwb_launch_link(B, QWB_LINK_ROWS_MERGE, attn_mma_combine_warp_kernel<HD / 32>, dim3((Hq + AM_COMBINE_THREADS / 32 - 1) / (AM_COMBINE_THREADS / 32), B),
                         AM_COMBINE_THREADS, 0, stream, part_acc, part_m, part_l, seq_len, (bf16*)out, Hq, window, runs_target, run_pages_max, max_runs);
         return qwb_check_launch("attn_mma_combine");

@@ -38,11 +38,16 @@ def require_true_fp32() -> None:
 
 STREAM_MAX_ROWS = 8         # up to here the own weight-streaming product is always the fastest.  With 9 to 16 rows (its
                             # two-tile form) it is where the rows of x cost it nothing or little: rows of up to 2,048 or 4,096
-                            # values (the ring product then keeps its pieces of x in registers: at 16 rows q/k/v 12.1 us
-                            # against the library's 12.1, o 9.2 against 9.3, gate/up with the SiLU 36.0 against 34.7 + 3 for
-                            # the separate SiLU kernel, the head 197 against 208) and matrices of up to 16 M weights (the
-STREAM_WIDE_MAX_WEIGHT = 1 << 24   # 0.6B model's); else the library is faster or as fast (x no longer fits into the L1 that the
-                            # ring leaves: at the 32B sizes a step of 16 rows loses 7 % with the ring on the long rows)
+                            # values (the ring product then keeps its pieces of x in registers: at 16 rows q/k/v 12.7 us
+                            # against the library's 12.1, o 9.6 against 9.3, gate/up with the SiLU 37.1 against 34.7 + 3 for
+                            # the separate SiLU kernel, the head 198 against 208), matrices of up to 16 M weights (the
+STREAM_WIDE_MAX_WEIGHT = 1 << 24   # 0.6B model's) and long rows (below)
+
+LONG_ROWS = 8192            # with 9 to 16 rows of at least this many values the ring product is within a few per cent of the
+                            # library again (Qwen3-8B down projection, 12,288: 21.1 against 21.3 us at 12 rows, 23.0 against
+                            # 21.3 at 16).  What is left to the library with 9 to 16 rows, all at the 32B sizes: rows between
+                            # 4,096 and 8,192 values of matrices above 16 M weights (q/k/v and gate/up, rows of 5,120: 26.5
+                            # and 107 us against 21.1 and 91) and matrices whose tiles fill the SMs' rounds badly (o and down)
 
 FEW_ROWS_KERNEL = os.environ.get("QWB200_FEW_ROWS", "ring")     # "ring" (gemm_ring, the default) or "stream" (gemm_stream, the
                                                                 # kernel before it, kept for comparison)
@@ -53,9 +58,17 @@ def _few_rows(M: int, weight: torch.Tensor) -> bool:
     from the shape alone, so the same trace gives the same bits in every process."""
     if M <= STREAM_MAX_ROWS:
         return True
-    K = weight.shape[1]
-    keeps_x = FEW_ROWS_KERNEL == "ring" and -(-K // ops.RING_STAGE_K) in ops.RING_KEEPS_X_STAGES
-    return M <= ops.STREAM_M and (keeps_x or weight.numel() <= STREAM_WIDE_MAX_WEIGHT)
+    if M > ops.STREAM_M:
+        return False
+    N, K = weight.shape
+    if FEW_ROWS_KERNEL != "ring":
+        return weight.numel() <= STREAM_WIDE_MAX_WEIGHT
+    if weight.numel() <= STREAM_WIDE_MAX_WEIGHT:
+        return True
+    if ops.ring_split_plan(N, K, weight.device) is not None:
+        return False            # whole tiles would fill the SMs' rounds badly, and with the split form a step of 16 rows at
+                                # the Qwen3-32B sizes is 3 % slower than with the library (1,132 against 1,165 tokens/s)
+    return -(-K // ops.RING_STAGE_K) in ops.RING_KEEPS_X_STAGES or K >= LONG_ROWS
 
 
 def _stream(x, weight, add_to, kind):

@@ -150,6 +150,27 @@ def bench_rmsnorm(M, K, iters) -> dict:
     return {"kernel": "rmsnorm", "M": M, "K": K, "us": us}
 
 
+def bench_rope(T, Hq, Hkv, hd, iters, store_kv=True) -> dict:
+    """q/k norm + rotation + cache write of one prompt of T tokens (``rope``)."""
+    page = ops.PAGE_SIZE
+    n_pages = math.ceil(T / page)
+    copies = max(2, min(8, math.ceil(2 * L2_BYTES / (T * (Hq + 2 * Hkv) * hd * 4))))
+    qkvs = [torch.randn(T, (Hq + 2 * Hkv) * hd, device="cuda") for _ in range(copies)]
+    k_pool = torch.zeros(n_pages * copies, Hkv, page, hd, device="cuda", dtype=torch.bfloat16)
+    v_pool = torch.zeros_like(k_pool)
+    tables = [(torch.arange(n_pages, dtype=torch.int32, device="cuda") + c * n_pages).reshape(1, n_pages) for c in range(copies)]
+    w = torch.ones(hd, device="cuda")
+    pos = torch.arange(T, dtype=torch.int32, device="cuda")
+    seq = torch.zeros(T, dtype=torch.int32, device="cuda")
+    inv_freq = torch.tensor([1e6 ** (-2.0 * i / hd) for i in range(hd // 2)], dtype=torch.float64, device="cuda")
+    cos, sin = ops.rope_table(pos, inv_freq)
+    fn = lambda i: ops.qk_norm_rope_store(qkvs[i], w, w, cos, sin, seq, pos, tables[i], k_pool, v_pool, Hq, Hkv, hd, hd, 1e-6,
+                                          store_kv=store_kv)
+    us = _time(fn, copies, iters)
+    nbytes = T * (Hq + 2 * Hkv) * hd * 4 + T * (Hq + 2 * Hkv) * hd * 2
+    return {"kernel": "qk_norm_rope_store", "T": T, "Hq": Hq, "Hkv": Hkv, "hd": hd, "us": us, "bytes": nbytes, "GBps": nbytes / us / 1e3}
+
+
 def bench_sample(B, V, temperature, top_k, top_p, iters, spread=3.0) -> dict:
     copies = max(2, math.ceil(2 * L2_BYTES / (B * V * 4)))
     copies = min(copies, 64)
@@ -164,7 +185,7 @@ def bench_sample(B, V, temperature, top_k, top_p, iters, spread=3.0) -> dict:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn_decode", "attn_prefill", "rmsnorm", "decode_shapes", "sample"])
+    ap.add_argument("what", choices=["gemm", "attn_decode", "attn_prefill", "rmsnorm", "rope", "decode_shapes", "sample"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=24576)
     ap.add_argument("--k", type=int, default=4096)
@@ -203,6 +224,8 @@ def main() -> int:
         print(json.dumps(bench_sample(args.batch, args.vocab, args.temp, args.top_k, args.top_p, args.iters)))
     elif args.what == "attn_prefill":
         print(json.dumps(bench_attn_prefill(args.tokens, args.heads, args.kv_heads, args.head_dim, args.iters, dtype)))
+    elif args.what == "rope":
+        print(json.dumps(bench_rope(args.tokens, args.heads, args.kv_heads, args.head_dim, args.iters)))
     else:
         print(json.dumps(bench_rmsnorm(args.m, args.k, args.iters)))
     return 0

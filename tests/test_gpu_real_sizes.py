@@ -129,3 +129,40 @@ def test_output_head_at_the_real_vocabulary(dtype):
         top = y.argmax(dim=1)
         ref_top = (x.double() @ W[top].double().t()).diagonal()
         assert torch.allclose(y.gather(1, top[:, None])[:, 0].double(), ref_top, rtol=1e-3, atol=1e-4)
+
+
+def test_early_launches_change_no_token(tmp_path):
+    """Kernels that are launched before their predecessor has ended (the few-rows products, decode attention, the norms
+    and the merge between them) must read what the predecessor wrote, not what lay there a step before.  Greedy
+    generation from CUDA graphs at the 8B widths, two layers, in a process of its own with those launches and in one
+    without (QWB200_PDL=0): the same kernels and sums, so every token must be the same.  Random weights make nearly flat
+    distributions: a value read too early shows as another token (with x read through the read-only path, `__ldg`, in
+    the few-rows product this test fails)."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    cfgd = dict(REAL["8b"], num_hidden_layers=2, vocab_size=4099)
+    folder = str(tmp_path / "model")
+    qw.write_model_folder(folder, config_from_dict(cfgd), seed=4, dtype="bfloat16")
+    script = (
+        "import json, sys, numpy as np\n"
+        "import questwend_b200 as qw\n"
+        "eng = qw.Engine.from_folder(sys.argv[1], dtype='bfloat16', max_tokens=4096)\n"
+        "rng = np.random.default_rng(5)\n"
+        "out = {}\n"
+        "for n in (1, 3, 8):\n"
+        "    prompts = [rng.integers(0, eng.vocab_size, int(k)).tolist() for k in rng.integers(5, 90, n)]\n"
+        "    out[n] = [r.tokens for r in qw.generate(eng, prompts, max_new_tokens=40, ignore_eos=True)]\n"
+        "print('TOKENS ' + json.dumps(out))\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    got = {}
+    for pdl in ("some", "0"):
+        env = dict(os.environ, QWB200_PDL=pdl, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+        proc = subprocess.run([sys.executable, "-c", script, folder], capture_output=True, text=True, timeout=600, env=env)
+        assert proc.returncode == 0, proc.stderr[-2000:]
+        line = [l for l in proc.stdout.splitlines() if l.startswith("TOKENS ")][-1]
+        got[pdl] = json.loads(line[len("TOKENS "):])
+    shutil.rmtree(folder, ignore_errors=True)
+    assert got["some"] == got["0"]

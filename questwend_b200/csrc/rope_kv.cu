@@ -146,16 +146,17 @@ qk_norm_rope_store_hd128_kernel(const float* __restrict__ qkv, const float* __re
     if (k_weight) wk = reinterpret_cast<const float4*>(k_weight)[lane];
     const int p = tok_pos[t];
     const size_t page = (size_t)page_table[(size_t)tok_seq[t] * table_width + p / page_size];
-    for (int h0 = warp; h0 < n_heads; h0 += RK_WARPS * RK_HEADS_AT_ONCE) {
+    const int h_step = RK_WARPS * gridDim.y;       // few tokens: gridDim.y blocks share a token's heads
+    for (int h0 = blockIdx.y * RK_WARPS + warp; h0 < n_heads; h0 += h_step * RK_HEADS_AT_ONCE) {
         float4 x[RK_HEADS_AT_ONCE];
 #pragma unroll
         for (int i = 0; i < RK_HEADS_AT_ONCE; ++i) {
-            const int head = h0 + i * RK_WARPS;
+            const int head = h0 + i * h_step;
             if (head < n_heads) x[i] = row[(size_t)head * (hd / 4) + lane];
         }
 #pragma unroll
         for (int i = 0; i < RK_HEADS_AT_ONCE; ++i) {
-            const int head = h0 + i * RK_WARPS;
+            const int head = h0 + i * h_step;
             if (head >= n_heads) break;                            // the same for the whole warp
             const bool is_q = head < Hq, is_k = !is_q && head < Hq + Hkv;
             TOut* dst;
@@ -203,12 +204,19 @@ extern "C" int qwb_qk_norm_rope_store(const float* qkv, const float* q_weight, c
                       (uintptr_t)k_pool % 16 == 0 && (uintptr_t)v_pool % 16 == 0 && (uintptr_t)cos_t % 16 == 0 &&
                       (uintptr_t)sin_t % 16 == 0 && (!q_weight || (uintptr_t)q_weight % 16 == 0) &&
                       (!k_weight || (uintptr_t)k_weight % 16 == 0);
+    // hd128 kernel: a block a token; with few tokens up to six blocks share a token's heads, so that there are blocks for the SMs
+    int share = 1;
+    if (T < 592) {
+        share = (592 + T - 1) / T;
+        const int most = (Hq + 2 * Hkv + RK_WARPS - 1) / RK_WARPS;
+        if (share > most) share = most;
+    }
     if (fast && dtype == QWB_DT_F32)
-        qwb_launch(qk_norm_rope_store_hd128_kernel<float>, dim3(T), RK_WARPS * 32, 0, stream, qkv, q_weight, k_weight, cos_t, sin_t,
+        qwb_launch(qk_norm_rope_store_hd128_kernel<float>, dim3(T, share), RK_WARPS * 32, 0, stream, qkv, q_weight, k_weight, cos_t, sin_t,
                    tok_seq, tok_pos, page_table, (float*)q_out, (float*)k_pool, (float*)v_pool, Hq, Hkv, eps, page_size,
                    table_width, store_kv);
     else if (fast && dtype == QWB_DT_BF16)
-        qwb_launch(qk_norm_rope_store_hd128_kernel<bf16>, dim3(T), RK_WARPS * 32, 0, stream, qkv, q_weight, k_weight, cos_t, sin_t,
+        qwb_launch(qk_norm_rope_store_hd128_kernel<bf16>, dim3(T, share), RK_WARPS * 32, 0, stream, qkv, q_weight, k_weight, cos_t, sin_t,
                    tok_seq, tok_pos, page_table, (bf16*)q_out, (bf16*)k_pool, (bf16*)v_pool, Hq, Hkv, eps, page_size,
                    table_width, store_kv);
     else if (dtype == QWB_DT_F32)

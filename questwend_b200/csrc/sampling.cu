@@ -873,6 +873,78 @@ sample_kernel(float* logits, int V, const int* __restrict__ recent, int window, 
     }
 }
 
+// Greedy with few rows: the row cut into chunks as above, grid (chunks, B): penalties and the maximum of the chunk (lowest
+// id among equals); then one warp per row picks among the chunks.  8 rows of 151,936 logits: 6 us against 10-13 with one
+// block per row, which reads its 600 KB alone.
+__global__ void __launch_bounds__(SPLIT_THREADS)
+sample_argmax_chunk_kernel(float* logits, int V, int chunk, const int* __restrict__ recent, int window, float repeat_penalty,
+                           float presence_penalty, float frequency_penalty, float* __restrict__ part_best,
+                           int* __restrict__ part_best_i) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float red_v[SPLIT_WARPS];
+    __shared__ int red_i[SPLIT_WARPS];
+    const int c = blockIdx.x, b = blockIdx.y, n_chunks = gridDim.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float* row = logits + (size_t)b * V;
+    const int i0 = min(V, c * chunk), i1 = min(V, i0 + chunk);
+    if (recent && window > 0 && (repeat_penalty != 1.f || presence_penalty != 0.f || frequency_penalty != 0.f)) {
+        apply_penalties(row, i0, i1, recent + (size_t)b * window, window, repeat_penalty, presence_penalty, frequency_penalty);
+        __syncthreads();
+    }
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    for_each_logit(row + i0, i1 - i0, [&](int i, float l, bool valid) {
+        if (valid && (l > best || (l == best && i0 + i < best_i))) { best = l; best_i = i0 + i; }
+    });
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    if (lane == 0) { red_v[warp] = best; red_i[warp] = best_i; }
+    __syncthreads();
+    if (tid == 0) {
+        for (int w = 1; w < SPLIT_WARPS; ++w)
+            if (red_v[w] > best || (red_v[w] == best && red_i[w] < best_i)) { best = red_v[w]; best_i = red_i[w]; }
+        part_best[(size_t)b * n_chunks + c] = best;
+        part_best_i[(size_t)b * n_chunks + c] = best_i;
+    }
+}
+
+__global__ void __launch_bounds__(32)
+sample_argmax_pick_kernel(const float* __restrict__ part_best, const int* __restrict__ part_best_i, int n_chunks,
+                          int* __restrict__ out_ids) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int b = blockIdx.x, lane = threadIdx.x;
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    for (int c = lane; c < n_chunks; c += 32) {
+        const float v = part_best[(size_t)b * n_chunks + c];
+        const int i = part_best_i[(size_t)b * n_chunks + c];
+        if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    if (lane == 0) out_ids[b] = best_i == 0x7fffffff ? 0 : best_i;     // a row of NaN or -inf: the reference's loop keeps 0
+}
+
+// Chunks a row for greedy sampling (0: one block does the whole row).
+static int greedy_chunks(int B, int V) {
+    int dev = 0, n_sm = 148;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
+    int chunks = 4 * n_sm / B;
+    if (chunks > 32) chunks = 32;
+    if (chunks > V / 2048) chunks = V / 2048;
+    return chunks < 16 ? 0 : chunks;          // as for the other split kernels: with more than 37 rows a block per row is as fast
+}
+
 // How the row is cut for the split kernels: 0 chunks = one block does the whole row.
 static int split_chunks(int B, int V, float temperature, int top_k, float top_p) {
     const bool small_k = top_k > 0 && top_k < V && top_k <= SAMPLE_THREADS;
@@ -897,6 +969,7 @@ static int split_chunks(int B, int V, float temperature, int top_k, float top_p)
 
 // Bytes of scratch that qwb_sample wants for these arguments (0: none); 16-byte aligned memory, any contents.
 extern "C" int qwb_sample_scratch_bytes(int B, int V, float temperature, int top_k, float top_p) {
+    if (!(temperature > 0.f)) return greedy_chunks(B, V) ? B * 32 * 8 : 0;
     const int chunks = split_chunks(B, V, temperature, top_k, top_p);     // at most 32 chunks of at most 296 rows: 20 MB
     if (!chunks) return 0;
     return B * chunks * (2 + 2) * 4 + B * (2 + 4) * 4 + B * SAMPLE_CAND_MAX * 8;
@@ -919,6 +992,17 @@ extern "C" int qwb_sample(float* logits, int B, int V, const int* recent, int wi
         cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "sample: %s", cudaGetErrorString(e));
         sized = true;
+    }
+    if (!(temperature > 0.f) && scratch && greedy_chunks(B, V)) {
+        if ((uintptr_t)scratch % 16) return qwb_fail(QWB_ERR_ARG, "sample: the scratch memory must be 16-byte aligned");
+        const int chunks = greedy_chunks(B, V);
+        float* part_best = reinterpret_cast<float*>(scratch);
+        int* part_best_i = reinterpret_cast<int*>(part_best + (size_t)B * chunks);
+        const int chunk = ((V + chunks - 1) / chunks + 3) / 4 * 4;
+        qwb_launch(sample_argmax_chunk_kernel, dim3(chunks, B), SPLIT_THREADS, 0, stream, logits, V, chunk, recent, window,
+                   repeat_penalty, presence_penalty, frequency_penalty, part_best, part_best_i);
+        qwb_launch(sample_argmax_pick_kernel, B, 32, 0, stream, (const float*)part_best, (const int*)part_best_i, chunks, out_ids);
+        return qwb_check_launch("sample");
     }
     Gathered pre = {};
     const int chunks = scratch && counters ? split_chunks(B, V, temperature, top_k, top_p) : 0;

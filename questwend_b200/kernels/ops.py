@@ -649,11 +649,13 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int = 0, top_p: floa
     scratch = counters = None
     if scratch_bytes:
         scratch = torch.empty((scratch_bytes,), dtype=torch.uint8, device=logits.device)
-        counters = _sample_counters(logits.device, B)
+        if temperature > 0:
+            counters = _sample_counters(logits.device, B)
     _call("sampling", "qwb_sample", _ptr(logits), _i(B), _i(V), _ptr(recent), _i(window), _f(repeat_penalty),
           _f(presence_penalty), _f(frequency_penalty), _f(temperature), _i(top_k), _f(top_p),
           ctypes.c_ulonglong(seed & (2 ** 64 - 1)), _ptr(seed_from), _ptr(sequence_index), ctypes.c_uint(step & 0xFFFFFFFF),
-          _ptr(step_add), _ptr(out), _ptr(out_u), _ptr(scratch), _ptr(counters), _stream(), kernels=3 if scratch_bytes else 1)
+          _ptr(step_add), _ptr(out), _ptr(out_u), _ptr(scratch), _ptr(counters), _stream(),
+          kernels=(3 if temperature > 0 else 2) if scratch_bytes else 1)
     return out
 
 

@@ -233,20 +233,38 @@ gemm_ring_kernel(const bf16* x, const __grid_constant__ CUtensorMap map_w, const
                 if (!SPLIT || (ks >= ks_lo && ks < ks_lo + n_here)) stage(i_lo + ks - ks_lo, ks, xkeep[q]);
             }
         } else {
-            for (int i = i_lo + (warp - i_lo % GR_WARPS + GR_WARPS) % GR_WARPS; i < i_lo + n_here; i += GR_WARPS) {
-                // a thread's 16 bytes are eight consecutive k of one row; W and x use the same renumbering of k inside a
-                // block of 32, so no shuffle is needed (the sum over k does not care about the order).  The rows of x are
-                // asked for before the wait for W: they do not depend on it.
-                const int ks = ks_lo + i - i_lo;
-                uint4 xv[KB][NT];
+            // a thread's 16 bytes are eight consecutive k of one row; W and x use the same renumbering of k inside a
+            // block of 32, so no shuffle is needed (the sum over k does not care about the order).  The rows of x for a
+            // stage are asked for one stage of the warp ahead (with one tile of rows; with two the registers do not
+            // reach), by plain loads: through L1, which holds rows of up to about 5,000 values beside the ring.
+            auto load_x = [&](int ks, uint4 (&xv)[KB][NT]) {
 #pragma unroll
                 for (int kb = 0; kb < KB; ++kb)
 #pragma unroll
                     for (int j = 0; j < NT; ++j) {
                         const int c = ks * (GR_KC / 8) + kb * 4 + t;
-                        xv[kb][j] = (c < chunks && x_ok[j]) ? __ldcg(xr[j] + c) : zero;
+                        xv[kb][j] = (c < chunks && x_ok[j]) ? xr[j][c] : zero;
                     }
-                stage(i, ks, xv);
+            };
+            const int i_first = i_lo + (warp - i_lo % GR_WARPS + GR_WARPS) % GR_WARPS;
+            if (NT == 1) {
+                uint4 xv[KB][NT], xn[KB][NT];
+                if (i_first < i_lo + n_here) load_x(ks_lo + i_first - i_lo, xv);
+                for (int i = i_first; i < i_lo + n_here; i += GR_WARPS) {
+                    const bool more = i + GR_WARPS < i_lo + n_here;
+                    if (more) load_x(ks_lo + i + GR_WARPS - i_lo, xn);
+                    stage(i, ks_lo + i - i_lo, xv);
+                    if (more) {
+#pragma unroll
+                        for (int kb = 0; kb < KB; ++kb) xv[kb][0] = xn[kb][0];
+                    }
+                }
+            } else {
+                for (int i = i_first; i < i_lo + n_here; i += GR_WARPS) {
+                    uint4 xv[KB][NT];
+                    load_x(ks_lo + i - i_lo, xv);
+                    stage(i, ks_lo + i - i_lo, xv);
+                }
             }
         }
         i_lo += n_here;

@@ -242,6 +242,25 @@ def test_attn_decode_tensor_cores(Hq, Hkv, hd, window, runs_target, run_pages_ma
                       dict(runs_target=runs_target, run_pages_max=run_pages_max))
 
 
+@pytest.mark.parametrize("Hq,Hkv,hd", [(8, 2, 128), (4, 4, 64)])
+def test_attn_decode_merges_many_runs(Hq, Hkv, hd):
+    """The merge of the runs' partial results with 18 runs (more than the 16 whose loads make one round) and 35 (more than
+    a warp has lanes), beside a sequence of one run: runs of one page, sequences of 1,100, 2,200 and 40 keys."""
+    lens = [1100, 2200, 40]
+    q, k, v = (rounded(a, torch.bfloat16) for a in make_qkv(lens, Hq, Hkv, hd, 7))
+    k_pool, table = paged(k, Hkv, hd, torch.bfloat16, seed=3)
+    v_pool, _ = paged(v, Hkv, hd, torch.bfloat16, seed=3)
+    q_last = torch.stack([torch.as_tensor(qq[-1]) for qq in q]).to(torch.bfloat16).to(DEV)
+    seq_len = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    out = ops.attn_decode(q_last, k_pool, v_pool, table, seq_len, 1 / math.sqrt(hd), max(lens), impl="mma", runs_target=1,
+                          run_pages_max=1)
+    ref = np.stack([pm.attention_causal(qq, kk, vv)[-1].reshape(Hq * hd) for qq, kk, vv in zip(q, k, v)])
+    close(out, ref, torch.bfloat16)
+    alone = ops.attn_decode(q_last[1:2], k_pool, v_pool, table[1:2], seq_len[1:2], 1 / math.sqrt(hd), 4096, impl="mma",
+                            runs_target=1, run_pages_max=1)
+    assert torch.equal(alone[0], out[1])
+
+
 def test_attn_decode_runs_by_length():
     """How the tensor-core kernel cuts a sequence of p pages: clamp(ceil(p / target), 1, most) pages a run."""
     def runs(pages, target, most):

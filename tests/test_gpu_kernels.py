@@ -726,6 +726,32 @@ def test_few_rows_cut_into_chunks_sample_the_same(B, V, case, k, p):
     assert int(ops._sample_counters(DEV, B).abs().sum()) == 0
 
 
+@pytest.mark.parametrize("B,V", [(1, 151936), (8, 36000), (30, 70001), (64, 40003)])
+def test_greedy_over_chunks_of_a_row(B, V):
+    """Greedy sampling with few rows cuts every row into chunks (two kernels); with 64 rows a block takes a whole row.
+    The same ids as the one-block way and as the plain argmax of the penalized logits, the lowest id among equals - also
+    when the equals lie in different chunks - and the same logits after the penalties."""
+    rng = np.random.default_rng(B)
+    rows = (rng.normal(size=(B, V)) * 2.0).astype(np.float32)
+    for r in range(B):
+        top = rows[r].max() + 1.0
+        rows[r, rng.choice(V, size=3, replace=False)] = top              # three equal maxima, anywhere in the row
+    rows[0, 5] = rows[0].max() + 2.0                                        # the mode of row 0 is penalized below it
+    recent = rng.integers(0, V, size=(B, 9)).astype(np.int32)
+    recent[0, 0] = 5
+    pen = dict(repeat_penalty=1.3, presence_penalty=2.5, frequency_penalty=0.2)
+    rec = torch.from_numpy(recent).to(DEV)
+    a, b = torch.from_numpy(rows).to(DEV), torch.from_numpy(rows).to(DEV)
+    ids = ops.sample(a, 0.0, recent=rec, **pen)
+    one = ops.sample(b, 0.0, recent=rec, split=False, **pen)
+    assert torch.equal(ids, one) and torch.equal(a, b)
+    for r in range(B):
+        want = pm.penalized_logits(rows[r], list(recent[r]), repeat_penalty=1.3, presence=2.5, frequency=0.2)
+        assert np.abs(f64(a[r]) - want).max() < 1e-5
+        assert int(ids[r]) == int(np.argmax(f64(a[r])))                     # numpy's argmax: the first of the equals
+    assert int(ids[0]) != 5
+
+
 def test_penalties():
     V = 200
     rng = np.random.default_rng(5)

@@ -167,7 +167,9 @@ gemm_ring_kernel(const bf16* x, const __grid_constant__ CUtensorMap map_w, const
     // SPW > 0: a tile has exactly SPW * GR_WARPS stages, so a warp meets the same k in every tile (stages kfix, kfix + 8, ...
     // of a tile, kfix = warp unless the block's share begins in the middle of a tile) and keeps its pieces of x in
     // registers for the whole product instead of asking L1 for them at every stage.
-    const int kfix = (begin + warp) % GR_WARPS;
+    // (With 1, 2 or 4 stages a tile the same holds with one stage a warp, kfix = warp modulo the stages, and a warp has a
+    // stage only in every 8th, 4th or 2nd tile.)
+    const int kfix = (begin + warp) % min(n_stages, GR_WARPS);
     uint4 xkeep[SPW > 0 ? SPW : 1][KB][NT];
     if (SPW > 0) {
 #pragma unroll
@@ -230,7 +232,8 @@ gemm_ring_kernel(const bf16* x, const __grid_constant__ CUtensorMap map_w, const
 #pragma unroll
             for (int q = 0; q < (SPW > 0 ? SPW : 1); ++q) {
                 const int ks = kfix + q * GR_WARPS;          // stage ks of the tile is stage i_lo + ks - ks_lo of the ring
-                if (!SPLIT || (ks >= ks_lo && ks < ks_lo + n_here)) stage(i_lo + ks - ks_lo, ks, xkeep[q]);
+                const int i = i_lo + ks - ks_lo;
+                if ((!SPLIT || (ks >= ks_lo && ks < ks_lo + n_here)) && (i % GR_WARPS == warp)) stage(i, ks, xkeep[q]);
             }
         } else {
             // a thread's 16 bytes are eight consecutive k of one row; W and x use the same renumbering of k inside a
@@ -375,9 +378,10 @@ static int launch_ring_as(const bf16* x, const bf16* W, const float* residual, f
 template <int NT, int EPI>
 static int launch_ring(const bf16* x, const bf16* W, const float* residual, float* y, bf16* act, int M, int N, int K,
                        int* error, cudaStream_t stream, int split_blocks = 0) {
-    // rows of up to 2,048 or 4,096 values: a warp meets the same one or two stages of k in every tile and keeps its x
+    // rows of 8 or 16 stages (up to 2,048 or 4,096 values), or of 1, 2 or 4: a warp meets the same one or two stages of k
+    // in every tile that it has a stage of, and keeps its x
     const int n_stages = (K + 255) / 256;
-    if (n_stages == 8) return launch_ring_as<NT, EPI, 256, 16, 8, 1>(x, W, residual, y, act, M, N, K, error, stream, split_blocks);
+    if (n_stages == 8 || n_stages == 4 || n_stages == 2 || n_stages == 1) return launch_ring_as<NT, EPI, 256, 16, 8, 1>(x, W, residual, y, act, M, N, K, error, stream, split_blocks);
     if (n_stages == 16) return launch_ring_as<NT, EPI, 256, 16, 8, 2>(x, W, residual, y, act, M, N, K, error, stream, split_blocks);
     return launch_ring_as<NT, EPI, 256, 16, 8, 0>(x, W, residual, y, act, M, N, K, error, stream, split_blocks);
 }

@@ -431,7 +431,7 @@ def gemm_stream_swiglu(x: torch.Tensor, weight: torch.Tensor, config: tuple | No
 
 
 RING_STAGE_K = 256              # k per stage of gemm_ring's ring; with 8 or 16 stages a row of W (rows of up to 2,048 or 4,096
-RING_KEEPS_X_STAGES = (8, 16)   # values) a warp meets the same k in every tile and keeps its pieces of x in registers
+RING_KEEPS_X_STAGES = (1, 2, 4, 8, 16)   # values) a warp meets the same k in every tile and keeps its pieces of x in registers
 
 
 def gemm_ring(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor | None = None,

@@ -1,9 +1,11 @@
 """Matrix products y = x W^T with 32-bit sums and a 32-bit result.
 
 Few rows (a decode step) go to the hand-written weight-streaming kernels: bfloat16
-with up to 8 rows (up to 16 for matrices of at most 16 M weights) to the tensor-core
-one (mma.sync), which also folds the residual sum or the gated SiLU into its
-epilogue; float32 (and odd inner sizes) with few rows to the plain one.  More rows go to the library product, as in the reference,
+with up to 8 rows (up to 16 where ``_few_rows`` says so: at the Qwen3-8B and 0.6B sizes every
+product) to the tensor-core one (``gemm_ring``: W streamed by TMA through a ring in shared
+memory, mma.sync), which also folds the residual sum or the gated SiLU into its epilogue, or
+leaves a product that is added onto the residual stream as partial sums for the norm that
+follows (``linear_onto``); float32 (and odd inner sizes) with few rows to the plain one.  More rows go to the library product, as in the reference,
 whose dispatcher sends up to 16 rows to its own kernels and the rest to cuBLAS
 (ggml-cuda/ggml-cuda.cu:1812-1866); the residual sum rides in the library call
 (beta = 1).  The exception is the gate/up projection of many bfloat16 rows: the

@@ -255,6 +255,27 @@ __global__ void silu_mul_kernel(const float* __restrict__ gu, TOut* __restrict__
     }
 }
 
+// The same for gates and ups interleaved in eights (the layout that the products with a fused epilogue want): a thread
+// takes 8 features: 64 bytes of gates and ups in four 16-byte loads, one store of 8 values.  64 rows of 12,288 features:
+// 3.2 us against 5.5 with a value a thread.
+template <typename TOut>
+__global__ void silu_mul_eights_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int T, int F) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int groups = F >> 3;
+    const size_t n = (size_t)T * groups;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / groups, grp = i - t * groups;
+        const float4* src = reinterpret_cast<const float4*>(gu + (t * 2 * F + grp * 16));
+        const float4 g0 = src[0], g1 = src[1], u0 = src[2], u1 = src[3];
+        TOut* dst = out + t * F + grp * 8;
+        Pack4<TOut>::store(dst, g0.x / (1.f + expf(-g0.x)) * u0.x, g0.y / (1.f + expf(-g0.y)) * u0.y,
+                           g0.z / (1.f + expf(-g0.z)) * u0.z, g0.w / (1.f + expf(-g0.w)) * u0.w);
+        Pack4<TOut>::store(dst + 4, g1.x / (1.f + expf(-g1.x)) * u1.x, g1.y / (1.f + expf(-g1.y)) * u1.y,
+                           g1.z / (1.f + expf(-g1.z)) * u1.z, g1.w / (1.f + expf(-g1.w)) * u1.w);
+    }
+}
+
 extern "C" int qwb_silu_mul(const float* gate_up, void* out, int out_dtype, int T, int F, int interleave, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (F <= 0) return qwb_fail(QWB_ERR_ARG, "silu_mul: bad width %d", F);
@@ -262,6 +283,14 @@ extern "C" int qwb_silu_mul(const float* gate_up, void* out, int out_dtype, int 
         return qwb_fail(QWB_ERR_ARG, "silu_mul: %d features cannot be interleaved in groups of %d", F, interleave);
     const size_t n = (size_t)T * F;
     const int block = 256;
+    if (interleave == 8 && F % 8 == 0 && (uintptr_t)gate_up % 16 == 0 && (uintptr_t)out % 16 == 0 &&
+        (out_dtype == QWB_DT_F32 || out_dtype == QWB_DT_BF16)) {
+        const size_t groups = n / 8;
+        const int g8 = (int)((groups + block - 1) / block < 148 * 16 ? (groups + block - 1) / block : 148 * 16);
+        if (out_dtype == QWB_DT_F32) qwb_launch(silu_mul_eights_kernel<float>, g8, block, 0, stream, gate_up, (float*)out, T, F);
+        else qwb_launch(silu_mul_eights_kernel<bf16>, g8, block, 0, stream, gate_up, (bf16*)out, T, F);
+        return qwb_check_launch("silu_mul");
+    }
     const int grid = (int)((n + block - 1) / block < 148 * 16 ? (n + block - 1) / block : 148 * 16);
     if (out_dtype == QWB_DT_F32)
         qwb_launch(silu_mul_kernel<float>, grid, block, 0, stream, gate_up, (float*)out, T, F, interleave);

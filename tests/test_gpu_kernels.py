@@ -80,6 +80,13 @@ def test_silu_mul(out_dtype):
     assert torch.equal(ops.silu_mul(inter, out_dtype, interleave=7), ops.silu_mul(gu, out_dtype))
     with pytest.raises(KernelError, match="interleaved"):
         ops.silu_mul(gu, out_dtype, interleave=8)
+    # in eights, the layout of the fused products (a kernel of its own: a thread takes 8 features), many rows and few
+    for T, F in ((5, 80), (70, 1000)):
+        gu8 = (torch.randn(T, 2 * F, generator=torch.Generator().manual_seed(T)) * 4).to(DEV)
+        inter8 = gu8.reshape(T, 2, F // 8, 8).permute(0, 2, 1, 3).reshape(T, 2 * F).contiguous()
+        got = ops.silu_mul(inter8, out_dtype, interleave=8)
+        close(got, pm.swiglu(f64(gu8)[:, :F], f64(gu8)[:, F:]), out_dtype)
+        assert torch.equal(got, ops.silu_mul(gu8, out_dtype))
 
 
 def test_add_inplace_and_decode_advance():

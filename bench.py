@@ -14,7 +14,7 @@ CUDA graphs and timed with CUDA events.  One JSON line is printed:
              all W + K; the first dozen steps after a prompt step run at the clocks the prompt left)
   prefill    one prompt of 2,048 tokens: tokens a second, and flops / time / peak
   roofline   decode: (every weight once + the live sequences' cache) / step time, against the HBM peak
-  points     decode tokens a second at batch 1 and 64 with their roofline fractions, prefill of 4,096 and 8,192 tokens,
+  points     decode tokens a second at batch 1 and 64 with their roofline fractions, prefill of 4,096 tokens (the context),
              and the benchmark's two other workloads (left out with --skip-other-models): Qwen3-0.6B sizes, 16 prompts
              with lengths uniform in [1, 2048] in one prefill step, then 128 decode steps; Qwen3-32B sizes, all 64
              layers, a 2,048-token prefill and decode at batch 1, 8 and 16 from 1,024-token prompts
@@ -449,7 +449,7 @@ def main() -> int:
                "h2d_bytes_per_step": 4 * args.batch, "d2h_bytes_per_step": 4 * args.batch,
                "steps": len(timed), "warmup_steps": len(stats.step_seconds) - len(timed),
                "value_all_steps": args.batch * stats.steps / stats.decode_seconds}
-        for n in (4096,):
+        for n in (4096,):          # the whole context of the benchmark's configuration
             ms = time_prefill(engine, torch, rng, n, reps=3)
             points[f"prefill_{n}"] = n / (ms / 1e3)
             points[f"prefill_{n}_frac"] = prefill_flops(cfgd, layers, n) / (ms / 1e3) / (peaks["bf16_tflops"] * 1e12)

@@ -115,14 +115,16 @@ template <> struct Pack4Store<bf16> {
     }
 };
 
-// The same for head size 128 rotated over all 128 values, the common case: one 16-byte load per lane (lane L holds
-// values 4L..4L+3), the rotation partner (64 values away) comes from lane L ^ 16 by shuffle, one 8- or 16-byte store.
-// A block takes one token: its eight warps share the token's heads (warp w: heads w, w + 8, ...), up to six heads' loads
-// on their way before the first is used (all of a warp's heads for a token of 48), the token's cos and sin, position and
-// page looked up once.  2,048 tokens of 32 + 2 x 8 heads: 19.7 us (3.8 TB/s); a block per four heads with one load a
-// thread, 24,576 blocks, took 27.6 us.
+// The same for head size 128 rotated over all 128 values, the common case.  Half a warp takes a head: lane L of the 16
+// holds values 4L..4L+3 and 64+4L..64+4L+3, so that a value and its rotation partner (64 places away) lie in one lane
+// and only the sum of squares crosses lanes (four shuffles).  A block takes one token: its eight warps share the
+// token's pairs of heads (warp w: pairs w, w + 8, ...), up to three pairs' loads on their way before the first is used
+// (all of a warp's for a token of 48 heads), the token's cos and sin, position and page looked up once.  A v head runs
+// through the same arithmetic with a factor, weights and cosines of one and sines of zero: x * 1 - x' * 0 is x.
+// 2,048 tokens of 32 + 2 x 8 heads: 16.8 us (4.5 TB/s); with a whole warp per head and the partner by shuffle 19.7 us (the kernel
+// issued instructions 58 % of the time and moved 29 % of what the memory can), with a block per four heads 27.6 us.
 #define RK_WARPS 8
-#define RK_HEADS_AT_ONCE 6
+#define RK_PAIRS_AT_ONCE 3
 template <typename TOut>
 __global__ void __launch_bounds__(RK_WARPS * 32)
 qk_norm_rope_store_hd128_kernel(const float* __restrict__ qkv, const float* __restrict__ q_weight,
@@ -135,54 +137,67 @@ qk_norm_rope_store_hd128_kernel(const float* __restrict__ qkv, const float* __re
     pdl_launch_dependents();
     constexpr int hd = 128;
     const int t = blockIdx.x;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, half = lane >> 4, l16 = lane & 15;
     const int n_heads = store_kv ? Hq + 2 * Hkv : Hq;               // without the cache write only q is made
     const int n_all = Hq + 2 * Hkv;
     const float4* row = reinterpret_cast<const float4*>(qkv + (size_t)t * n_all * hd);
-    const float4 c = reinterpret_cast<const float4*>(cos_t + (size_t)t * (hd / 2))[lane & 15];
-    const float4 sn = reinterpret_cast<const float4*>(sin_t + (size_t)t * (hd / 2))[lane & 15];
-    float4 wq = make_float4(1.f, 1.f, 1.f, 1.f), wk = wq;
-    if (q_weight) wq = reinterpret_cast<const float4*>(q_weight)[lane];
-    if (k_weight) wk = reinterpret_cast<const float4*>(k_weight)[lane];
+    const float4 c = reinterpret_cast<const float4*>(cos_t + (size_t)t * (hd / 2))[l16];
+    const float4 sn = reinterpret_cast<const float4*>(sin_t + (size_t)t * (hd / 2))[l16];
+    const float4 one = make_float4(1.f, 1.f, 1.f, 1.f), zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 wq_lo = one, wq_hi = one, wk_lo = one, wk_hi = one;
+    if (q_weight) { wq_lo = reinterpret_cast<const float4*>(q_weight)[l16]; wq_hi = reinterpret_cast<const float4*>(q_weight)[16 + l16]; }
+    if (k_weight) { wk_lo = reinterpret_cast<const float4*>(k_weight)[l16]; wk_hi = reinterpret_cast<const float4*>(k_weight)[16 + l16]; }
     const int p = tok_pos[t];
     const size_t page = (size_t)page_table[(size_t)tok_seq[t] * table_width + p / page_size];
-    const int h_step = RK_WARPS * gridDim.y;       // few tokens: gridDim.y blocks share a token's heads
-    for (int h0 = blockIdx.y * RK_WARPS + warp; h0 < n_heads; h0 += h_step * RK_HEADS_AT_ONCE) {
-        float4 x[RK_HEADS_AT_ONCE];
+    const int pair_step = RK_WARPS * gridDim.y;     // few tokens: gridDim.y blocks share a token's heads
+    const int n_pairs = (n_heads + 1) >> 1;
+    for (int p0 = blockIdx.y * RK_WARPS + warp; p0 < n_pairs; p0 += pair_step * RK_PAIRS_AT_ONCE) {
+        float4 lo[RK_PAIRS_AT_ONCE], hi[RK_PAIRS_AT_ONCE];
 #pragma unroll
-        for (int i = 0; i < RK_HEADS_AT_ONCE; ++i) {
-            const int head = h0 + i * h_step;
-            if (head < n_heads) x[i] = row[(size_t)head * (hd / 4) + lane];
+        for (int i = 0; i < RK_PAIRS_AT_ONCE; ++i) {
+            const int head = 2 * (p0 + i * pair_step) + half;
+            if (head < n_heads) {
+                lo[i] = row[(size_t)head * (hd / 4) + l16];
+                hi[i] = row[(size_t)head * (hd / 4) + 16 + l16];
+            } else {
+                lo[i] = hi[i] = zero;
+            }
         }
 #pragma unroll
-        for (int i = 0; i < RK_HEADS_AT_ONCE; ++i) {
-            const int head = h0 + i * h_step;
-            if (head >= n_heads) break;                            // the same for the whole warp
-            const bool is_q = head < Hq, is_k = !is_q && head < Hq + Hkv;
-            TOut* dst;
-            if (is_q) {
-                dst = q_out + ((size_t)t * Hq + head) * hd;
-            } else {
-                const int kvh = is_k ? head - Hq : head - Hq - Hkv;
-                dst = (is_k ? k_pool : v_pool) + ((page * Hkv + kvh) * page_size + (p % page_size)) * hd;
+        for (int i = 0; i < RK_PAIRS_AT_ONCE; ++i) {
+            const int pair = p0 + i * pair_step;
+            if (pair >= n_pairs) break;                            // the same for the whole warp
+            const int head = 2 * pair + half;
+            const bool live = head < n_heads, is_q = head < Hq, is_k = !is_q && head < Hq + Hkv;
+            const bool normed = live && (is_q ? q_weight != nullptr : (is_k && k_weight != nullptr));
+            float4 a = lo[i], b = hi[i];
+            float ss = a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+            ss += __shfl_xor_sync(0xffffffffu, ss, 1);             // within the 16 lanes of the head
+            ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+            ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+            ss += __shfl_xor_sync(0xffffffffu, ss, 8);
+            if (normed) {
+                const float scale = rsqrtf(ss / (float)hd + eps);
+                const float4 w_lo = is_q ? wq_lo : wk_lo, w_hi = is_q ? wq_hi : wk_hi;
+                a = make_float4(a.x * scale * w_lo.x, a.y * scale * w_lo.y, a.z * scale * w_lo.z, a.w * scale * w_lo.w);
+                b = make_float4(b.x * scale * w_hi.x, b.y * scale * w_hi.y, b.z * scale * w_hi.z, b.w * scale * w_hi.w);
             }
-            float4 y = x[i];
+            float4 ya = a, yb = b;
             if (is_q || is_k) {
-                if (is_q ? q_weight != nullptr : k_weight != nullptr) {
-                    const float ss = warp_sum(y.x * y.x + y.y * y.y + y.z * y.z + y.w * y.w);
-                    const float scale = rsqrtf(ss / (float)hd + eps);
-                    const float4 w = is_q ? wq : wk;
-                    y = make_float4(y.x * scale * w.x, y.y * scale * w.y, y.z * scale * w.z, y.w * scale * w.w);
-                }
-                float4 other;                                      // the values 64 places away
-                other.x = __shfl_xor_sync(0xffffffffu, y.x, 16);
-                other.y = __shfl_xor_sync(0xffffffffu, y.y, 16);
-                other.z = __shfl_xor_sync(0xffffffffu, y.z, 16);
-                other.w = __shfl_xor_sync(0xffffffffu, y.w, 16);
-                if (lane < 16) y = make_float4(y.x * c.x - other.x * sn.x, y.y * c.y - other.y * sn.y, y.z * c.z - other.z * sn.z, y.w * c.w - other.w * sn.w);
-                else y = make_float4(other.x * sn.x + y.x * c.x, other.y * sn.y + y.y * c.y, other.z * sn.z + y.z * c.z, other.w * sn.w + y.w * c.w);
+                ya = make_float4(a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y, a.z * c.z - b.z * sn.z, a.w * c.w - b.w * sn.w);
+                yb = make_float4(a.x * sn.x + b.x * c.x, a.y * sn.y + b.y * c.y, a.z * sn.z + b.z * c.z, a.w * sn.w + b.w * c.w);
             }
-            Pack4Store<TOut>::store(dst + 4 * lane, y);
+            if (live) {
+                TOut* dst;
+                if (is_q) {
+                    dst = q_out + ((size_t)t * Hq + head) * hd;
+                } else {
+                    const int kvh = is_k ? head - Hq : head - Hq - Hkv;
+                    dst = (is_k ? k_pool : v_pool) + ((page * Hkv + kvh) * page_size + (p % page_size)) * hd;
+                }
+                Pack4Store<TOut>::store(dst + 4 * l16, ya);
+                Pack4Store<TOut>::store(dst + 64 + 4 * l16, yb);
+            }
         }
     }
 }
@@ -208,7 +223,7 @@ extern "C" int qwb_qk_norm_rope_store(const float* qkv, const float* q_weight, c
     int share = 1;
     if (T < 592) {
         share = (592 + T - 1) / T;
-        const int most = (Hq + 2 * Hkv + RK_WARPS - 1) / RK_WARPS;
+        const int most = ((Hq + 2 * Hkv + 1) / 2 + RK_WARPS - 1) / RK_WARPS;
         if (share > most) share = most;
     }
     if (fast && dtype == QWB_DT_F32)

@@ -164,17 +164,18 @@ __global__ void rmsnorm_kernel(const float* x, const float* delta, const float* 
     }
 }
 
-// Rows of up to 4 x 4 x 256 values, no planes: the row stays in the threads' registers between the two passes (a thread's
-// four loads are issued together; 2,048 rows of 4,096: 8.6 us against 11.8 through shared memory; a decode step of 8 rows
-// 0.5 % faster).
-template <typename TOut>
+// Rows of up to 4 x ITERS x 256 values (ITERS 4 or 8: up to 4,096 or 8,192): the row stays in the threads' registers
+// between the two passes (a thread's loads are issued together; 2,048 rows of 4,096: 8.6 us against 11.8 through shared
+// memory; a decode step of 8 rows 0.5 % faster).
+template <typename TOut, int ITERS>
 __global__ void __launch_bounds__(256)
-rmsnorm_rows_kernel(const float* x, const float* delta, float* sum_out, const float* __restrict__ w, TOut* __restrict__ out,
+rmsnorm_rows_kernel(const float* x, const float* delta, const float* planes, const unsigned char* __restrict__ plane_count,
+                    size_t plane_stride, float* sum_out, const float* __restrict__ w, TOut* __restrict__ out,
                     const int* __restrict__ rows, int D, float eps) {
     pdl_launch_dependents();            // the trigger first, and the weight asked for before the wait: as in rmsnorm_kernel
-    float4 g[4];
+    float4 g[ITERS];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
+    for (int k = 0; k < ITERS; ++k) {
         const int i = threadIdx.x + k * 256;
         g[k] = i < D / 4 ? reinterpret_cast<const float4*>(w)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
@@ -184,22 +185,39 @@ rmsnorm_rows_kernel(const float* x, const float* delta, float* sum_out, const fl
     const size_t src = (size_t)(rows ? rows[r] : r) * D;
     const float4* x4 = reinterpret_cast<const float4*>(x + src);
     const float4* d4 = delta ? reinterpret_cast<const float4*>(delta + src) : nullptr;
-    float4 v[4];
+    float4 v[ITERS];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
+    for (int k = 0; k < ITERS; ++k) {
         const int i = threadIdx.x + k * 256;
         v[k] = i < D / 4 ? x4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     if (d4) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
+        for (int k = 0; k < ITERS; ++k) {
             const int i = threadIdx.x + k * 256;
             if (i < D / 4) { const float4 d = d4[i]; v[k].x += d.x; v[k].y += d.y; v[k].z += d.z; v[k].w += d.w; }
         }
     }
+    if (planes) {                       // a product left as sums over pieces of k: a column's planes, in their order
+#pragma unroll
+        for (int k = 0; k < ITERS; ++k) {
+            const int i = threadIdx.x + k * 256;
+            if (i < D / 4) {
+                const int n_planes = plane_count[4 * i / RMS_PLANE_COLS];
+                const float* p4 = planes + src + 4 * (size_t)i;
+                float4 pv[RMS_MAX_PLANES];
+#pragma unroll
+                for (int p = 0; p < RMS_MAX_PLANES; ++p)
+                    if (p < n_planes) pv[p] = *reinterpret_cast<const float4*>(p4 + p * plane_stride);
+#pragma unroll
+                for (int p = 0; p < RMS_MAX_PLANES; ++p)
+                    if (p < n_planes) { v[k].x += pv[p].x; v[k].y += pv[p].y; v[k].z += pv[p].z; v[k].w += pv[p].w; }
+            }
+        }
+    }
     float ss = 0.f;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
+    for (int k = 0; k < ITERS; ++k) {
         const int i = threadIdx.x + k * 256;
         if (sum_out && i < D / 4) reinterpret_cast<float4*>(sum_out + src)[i] = v[k];
         ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
@@ -207,7 +225,7 @@ rmsnorm_rows_kernel(const float* x, const float* delta, float* sum_out, const fl
     const float scale = rsqrtf(block_sum(ss, red) / (float)D + eps);
     TOut* o = out + (size_t)r * D;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
+    for (int k = 0; k < ITERS; ++k) {
         const int i = threadIdx.x + k * 256;
         if (i < D / 4)
             Pack4<TOut>::store(o + 4 * i, v[k].x * scale * g[k].x, v[k].y * scale * g[k].y, v[k].z * scale * g[k].z, v[k].w * scale * g[k].w);
@@ -224,8 +242,10 @@ static int launch_rmsnorm(const float* x, const float* delta, const float* plane
     const int work = vec ? D / 4 : D;
     const int block = work >= 1024 ? 256 : (work >= 256 ? 128 : 64);
     cudaError_t e = cudaSuccess;
-    if (vec && !planes && D / 4 <= 4 * 256) {
-        qwb_launch_link(n_rows, QWB_LINK_ROWS_NORM, rmsnorm_rows_kernel<TOut>, n_rows, 256, 0, stream, x, delta, sum_out, w, out, rows, D, eps);
+    if (vec && D / 4 <= 4 * 256) {
+        qwb_launch_link(n_rows, QWB_LINK_ROWS_NORM, rmsnorm_rows_kernel<TOut, 4>, n_rows, 256, 0, stream, x, delta, planes, plane_count, plane_stride, sum_out, w, out, rows, D, eps);
+    } else if (vec && D / 4 <= 8 * 256) {
+        qwb_launch_link(n_rows, QWB_LINK_ROWS_NORM, rmsnorm_rows_kernel<TOut, 8>, n_rows, 256, 0, stream, x, delta, planes, plane_count, plane_stride, sum_out, w, out, rows, D, eps);
     } else if (vec) {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(rmsnorm_kernel<TOut, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "rmsnorm: %s", cudaGetErrorString(e));

@@ -86,7 +86,7 @@ def bench_gemm(M: int, N: int, K: int, impl: str, iters: int, dtype=torch.bfloat
             "GBps": nbytes / us / 1e3, "TFLOPs": 2.0 * M * N * K / us / 1e6}
 
 
-def bench_attn_decode(B, ctx, Hq, Hkv, hd, iters, dtype=torch.bfloat16, split=0, runs_target=0, run_pages_max=0,
+def bench_attn_decode(B, ctx, Hq, Hkv, hd, iters, dtype=torch.bfloat16, split=0, runs_target=0, run_pages_max=0, max_len=0,
                       fused=False) -> dict:
     page = ops.PAGE_SIZE
     pages_per = math.ceil(ctx / page)
@@ -109,14 +109,15 @@ def bench_attn_decode(B, ctx, Hq, Hkv, hd, iters, dtype=torch.bfloat16, split=0,
             how["runs_target"] = runs_target
         if run_pages_max:
             how["run_pages_max"] = run_pages_max
-    fn = lambda i: ops.attn_decode(q, k_pool, v_pool, tables[i], seq_len, 1 / math.sqrt(hd), ctx, **how)
+    max_len = max_len or ctx            # the bound a graph is captured for may be larger than the sequences
+    fn = lambda i: ops.attn_decode(q, k_pool, v_pool, tables[i], seq_len, 1 / math.sqrt(hd), max_len, **how)
     if fused:       # the kernel that also norms and rotates q and k and writes the new key and value (what a step of few sequences runs)
         how.pop("split_tokens", None)
         qkv = torch.randn(B, (Hq + 2 * Hkv) * hd, device="cuda")
         w = torch.ones(hd, device="cuda")
         inv = torch.tensor([1e6 ** (-2.0 * i / hd) for i in range(hd // 2)], dtype=torch.float64, device="cuda")
         cos, sin = ops.rope_table(seq_len - 1, inv)
-        fn = lambda i: ops.attn_decode_fused(qkv, w, w, cos, sin, 1e-6, k_pool, v_pool, tables[i], seq_len, 1 / math.sqrt(hd), ctx,
+        fn = lambda i: ops.attn_decode_fused(qkv, w, w, cos, sin, 1e-6, k_pool, v_pool, tables[i], seq_len, 1 / math.sqrt(hd), max_len,
                                              Hq, Hkv, hd, **how)
     us = _time(fn, copies, iters)
     nbytes = 2 * B * ctx * Hkv * hd * elem
@@ -203,6 +204,7 @@ def main() -> int:
     ap.add_argument("--top-p", type=float, default=0.95)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--tile-n", type=int, default=None)
+    ap.add_argument("--max-len", type=int, default=0, help="decode attention: the bound on the lengths (default: the context)")
     ap.add_argument("--split", type=int, default=0, help="keys per run of the decode attention kernel (0: its own choice)")
     ap.add_argument("--runs-target", type=int, default=0, help="tensor-core decode attention: about this many runs a sequence")
     ap.add_argument("--run-pages-max", type=int, default=0, help="tensor-core decode attention: at most this many pages a run")
@@ -219,7 +221,7 @@ def main() -> int:
             print(json.dumps(r))
     elif args.what == "attn_decode":
         print(json.dumps(bench_attn_decode(args.batch, args.ctx, args.heads, args.kv_heads, args.head_dim, args.iters, dtype, args.split,
-                                           args.runs_target, args.run_pages_max, args.fused)))
+                                           args.runs_target, args.run_pages_max, fused=args.fused, max_len=args.max_len)))
     elif args.what == "sample":
         print(json.dumps(bench_sample(args.batch, args.vocab, args.temp, args.top_k, args.top_p, args.iters)))
     elif args.what == "attn_prefill":

@@ -180,17 +180,56 @@ def toy_routed_plan(cfg: ToyRoutedConfig) -> ModelPlan:
                                               "tied_to": "emb.weight"}))
 
 
-def test_toy_architecture_with_routing_and_two_position_encodings():
+def toy_routed_plain_logits(w, toks, n_experts):
+    """The toy architecture of ``toy_routed_plan`` in NumPy, whole sequence, no cache, from the parts' formulas: what
+    the assembled engine is compared with (not the engine with itself)."""
+    T = len(toks)
+    pos = np.arange(T)
+    h = w["emb.weight"][np.asarray(toks)]
+    for i in range(3):
+        px = f"layers.{i}."
+        wide = i != 1
+        Hq, Hkv, hd = (4, 2, 16) if wide else (3, 1, 32)
+        x = pm.rms_norm(h, w[px + "input_layernorm.weight"], 1e-6)
+        q = pm.linear(x, w[px + "self_attn.q_proj.weight"]).reshape(T, Hq, hd)
+        k = pm.linear(x, w[px + "self_attn.k_proj.weight"]).reshape(T, Hkv, hd)
+        v = pm.linear(x, w[px + "self_attn.v_proj.weight"]).reshape(T, Hkv, hd)
+        if wide:                                        # per-head norm, then the slowed rotation over all 16 values
+            q = pm.rms_norm(q, w[px + "self_attn.q_norm.weight"], 1e-6)
+            k = pm.rms_norm(k, w[px + "self_attn.k_norm.weight"], 1e-6)
+            ang, rot, window = pm.rope_angles(pos / 3.0, 16, 1e3), 16, None
+        else:                                           # the library's rotation over all 32 values, a window of 24 keys
+            ang, rot, window = pm.rope_angles(pos, 32, 1e4), 32, 24
+        q, k = pm.apply_rope_neox(q, ang, rot), pm.apply_rope_neox(k, ang, rot)
+        att = pm.attention_causal(q, k, v, window=window).reshape(T, Hq * hd)
+        h = h + pm.linear(att, w[px + "self_attn.o_proj.weight"])
+        x = pm.rms_norm(h, w[px + "post_attention_layernorm.weight"], 1e-6)
+        if wide:
+            ff, _ = plain_top_one(x, w, px + "mlp.", n_experts, lambda a: a)
+        else:
+            ff = pm.linear(pm.swiglu(pm.linear(x, w[px + "mlp.gate_proj.weight"]), pm.linear(x, w[px + "mlp.up_proj.weight"])),
+                           w[px + "mlp.down_proj.weight"])
+        h = h + ff
+    return pm.linear(pm.rms_norm(h, w["norm.weight"], 1e-6), w["lm_head.weight"])
+
+
+def test_toy_architecture_with_routing_and_two_position_encodings(tmp_path):
+    import questwend_b200 as qw
     register_feed_forward("toy_top_one", TopOneExperts, replace=True)
     register_position("toy_slowed_rotary", SlowedRotary, replace=True)
     register_architecture("ToyRoutedForCausalLM", ToyRoutedConfig, toy_routed_plan, replace=True)
-    eng = Engine.from_config(ToyRoutedConfig(48, 61, 3), seed=3, dtype="float32", max_tokens=512)
+    folder = qw.write_model_folder(str(tmp_path / "toy"), ToyRoutedConfig(48, 61, 3), 3, "float32")
+    w = {k: v.astype(np.float64) for k, v in pm.read_safetensors(folder + "/model.safetensors").items()}
+    eng = Engine.from_folder(folder, dtype="float32", max_tokens=512)
     assert eng.cache.n_groups() == 2                                     # heads 2x16 without window, 1x32 with one
     rng = np.random.default_rng(4)
     seqs = [rng.integers(0, 61, n).tolist() for n in (41, 7, 90)]
     slots = eng.open_sequences(3)
     whole = eng.step([StepEntry(s, t, list(range(len(t)))) for s, t in zip(slots, seqs)]).cpu().numpy()
     eng.close_sequences(slots)
+    # the assembled toy against its NumPy model: every row of every sequence
+    ref = np.concatenate([toy_routed_plain_logits(w, t, 3) for t in seqs])
+    assert rel_err(whole, ref) < FP32_TOL
     # again, each alone: a prompt, then the last 6 tokens one by one, in slots that were used before
     off = 0
     for t in seqs:

@@ -286,3 +286,31 @@ def test_products_left_in_pieces_for_the_next_norm(folders, name, monkeypatch):
     prompts = [[3, 14, 15, 92, 65], [35, 89, 79], [32, 38, 46, 26, 43, 38, 32, 79, 50]]
     want = [pm.greedy_continue(cfg, w, p, 12, round16="bf16") for p in prompts]
     assert [r.tokens for r in qw.generate(eng, prompts, max_new_tokens=12, ignore_eos=True)] == want
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_decoding_after_a_rewind(folders, name, dtype):
+    """The reference's rewind (core/runtime.cpp:2804-2811): a sequence is cut back to a shorter length and goes on with
+    other tokens.  The keys and values beyond the cut stay in their pages (nothing is zeroed) and must neither be read nor
+    survive: 150 tokens, cut back to 70 (into the second page) and to 64 (a page's edge), then 40 other tokens, some as a
+    short prompt and the rest one by one, against the plain implementation on the sequence as it now is."""
+    folder = folders[name, dtype]
+    cfg, w = pm.read_model_folder(folder)
+    eng = qw.Engine.from_folder(folder, dtype=dtype, max_tokens=512)
+    rng = np.random.default_rng(8)
+    first = rng.integers(0, cfg["vocab_size"], 150).tolist()
+    (s,) = eng.open_sequences(1)
+    eng.step([StepEntry(s, first, [])])
+    for keep in (70, 64):
+        eng.cache.truncate(s, keep)
+        assert eng.cache.length(s) == keep
+        other = rng.integers(0, cfg["vocab_size"], 40).tolist()
+        ref = pm.forward_logits(cfg, w, first[:keep] + other, round16=None if dtype == "float32" else "bf16")[keep:]
+        rows = list(eng.step([StepEntry(s, other[:9], list(range(9)))]).cpu().numpy())
+        for t in other[9:]:
+            rows.append(eng.step([StepEntry(s, [t], [0])]).cpu().numpy()[0])
+        err = np.abs(np.stack(rows) - ref).max(axis=1) / np.abs(ref).max()
+        assert err.max() < tol(dtype), f"after a cut to {keep}: first position off: {keep + int(np.argmax(err > tol(dtype)))}"
+    eng.close_sequences([s])
+    assert eng.cache.free_pages() == [eng.cache.n_pages]

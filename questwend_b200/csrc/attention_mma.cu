@@ -393,13 +393,14 @@ __device__ __forceinline__ void fused_new_row(const FusedQKV& f, const float* sr
     }
 }
 
-template <int HD, bool FUSED>
+template <int HD, bool FUSED, bool K_TWO>
 __global__ void __launch_bounds__(32)
 attn_mma_decode_kernel(const FusedQKV fused, const bf16* q, const bf16* k_pool, const bf16* v_pool,
                        const int* __restrict__ page_table, const int* __restrict__ seq_len, float* __restrict__ part_acc,
                        float* __restrict__ part_m, float* __restrict__ part_l, bf16* __restrict__ out, int Hq, int Hkv,
                        int table_width, float scale, int window, int runs_target, int run_pages_max, int max_runs, int Gc,
                        int chunks) {
+    constexpr bool k_two = K_TWO;
     // Launched with programmatic stream serialization, the block may start while the kernel before it still runs.
     // FUSED, that kernel is the q/k/v projection, and what the block needs first does not come from it: the sequences'
     // lengths and page tables were set before the step, and the keys and values of earlier tokens in earlier steps.  So
@@ -430,16 +431,25 @@ attn_mma_decode_kernel(const FusedQKV fused, const bf16* q, const bf16* k_pool, 
     // The run's pages one after the other, through one K and one V buffer: as soon as the scores of a page are formed
     // its K buffer takes the next page's K, and after O += P V its V buffer the next page's V, so that the copies of
     // page i + 1 run under the arithmetic of page i.  The first page's copies go out before anything else.
-    bf16* k_tile = my_tiles;
+    // k_two (the host gives the block a third tile when all blocks still find room on the SMs): K has two buffers, so
+    // that the next page's K is asked for a page ahead - the second page's with the first, before anything else - and
+    // only V waits for its buffer.  The arithmetic is the same either way.
+    bf16* k_tiles[2] = {my_tiles, k_two ? my_tiles + 2 * AM_TILE * HD : my_tiles};
     bf16* v_tile = my_tiles + AM_TILE * HD;
     int base_tok = max(tok_begin, (k_lo / AM_TILE) * AM_TILE);                 // pages wholly before the window are skipped
     if (base_tok < tok_end) {
         const size_t src = ((size_t)pages[base_tok / AM_TILE] * Hkv + kvh) * AM_TILE * HD;
         const int n_valid = min(AM_TILE, len - base_tok);
-        load_tile<HD>(k_tile, k_pool + src, n_valid, lane, 32);
+        load_tile<HD>(k_tiles[0], k_pool + src, n_valid, lane, 32);
         cp_async_commit();
         load_tile<HD>(v_tile, v_pool + src, n_valid, lane, 32);
         cp_async_commit();
+        if (k_two && base_tok + AM_TILE < tok_end) {
+            const int next_tok = base_tok + AM_TILE;
+            const size_t src1 = ((size_t)pages[next_tok / AM_TILE] * Hkv + kvh) * AM_TILE * HD;
+            load_tile<HD>(k_tiles[1], k_pool + src1, min(AM_TILE, len - next_tok), lane, 32);
+            cp_async_commit();
+        }
     }
 
     if (page_first) pdl_wait();
@@ -488,7 +498,9 @@ attn_mma_decode_kernel(const FusedQKV fused, const bf16* q, const bf16* k_pool, 
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f}, o[HD / 8][4];
 #pragma unroll
     for (int d = 0; d < HD / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+    if constexpr (!K_TWO) {
     for (; base_tok < tok_end; base_tok += AM_TILE) {
+        bf16* k_tile = k_tiles[0];
         const int next_tok = base_tok + AM_TILE;
         const bool more = next_tok < tok_end;
         size_t src = 0;
@@ -519,6 +531,50 @@ attn_mma_decode_kernel(const FusedQKV fused, const bf16* q, const bf16* k_pool, 
             load_tile<HD>(v_tile, v_pool + src, n_valid, lane, 32);
             cp_async_commit();
         }
+    }
+    } else {
+    for (int page_i = 0; base_tok < tok_end; base_tok += AM_TILE, ++page_i) {
+        const int next_tok = base_tok + AM_TILE;
+        const bool more = next_tok < tok_end, more2 = next_tok + AM_TILE < tok_end;
+        bf16* k_tile = k_tiles[page_i & 1];
+        size_t src = 0;
+        int n_valid = 0;
+        if (more) {
+            src = ((size_t)pages[next_tok / AM_TILE] * Hkv + kvh) * AM_TILE * HD;
+            n_valid = min(AM_TILE, len - next_tok);
+        }
+        float s[AM_TILE / 8][4], sbase[2];
+        // this page's K has landed (its V may not have; with two K buffers neither the next page's K, asked for before V)
+        if (k_two && more) cp_async_wait<2>(); else cp_async_wait<1>();
+        __syncwarp();
+        const bool new_here = has_new && new_pos >= base_tok && new_pos < base_tok + AM_TILE;
+        if (new_here) { patch(k_tile, new_k); __syncwarp(); }
+        tile_scores<HD, AM_TILE>(qf, k_tile, base_tok, row_pos, len, window, sl2, m, l, o, lane, 0, s, sbase);
+        __syncwarp();                                                           // every lane is done reading K
+        bool started = false;                                                   // a copy of K started just now
+        if (k_two) {
+            if (more2) {                                                        // the page after the next into this page's buffer
+                const int tok2 = next_tok + AM_TILE;
+                const size_t src2 = ((size_t)pages[tok2 / AM_TILE] * Hkv + kvh) * AM_TILE * HD;
+                load_tile<HD>(k_tile, k_pool + src2, min(AM_TILE, len - tok2), lane, 32);
+                cp_async_commit();
+                started = true;
+            }
+        } else if (more) {
+            load_tile<HD>(k_tile, k_pool + src, n_valid, lane, 32);
+            cp_async_commit();
+            started = true;
+        }
+        if (started) cp_async_wait<1>(); else cp_async_wait<0>();               // all but the copy just started: this page's V
+        __syncwarp();
+        if (new_here) { patch(v_tile, new_v); __syncwarp(); }
+        tile_pv<HD, AM_TILE>(v_tile, s, sbase, sl2, l, o, lane, 0);
+        __syncwarp();                                                           // every lane is done reading V
+        if (more) {
+            load_tile<HD>(v_tile, v_pool + src, n_valid, lane, 32);
+            cp_async_commit();
+        }
+    }
     }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -659,22 +715,45 @@ extern "C" int qwb_attn_mma_prefill(const void* q, const void* k_pool, const voi
     return launch_prefill<128>(q, k_pool, v_pool, page_table, cu_seqlens, pos0, out, B, max_new, Hq, Hkv, table_width, scale, window, stream);
 }
 
+static int am_sm_count() {
+    static int n_sm = 0;
+    if (!n_sm) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
+    }
+    return n_sm;
+}
+
 template <int HD, bool FUSED>
 static int launch_decode(const FusedQKV& fused, const void* q, const void* k_pool, const void* v_pool, const int* page_table,
                          const int* seq_len, float* scratch, void* out, int B, int Hq, int Hkv, int table_width, float scale,
                          int window, int runs_target, int run_pages_max, int max_runs, cudaStream_t stream) {
     const int G = Hq / Hkv, Gc = group_chunk(G), chunks = (G + Gc - 1) / Gc;
-    const size_t smem = (size_t)2 * AM_TILE * HD * sizeof(bf16);
-    cudaError_t e = cudaFuncSetAttribute(attn_mma_decode_kernel<HD, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "attn_mma_decode: %s", cudaGetErrorString(e));
+    // A third tile (two for K) while every block of the grid still finds room: 4 blocks of 48 KB an SM.  Decode steps at
+    // the Qwen3-8B sizes: the same with one or two sequences of 1,024 keys, 2 % faster with 4; 5 % faster with 4 of
+    // 4,096 and 2.7 % with one of 16,384.  With 8 sequences and a bound of 2,048 keys the grid has 1,024 blocks: 1.7 %
+    // faster while they have 1,040 keys (576 blocks with keys), 7 % slower at 4,096 (all 1,024): so by the grid, which is
+    // all that the host knows.  The kernel without it keeps its loop as it was: one loop for both cost a step of 8
+    // sequences 0.7 %.
+    // QWB200_ATTN_K2=0 switches it off, for measurements.
+    static const bool k_two_allowed = [] { const char* e = getenv("QWB200_ATTN_K2"); return !(e && e[0] == '0'); }();
+    const bool k_two = k_two_allowed && (long long)Hkv * chunks * B * max_runs <= 4LL * am_sm_count();
+    const size_t smem = (size_t)(k_two ? 3 : 2) * AM_TILE * HD * sizeof(bf16);
     float* part_acc = scratch;
     float* part_m = scratch + (size_t)B * Hq * max_runs * HD;
     float* part_l = part_m + (size_t)B * Hq * max_runs;
     dim3 grid(Hkv * chunks, B, max_runs);
     // early: see the kernel's first lines
-    qwb_launch_early(attn_mma_decode_kernel<HD, FUSED>, grid, 32, smem, stream, fused, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool,
-        page_table, seq_len, part_acc, part_m, part_l, (bf16*)out, Hq, Hkv, table_width, scale, window, runs_target, run_pages_max,
-        max_runs, Gc, chunks);
+    auto go = [&](auto kernel) -> int {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return qwb_fail(QWB_ERR_CUDA, "attn_mma_decode: %s", cudaGetErrorString(e));
+        qwb_launch_early(kernel, grid, 32, smem, stream, fused, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, page_table, seq_len,
+                         part_acc, part_m, part_l, (bf16*)out, Hq, Hkv, table_width, scale, window, runs_target, run_pages_max, max_runs,
+                         Gc, chunks);
+        return 0;
+    };
+    if (int rc = k_two ? go(attn_mma_decode_kernel<HD, FUSED, true>) : go(attn_mma_decode_kernel<HD, FUSED, false>)) return rc;
     if (int rc = qwb_check_launch("attn_mma_decode")) return rc;
     if (max_runs > 1) {
         // (launched early with more sequences, even with its trigger after its wait, a step of 8 got 1 % slower)

@@ -77,6 +77,11 @@ def bench_gemm(M: int, N: int, K: int, impl: str, iters: int, dtype=torch.bfloat
         fn = lambda i: ops.gemm_tc(x, ws[i], epilogue="add", out=acc, tile_n=tile_n)
     elif impl == "tc_swiglu":
         fn = lambda i: ops.gemm_tc(x, ws[i], epilogue="swiglu", tile_n=tile_n)
+    elif impl == "library_add":
+        acc = torch.zeros(M, N, device="cuda")
+        fn = lambda i: torch.addmm(acc, x, ws[i].t(), out_dtype=torch.float32, out=acc)
+    elif impl == "library_swiglu":
+        fn = lambda i: ops.silu_mul(torch.mm(x, ws[i].t(), out_dtype=torch.float32), torch.bfloat16, ops.GATE_UP_GROUP)
     else:
         fn = (lambda i: torch.mm(x, ws[i].t(), out_dtype=torch.float32)) if dtype == torch.bfloat16 else \
              (lambda i: torch.mm(x, ws[i].t()))
@@ -190,7 +195,7 @@ def main() -> int:
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=24576)
     ap.add_argument("--k", type=int, default=4096)
-    ap.add_argument("--impl", default="stream", choices=["stream", "stream_swiglu", "ring", "ring_swiglu", "ring_add", "ring_split", "small", "library", "tc", "tc_add", "tc_swiglu"])
+    ap.add_argument("--impl", default="stream", choices=["stream", "stream_swiglu", "ring", "ring_swiglu", "ring_add", "ring_split", "small", "library", "tc", "tc_add", "tc_swiglu", "library_add", "library_swiglu"])
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=1152)

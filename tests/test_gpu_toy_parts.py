@@ -1,5 +1,6 @@
 """Toy parts, defined here and registered without touching the library's files: a feed-forward that routes
-each token to one of a few small experts, and a position encoding other than the library's own.  They show
+each token to one of a few small experts, a position encoding other than the library's own, and a norm other
+than the library's own.  They show
 that a layer's parts are chosen by kind, layer by layer, and that the step function, the cache and the
 schedule do not care what the parts are.  The toys are written with torch operations; they are a test's
 toys, not anyone's model (needs a B200)."""
@@ -15,9 +16,9 @@ from questwend_b200.cache import CacheManager
 from questwend_b200.config import ConfigReader, ModelConfig, register_architecture
 from questwend_b200.engine.engine import Engine, StepEntry, build_step_context
 from questwend_b200.engine.plan import LayerSpec, ModelPlan, Run
-from questwend_b200.parts import (FeedForward, PartSpec, PositionEncoding, Runtime, build_part, register_feed_forward,
-                                  register_position)
-from questwend_b200.weights import MATRIX, TensorSpec, random_tensors
+from questwend_b200.parts import (FeedForward, Norm, PartSpec, PositionEncoding, Runtime, build_part, register_feed_forward,
+                                  register_norm, register_position)
+from questwend_b200.weights import MATRIX, NORM_WEIGHT, VECTOR, TensorSpec, random_tensors
 
 pytestmark = pytest.mark.gpu
 DEV = torch.device("cuda:0")
@@ -241,4 +242,150 @@ def test_toy_architecture_with_routing_and_two_position_encodings(tmp_path):
         eng.close_sequences([slot])
         assert rel_err(np.stack(rows), whole[off:off + len(t)]) < FP32_TOL
         off += len(t)
+    assert eng.cache.slots.n_free == eng.max_batch
+
+
+# ----------------------------------------------------------------------------- another norm
+class CenteredNorm(Norm):
+    """y = c * rsqrt(mean(c^2) + eps) * w with c = v - mean(v), v = x (+ delta).  params: dim, eps; tensor: <prefix>weight.
+    It does not say ``adds_split_sums``: a product that was left as sums over pieces of k is added onto the residual
+    stream before this norm is called, and it never sees one."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.dim, self.eps, self.weight = int(spec.params["dim"]), float(spec.params["eps"]), None
+        self.saw = []
+
+    def tensors(self):
+        return [TensorSpec(self.prefix + "weight", (self.dim,), VECTOR, NORM_WEIGHT)]
+
+    def bind(self, weights):
+        self.weight = weights[self.prefix + "weight"].to(torch.float32).contiguous()
+
+    def kernel_modules(self):
+        return ()
+
+    def forward(self, x, delta=None, write_sum=False, rows=None, out_dtype=None):
+        self.saw.append(type(delta).__name__)
+        v = x if delta is None else x + delta
+        if write_sum and delta is not None:
+            x.copy_(v)
+        if rows is not None:
+            v = v[rows.long()]
+        c = v - v.mean(dim=1, keepdim=True)
+        return (c * torch.rsqrt((c * c).mean(dim=1, keepdim=True) + self.eps) * self.weight).to(out_dtype or self.runtime.dtype)
+
+
+@dataclass(frozen=True)
+class ToyCenteredConfig(ModelConfig):
+    hidden_size: int
+    vocab_size: int
+    eps: float
+    architecture = "ToyCenteredForCausalLM"
+
+    @classmethod
+    def from_reader(cls, r: ConfigReader):
+        return cls(r.integer("hidden_size"), r.integer("vocab_size"), r.number("eps"))
+
+    def to_dict(self):
+        return {"architectures": [self.architecture], "hidden_size": self.hidden_size, "vocab_size": self.vocab_size,
+                "eps": self.eps}
+
+
+def toy_centered_plan(cfg: ToyCenteredConfig) -> ModelPlan:
+    D = cfg.hidden_size
+    norm = PartSpec("toy_centered", {"dim": D, "eps": cfg.eps})
+    layer = lambda i: LayerSpec(PartSpec("pre_norm", {}, prefix=f"layers.{i}."),
+                                PartSpec("gqa", {"hidden_size": D, "n_heads": 4, "n_kv_heads": 2, "head_dim": 16}),
+                                PartSpec("gated_mlp", {"hidden_size": D, "intermediate_size": 72}), norm,
+                                PartSpec("rotary_neox", {"theta": 1e4, "rotary_dim": 16}))
+    return ModelPlan(architecture=cfg.architecture, hidden_size=D, vocab_size=cfg.vocab_size,
+                     embedding=PartSpec("token", {"vocab_size": cfg.vocab_size, "hidden_size": D, "name": "emb.weight"}),
+                     layers=[layer(0), layer(1)], schedule=[Run(0), Run(1)],
+                     final_norm=PartSpec("toy_centered", {"dim": D, "eps": cfg.eps}, prefix="norm."),
+                     head=PartSpec("linear", {"vocab_size": cfg.vocab_size, "hidden_size": D, "tied": True,
+                                              "tied_to": "emb.weight"}))
+
+
+def toy_centered_plain_logits(w, toks, eps):
+    """``toy_centered_plan`` in NumPy: whole sequence, no cache."""
+    def norm(v, weight):
+        c = v - v.mean(axis=-1, keepdims=True)
+        return c / np.sqrt((c * c).mean(axis=-1, keepdims=True) + eps) * weight
+
+    T = len(toks)
+    h = w["emb.weight"][np.asarray(toks)]
+    ang = pm.rope_angles(np.arange(T), 16, 1e4)
+    for i in range(2):
+        px = f"layers.{i}."
+        x = norm(h, w[px + "input_layernorm.weight"])
+        q = pm.apply_rope_neox(pm.linear(x, w[px + "self_attn.q_proj.weight"]).reshape(T, 4, 16), ang, 16)
+        k = pm.apply_rope_neox(pm.linear(x, w[px + "self_attn.k_proj.weight"]).reshape(T, 2, 16), ang, 16)
+        v = pm.linear(x, w[px + "self_attn.v_proj.weight"]).reshape(T, 2, 16)
+        h = h + pm.linear(pm.attention_causal(q, k, v).reshape(T, 64), w[px + "self_attn.o_proj.weight"])
+        x = norm(h, w[px + "post_attention_layernorm.weight"])
+        h = h + pm.linear(pm.swiglu(pm.linear(x, w[px + "mlp.gate_proj.weight"]), pm.linear(x, w[px + "mlp.up_proj.weight"])),
+                          w[px + "mlp.down_proj.weight"])
+    return pm.linear(norm(h, w["norm.weight"]), w["emb.weight"])
+
+
+def test_toy_architecture_with_another_norm(tmp_path, monkeypatch):
+    """A norm registered from here takes the library norm's place in the blocks and before the head: the 32-bit engine
+    against the NumPy model of the toy; then the bfloat16 engine with its o and down products forced into the ring
+    product's split form, whose sums over pieces of k this norm cannot add: the block adds them first, the norm sees
+    tensors only, and the logits are the ones without the split form, beyond rounding; generation from graphs gives the
+    tokens of generation without them."""
+    import questwend_b200 as qw
+    from questwend_b200.kernels import ops
+    register_norm("toy_centered", CenteredNorm, replace=True)
+    register_architecture("ToyCenteredForCausalLM", ToyCenteredConfig, toy_centered_plan, replace=True)
+    rng = np.random.default_rng(8)
+    seqs = [rng.integers(0, 53, n).tolist() for n in (23, 5, 38)]
+    folder, ref = {}, {}
+    for dtype in ("float32", "bfloat16"):
+        folder[dtype] = qw.write_model_folder(str(tmp_path / dtype), ToyCenteredConfig(40, 53, 1e-5), 5, dtype)
+        w = {k: v.astype(np.float64) for k, v in pm.read_safetensors(folder[dtype] + "/model.safetensors").items()}
+        ref[dtype] = [toy_centered_plain_logits(w, t, 1e-5) for t in seqs]
+
+    def run(eng):                       # a batch of unequal prompts cut 4 tokens before their ends, then token by token
+        slots = eng.open_sequences(3)
+        rows = [list(r) for r in np.split(eng.step([StepEntry(s, t[:-4], list(range(len(t) - 4))) for s, t in zip(slots, seqs)])
+                                          .cpu().numpy(), np.cumsum([len(t) - 4 for t in seqs])[:-1])]
+        for i in range(4):
+            out = eng.step([StepEntry(s, [t[len(t) - 4 + i]], [0]) for s, t in zip(slots, seqs)]).cpu().numpy()
+            for r, o in zip(rows, out):
+                r.append(o)
+        eng.close_sequences(slots)
+        return [np.stack(r) for r in rows]
+
+    eng = Engine.from_folder(folder["float32"], dtype="float32", max_tokens=512)
+    for got, want in zip(run(eng), ref["float32"]):
+        assert rel_err(got, want) < FP32_TOL
+    plain = run(Engine.from_folder(folder["bfloat16"], dtype="bfloat16", max_tokens=512))
+    for got, want in zip(plain, ref["bfloat16"]):
+        assert rel_err(got, want) < 4 * BF16_TOL                        # the NumPy model rounds no activation to 16 bits
+
+    used = []
+
+    def forced(N, K, n_sm, device):
+        blocks = min(5, -(-N // 16) * -(-K // 256))
+        counts = ops.ring_split_counts(N, K, blocks)
+        if max(counts) > ops.RING_SPLIT_MAX_PLANES:
+            return None
+        used.append((N, K))
+        return blocks, max(counts), torch.tensor(counts, dtype=torch.uint8, device=device)
+
+    monkeypatch.setattr(ops, "_ring_split_plan", forced)
+    monkeypatch.setattr(ops, "_RING_PLANS", {})
+    eng = Engine.from_folder(folder["bfloat16"], dtype="bfloat16", max_tokens=512)
+    split = run(eng)
+    assert used, "no matrix took the split form"
+    for got, want in zip(split, plain):
+        assert rel_err(got, want) < BF16_TOL
+    norms = [p for b in eng.model.blocks for p in (b.norm1, b.norm2)] + [eng.model.final_norm]
+    assert all(isinstance(n, CenteredNorm) for n in norms)
+    assert {kind for n in norms for kind in n.saw} <= {"Tensor", "NoneType"}
+    prompts = [[3, 14, 15, 9, 26], [35, 8, 7], [32, 38, 46, 26, 43, 38, 32]]
+    with_graphs = [r.tokens for r in qw.generate(eng, prompts, max_new_tokens=10, ignore_eos=True)]
+    assert with_graphs == [r.tokens for r in qw.generate(eng, prompts, max_new_tokens=10, ignore_eos=True, use_graph=False)]
     assert eng.cache.slots.n_free == eng.max_batch

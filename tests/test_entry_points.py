@@ -81,3 +81,59 @@ def test_bench_refuses_more_than_one_gpu_with_one_line():
     assert p.returncode == 2
     lines = [line for line in (p.stdout + p.stderr).splitlines() if line.strip()]
     assert len(lines) == 1 and "one GPU" in lines[0]
+
+
+def test_replay_protocol_with_a_stand_in_engine(tmp_path, monkeypatch, capsys):
+    """trace_run's own part of the work: a slot per request at its first step, a file only for a step that wants
+    logits (rows in the order of the entries and of ``want``), ``done <step>`` after every step, slots given back at
+    ``end``.  The engine is a stand-in that records its calls; the real one is replayed in the GPU tests."""
+    import io
+
+    import numpy as np
+    import torch
+
+    from questwend_b200 import replay
+    from questwend_b200.engine import engine as engine_module
+
+    calls = []
+
+    class StandIn:
+        def __init__(self):
+            self.free = list(range(5))
+
+        def open_sequences(self, n):
+            got, self.free = self.free[:n], self.free[n:]
+            calls.append(("open", got))
+            return got
+
+        def close_sequences(self, slots):
+            calls.append(("close", list(slots)))
+            self.free = sorted(self.free + list(slots))
+
+        def step(self, entries):
+            calls.append(("step", [(e.slot, list(e.tokens), list(e.want)) for e in entries]))
+            rows = [[e.slot, e.tokens[w], w] for e in entries for w in e.want]
+            return torch.tensor(rows, dtype=torch.float32).reshape(len(rows), 3)
+
+    made = {}
+
+    def from_folder(folder, **kw):
+        made.update(kw, folder=folder)
+        return StandIn()
+
+    monkeypatch.setattr(engine_module.Engine, "from_folder", staticmethod(from_folder))
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]}, {"id": "b", "tokens": [9], "want": [0]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": [4], "want": []}, {"id": "b", "tokens": [7], "want": []}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": [8], "want": [0]}], "end": ["a"]},
+             {"step": 3, "entries": [{"id": "c", "tokens": [1, 2], "want": [1]}], "end": ["c", "never-seen"]}]
+    monkeypatch.setattr(sys, "stdin", io.StringIO("".join(json.dumps(s) + "\n" for s in steps) + "\n"))
+    out = tmp_path / "out"
+    assert replay.main(["--model", "somewhere", "--dtype", "float32", "--out", str(out), "--max-tokens", "200"]) == 0
+    assert made["folder"] == "somewhere" and made["dtype"] == "float32" and made["max_tokens"] == 200 and made["max_batch"] == 4
+    assert capsys.readouterr().out.split() == ["done", "0", "done", "1", "done", "2", "done", "3"]
+    assert sorted(os.listdir(out)) == ["0.f32", "2.f32", "3.f32"]                  # step 1 wanted nothing
+    assert np.fromfile(out / "0.f32", dtype="<f4").reshape(3, 3).tolist() == [[0, 5, 0], [0, 3, 2], [1, 9, 0]]
+    assert np.fromfile(out / "2.f32", dtype="<f4").tolist() == [0, 8, 0]
+    assert np.fromfile(out / "3.f32", dtype="<f4").tolist() == [0, 2, 1]           # c in a slot that was given back
+    assert [c for c in calls if c[0] != "step"] == [("open", [0]), ("open", [1]), ("close", [1]), ("close", [0]), ("open", [0]),
+                                                    ("close", [0])]

@@ -314,3 +314,16 @@ def test_decoding_after_a_rewind(folders, name, dtype):
         assert err.max() < tol(dtype), f"after a cut to {keep}: first position off: {keep + int(np.argmax(err > tol(dtype)))}"
     eng.close_sequences([s])
     assert eng.cache.free_pages() == [eng.cache.n_pages]
+
+
+def test_the_smoke_entry_point():
+    """What the build's smoke check does (a few greedy tokens of a tiny random model in both dtypes against the plain
+    implementation, and a 640-token prompt): it raises on a mismatch."""
+    import importlib.util
+    import os
+
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "__graft_entry__.py")
+    spec = importlib.util.spec_from_file_location("graft_entry_for_test", path)
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    module.smoke()
